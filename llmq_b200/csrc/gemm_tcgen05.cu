@@ -1,0 +1,381 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[M,N] (+)= alpha * A * B^T (+ bias[N]),   fp32 accumulation in tensor memory.
+//
+// Operands are bf16 or 8-bit floats (e4m3 / e5m2).  Each operand may be stored K-major
+// (row = M/N index, K contiguous) or MN-major (row = K index, M/N contiguous); the MN-major
+// form is what lets the backward GEMMs (dX = dY * W, dW = dY^T * X) read the very same tensors
+// as the forward pass without any transpose kernel.  alpha is the product of two optional
+// per-tensor dequantisation factors read from device memory, so no host synchronisation is
+// needed between the abs-max reduction and the GEMM.
+//
+// Replaces the cuBLASLt wrapper and the mma.sync kernel of the reference
+// (src/kernels/matmul.cpp:46-153, src/kernels/gemm_mma.cu:21-291).
+//
+// Structure (192 threads per CTA, one CTA per SM):
+//   warp 0     TMA producer: fills a 4-stage ring of 128x(128 B) A and 256x(128 B) B tiles
+//   warp 1     MMA issuer (one elected lane): 4 tcgen05.mma per stage into one of two
+//              128x256 fp32 accumulators in TMEM, tcgen05.commit to free the stage
+//   warps 2-5  epilogue: tcgen05.ld the finished accumulator (while the other one is being
+//              computed), scale, add bias, optionally add the previous C, track abs-max, store
+#include "ptx_sm100.cuh"
+#include "api.h"
+#include "common.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int ROW_BYTES = 128;            // one swizzle row
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * ROW_BYTES;   // 16 KiB
+constexpr int B_STAGE_BYTES = BN * ROW_BYTES;   // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;            // two 256-column accumulators
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmParams {
+    int M, N, K;
+    int elem_bytes;        // 1 or 2
+    int a_mn_major, b_mn_major;
+    int a_fmt, b_fmt;      // instruction-descriptor format codes
+    void* C;
+    long long ldc;         // elements
+    int c_dtype;           // 0 = bf16, 1 = fp32
+    int accumulate;
+    const void* bias;      // bf16 or fp32 (bias_dtype) or null, indexed by N
+    int bias_dtype;
+    const float* scale_a;  // optional dequant factors
+    const float* scale_b;
+    float alpha;
+    float* absmax_out;     // optional
+    unsigned int* status;  // error word
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    // Grouped rasterisation: 16 row tiles share every column tile while it is hot in L2.
+    constexpr int G = 16;
+    int per_group = G * tiles_n;
+    int group = t / per_group;
+    int first_m = group * G;
+    int gsz = min(tiles_m - first_m, G);
+    int r = t - group * per_group;
+    tm = first_m + (r % gsz);
+    tn = r / gsz;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128B-swizzled tiles must start on a 1024-byte boundary
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int bk = ROW_BYTES / p.elem_bytes;          // K elements per stage (K-major row)
+    const int k_iters = (p.K + bk - 1) / bk;
+    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            int stage = 0; uint32_t phase = 0;
+            const int mn_chunk = ROW_BYTES / p.elem_bytes;     // M/N elements per 128-byte row (MN-major)
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+                for (int k = 0; k < k_iters; ++k) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrEmptyWait); ok = false; break; }
+                    uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    uint32_t sb = sa + A_STAGE_BYTES;
+                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    if (!p.a_mn_major) {
+                        tma_load_2d(sa, &tmap_a, full_bar(stage), k * bk, tm * BM);
+                    } else {
+                        // boxes of [bk K-rows][128 B of M]; BM*elem_bytes/128 boxes side by side
+                        int nbox = BM * p.elem_bytes / ROW_BYTES;
+                        for (int b = 0; b < nbox; ++b)
+                            tma_load_2d(sa + b * (A_STAGE_BYTES / nbox), &tmap_a, full_bar(stage), tm * BM + b * mn_chunk, k * bk);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_2d(sb, &tmap_b, full_bar(stage), k * bk, tn * BN);
+                    } else {
+                        int nbox = BN * p.elem_bytes / ROW_BYTES;
+                        for (int b = 0; b < nbox; ++b)
+                            tma_load_2d(sb + b * (B_STAGE_BYTES / nbox), &tmap_b, full_bar(stage), tn * BN + b * mn_chunk, k * bk);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(p.a_fmt, p.b_fmt, p.a_mn_major, p.b_mn_major, BM, BN);
+            // K-major: 8-row groups are 1024 B apart, a K step of one MMA is 32 B inside the row.
+            // MN-major: a K step of one MMA is (mma_k rows * 128 B); next 128 B chunk along M/N
+            //           is one whole box (bk rows * 128 B) further on.
+            const int mma_k = 32 / p.elem_bytes;
+            const uint32_t box_bytes = static_cast<uint32_t>(bk) * ROW_BYTES;
+            const uint32_t a_step = p.a_mn_major ? mma_k * ROW_BYTES : 32;
+            const uint32_t b_step = p.b_mn_major ? mma_k * ROW_BYTES : 32;
+            const uint32_t a_lbo = p.a_mn_major ? box_bytes : 16;
+            const uint32_t b_lbo = p.b_mn_major ? box_bytes : 16;
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrTmemEmpty); ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int k = 0; k < k_iters; ++k) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicOr(p.status, kErrFullWait); ok = false; break; }
+                    tc_fence_after_sync();
+                    uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint64_t ad = make_smem_desc(sa + j * a_step, a_lbo, 1024);
+                        uint64_t bd = make_smem_desc(sb + j * b_step, b_lbo, 1024);
+                        uint32_t accum = (k > 0 || j > 0) ? 1u : 0u;
+                        if (p.elem_bytes == 2) mma_f16(d_tmem, ad, bd, idesc, accum);
+                        else                   mma_f8(d_tmem, ad, bd, idesc, accum);
+                    }
+                    mma_commit(empty_bar(stage));          // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                mma_commit(tfull_bar(acc));                // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps)
+        const int q = warp & 3;                            // TMEM lane quarter this warp may access
+        float alpha = p.alpha;
+        if (p.scale_a) alpha *= *p.scale_a;
+        if (p.scale_b) alpha *= *p.scale_b;
+        float tmax = 0.f;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { if (lane == 0) atomicOr(p.status, kErrTmemFull); ok = false; break; }
+            tc_fence_after_sync();
+            const int row = tm * BM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                const int col0 = tn * BN + c;
+                if (col0 >= p.N) break;                    // uniform across the warp
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + c, r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        int cj = col0 + j;
+                        if (cj < p.N) {
+                            v[j] += p.bias_dtype == 0 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[cj])
+                                                      : static_cast<const float*>(p.bias)[cj];
+                        }
+                    }
+                }
+                if (row_ok) {
+                    const bool full = (col0 + 32 <= p.N);
+                    if (p.c_dtype == 0) {
+                        __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+                        if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                uint4 o;
+                                if (p.accumulate) {
+                                    uint4 old = *reinterpret_cast<const uint4*>(cp + g * 8);
+                                    const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        float2 f = __bfloat1622float2(oh[j]);
+                                        v[g * 8 + 2 * j] += f.x; v[g * 8 + 2 * j + 1] += f.y;
+                                    }
+                                }
+                                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+                                *reinterpret_cast<uint4*>(cp + g * 8) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.N) {
+                                    if (p.accumulate) v[j] += __bfloat162float(cp[j]);
+                                    cp[j] = __float2bfloat16_rn(v[j]);
+                                }
+                            }
+                        }
+                    } else {
+                        float* cp = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+                        if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                                if (p.accumulate) {
+                                    float4 old = *reinterpret_cast<const float4*>(cp + g * 4);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                    v[g * 4] = o.x; v[g * 4 + 1] = o.y; v[g * 4 + 2] = o.z; v[g * 4 + 3] = o.w;
+                                }
+                                *reinterpret_cast<float4*>(cp + g * 4) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.N) {
+                                    if (p.accumulate) v[j] += cp[j];
+                                    cp[j] = v[j];
+                                }
+                            }
+                        }
+                    }
+                    if (p.absmax_out) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) tmax = fmaxf(tmax, fabsf(v[j]));
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(tempty_bar(acc));                  // 128 arrivals release the accumulator
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (p.absmax_out) {
+            tmax = warp_reduce_max(tmax);
+            if (lane == 0 && tmax > 0.f) atomic_max_float(p.absmax_out, tmax);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side: tensor-map encoding through the driver entry point (no link-time libcuda dependency).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || !ptr)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+}  // namespace
+
+// Encodes a 2-D tiled map over a row-major [rows, cols] matrix with leading dimension ld (elements).
+// The box is [box_rows][128 bytes] with the 128-byte swizzle.  Returns 0 on success.
+int llmq_encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, long long rows, long long cols,
+                        long long ld, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -1;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias,
+                         int M, int N, int K,
+                         int ab_dtype,            // 0 bf16, 1 e4m3, 2 e5m2 (A), B shares the width
+                         int b_dtype,
+                         int a_mn_major, int b_mn_major,
+                         long long lda, long long ldb, long long ldc,
+                         int c_dtype, int bias_dtype, int accumulate,
+                         const float* scale_a, const float* scale_b, float alpha,
+                         float* absmax_out, unsigned int* status, int num_sms, cudaStream_t stream) {
+    const int eb = ab_dtype == 0 ? 2 : 1;
+    if ((b_dtype == 0 ? 2 : 1) != eb) return -2;
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    // TMA needs 16-byte aligned bases and row pitches
+    if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) return -3;
+    if ((lda * eb) % 16 || (ldb * eb) % 16) return -4;
+
+    CUtensorMap ta, tb;
+    const int bk = 128 / eb;
+    int rc;
+    if (!a_mn_major) rc = llmq_encode_tmap_2d(&ta, A, eb, M, K, lda, BM);
+    else             rc = llmq_encode_tmap_2d(&ta, A, eb, K, M, lda, bk);
+    if (rc) return rc;
+    if (!b_mn_major) rc = llmq_encode_tmap_2d(&tb, B, eb, N, K, ldb, BN);
+    else             rc = llmq_encode_tmap_2d(&tb, B, eb, K, N, ldb, bk);
+    if (rc) return rc;
+
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K; p.elem_bytes = eb;
+    p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+    p.a_fmt = ab_dtype == 0 ? 1 : (ab_dtype == 1 ? 0 : 1);
+    p.b_fmt = b_dtype == 0 ? 1 : (b_dtype == 1 ? 0 : 1);
+    p.C = C; p.ldc = ldc; p.c_dtype = c_dtype; p.accumulate = accumulate;
+    p.bias = bias; p.bias_dtype = bias_dtype;
+    p.scale_a = scale_a; p.scale_b = scale_b; p.alpha = alpha;
+    p.absmax_out = absmax_out; p.status = status;
+
+    static bool attr_set[64] = {};          // the attribute is per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        attr_set[dev & 63] = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int grid = tiles < num_sms ? tiles : num_sms;
+    gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    return static_cast<int>(cudaGetLastError());
+}
