@@ -1,0 +1,202 @@
+// SwiGLU forward / backward and rotary position embedding kernels.
+// Behavioural counterparts of src/kernels/swiglu.cu:21-405 and src/kernels/rope.cu:41-153 of the reference.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU.  Input rows are [up(D) | gate(D)];  out = up * gate * sigmoid(gate).
+// With q_out the kernel emits e4m3 directly using an abs-max that is already known (recompute path).
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(T* __restrict__ out, e4m3* __restrict__ q_out, const T* __restrict__ inp, long long rows, int D,
+                  float* __restrict__ absmax_out, const float* __restrict__ known_absmax, float* __restrict__ q_scale_out) {
+    __shared__ float scratch[32];
+    using V = Vec16<T>;
+    const int vec_per_row = D / V::N;
+    const long long total = rows * vec_per_row;
+    float qmul = 0.f;
+    if (q_out) {
+        float am = fmaxf(*known_absmax, 1e-10f);
+        qmul = 448.f / am;
+        if (blockIdx.x == 0 && threadIdx.x == 0 && q_scale_out) *q_scale_out = am / 448.f;
+    }
+    float tmax = 0.f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        long long r = i / vec_per_row;
+        int c = static_cast<int>(i - r * vec_per_row) * V::N;
+        const T* up = inp + r * 2 * D + c;
+        V vu = V::load_stream(up), vg = V::load_stream(up + D), vo;
+        alignas(8) e4m3 q[V::N];
+#pragma unroll
+        for (int k = 0; k < V::N; ++k) {
+            float u = to_float(vu.v[k]), g = to_float(vg.v[k]);
+            vo.v[k] = from_float<T>(u * g * fast_sigmoid(g));
+            float f = to_float(vo.v[k]);
+            tmax = fmaxf(tmax, fabsf(f));
+            if (q_out) q[k] = e4m3(f * qmul);
+        }
+        if (out) vo.store(out + r * D + c);
+        if (q_out) {
+            if constexpr (V::N == 8) *reinterpret_cast<uint2*>(q_out + r * D + c) = *reinterpret_cast<uint2*>(q);
+            else *reinterpret_cast<uint32_t*>(q_out + r * D + c) = *reinterpret_cast<uint32_t*>(q);
+        }
+    }
+    block_absmax_commit(absmax_out, tmax, scratch);
+}
+
+// Backward: dinp = [d_up | d_gate]; dinp may alias inp (in-place over the saved up-projection).
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(T* dinp, const T* __restrict__ dout, const T* inp, long long rows, int D, float* __restrict__ absmax_out) {
+    __shared__ float scratch[32];
+    using V = Vec16<T>;
+    const int vec_per_row = D / V::N;
+    const long long total = rows * vec_per_row;
+    float tmax = 0.f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        long long r = i / vec_per_row;
+        int c = static_cast<int>(i - r * vec_per_row) * V::N;
+        const T* up = inp + r * 2 * D + c;
+        V vu = V::load(up), vg = V::load(up + D), vd = V::load_stream(dout + r * D + c), du, dg;
+#pragma unroll
+        for (int k = 0; k < V::N; ++k) {
+            float u = to_float(vu.v[k]), g = to_float(vg.v[k]), d = to_float(vd.v[k]);
+            float s = fast_sigmoid(g);
+            du.v[k] = from_float<T>(d * g * s);
+            dg.v[k] = from_float<T>(d * u * s * (1.f + g * (1.f - s)));
+            tmax = fmaxf(tmax, fmaxf(fabsf(to_float(du.v[k])), fabsf(to_float(dg.v[k]))));
+        }
+        du.store(dinp + r * 2 * D + c);
+        dg.store(dinp + r * 2 * D + D + c);
+    }
+    block_absmax_commit(absmax_out, tmax, scratch);
+}
+
+// ------------------------------------------------------------------------------------------------
+// RoPE on the packed (B, T, Hq + 2*Hkv, HS) tensor; query and key heads are rotated with the half-split
+// pairing (d, d + HS/2), value heads are copied (or left alone when in place).  freqs is (T, HS/2, 2)
+// fp32 {cos, sin}.  Backward is the conjugate rotation.
+template <typename T, bool Backward>
+__global__ void __launch_bounds__(256)
+rope_kernel(T* out, const T* inp, const float* __restrict__ freqs, int B, int Tlen, int Hq, int Hkv, int HS,
+            float* __restrict__ absmax_out) {
+    __shared__ float scratch[32];
+    using V = Vec16<T>;
+    const int half = HS / 2;
+    const int vec_per_half = half / V::N;
+    const int H = Hq + 2 * Hkv;
+    const long long total = static_cast<long long>(B) * Tlen * H * vec_per_half;
+    float tmax = 0.f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        int v = static_cast<int>(i % vec_per_half);
+        long long rest = i / vec_per_half;
+        int h = static_cast<int>(rest % H);
+        long long bt = rest / H;
+        int t = static_cast<int>(bt % Tlen);
+        long long base = (bt * H + h) * HS + v * V::N;
+        V x1 = V::load(inp + base), x2 = V::load(inp + base + half);
+        if (h < Hq + Hkv) {
+            const float* f = freqs + (static_cast<long long>(t) * half + v * V::N) * 2;
+#pragma unroll
+            for (int k = 0; k < V::N; ++k) {
+                float c = f[2 * k], s = f[2 * k + 1];
+                if (Backward) s = -s;
+                float a = to_float(x1.v[k]), b = to_float(x2.v[k]);
+                x1.v[k] = from_float<T>(a * c - b * s);
+                x2.v[k] = from_float<T>(b * c + a * s);
+            }
+        } else if (out == inp && !absmax_out) {
+            continue;
+        }
+        if (absmax_out) {
+#pragma unroll
+            for (int k = 0; k < V::N; ++k) tmax = fmaxf(tmax, fmaxf(fabsf(to_float(x1.v[k])), fabsf(to_float(x2.v[k]))));
+        }
+        if (!(out == inp && h >= Hq + Hkv)) {
+            x1.store(out + base);
+            x2.store(out + base + half);
+        }
+    }
+    block_absmax_commit(absmax_out, tmax, scratch);
+}
+
+__global__ void rope_table_kernel(float* freqs, int Tlen, int half, float theta) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= Tlen * half) return;
+    int t = i / half, d = i % half;
+    // inverse frequency in double precision so long contexts keep their phase
+    double inv = pow(static_cast<double>(theta), -static_cast<double>(2 * d) / (2.0 * half));
+    double ang = t * inv;
+    freqs[2 * i] = static_cast<float>(cos(ang));
+    freqs[2 * i + 1] = static_cast<float>(sin(ang));
+}
+
+int grid_for(long long work_items, int threads, int num_sms) {
+    long long blocks = ceil_div_ll(work_items, threads);
+    long long cap = static_cast<long long>(num_sms) * 8;
+    return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace
+
+extern "C" int llmq_swiglu_forward(void* out, void* q_out, const void* inp, long long rows, int D, int dtype, float* absmax,
+                                   const float* known_absmax, float* q_scale, int num_sms, cudaStream_t s) {
+    if (rows <= 0) return 0;
+    if (dtype == 0) {
+        if (D % 8) return -1;
+        swiglu_fwd_kernel<bf16><<<grid_for(rows * (D / 8), 256, num_sms), 256, 0, s>>>(
+            static_cast<bf16*>(out), static_cast<e4m3*>(q_out), static_cast<const bf16*>(inp), rows, D, absmax, known_absmax, q_scale);
+    } else if (dtype == 3) {
+        if (D % 4) return -1;
+        swiglu_fwd_kernel<float><<<grid_for(rows * (D / 4), 256, num_sms), 256, 0, s>>>(
+            static_cast<float*>(out), static_cast<e4m3*>(q_out), static_cast<const float*>(inp), rows, D, absmax, known_absmax, q_scale);
+    } else return -10;
+    return LLMQ_LAUNCH_CHECK();
+}
+
+extern "C" int llmq_swiglu_backward(void* dinp, const void* dout, const void* inp, long long rows, int D, int dtype,
+                                    float* absmax, int num_sms, cudaStream_t s) {
+    if (rows <= 0) return 0;
+    if (dtype == 0) {
+        if (D % 8) return -1;
+        swiglu_bwd_kernel<bf16><<<grid_for(rows * (D / 8), 256, num_sms), 256, 0, s>>>(
+            static_cast<bf16*>(dinp), static_cast<const bf16*>(dout), static_cast<const bf16*>(inp), rows, D, absmax);
+    } else if (dtype == 3) {
+        if (D % 4) return -1;
+        swiglu_bwd_kernel<float><<<grid_for(rows * (D / 4), 256, num_sms), 256, 0, s>>>(
+            static_cast<float*>(dinp), static_cast<const float*>(dout), static_cast<const float*>(inp), rows, D, absmax);
+    } else return -10;
+    return LLMQ_LAUNCH_CHECK();
+}
+
+extern "C" int llmq_rope(void* out, const void* inp, const float* freqs, int B, int T, int Hq, int Hkv, int HS, int dtype,
+                         int backward, float* absmax, int num_sms, cudaStream_t s) {
+    if (B <= 0 || T <= 0) return 0;
+    const int H = Hq + 2 * Hkv;
+    if (dtype == 0) {
+        if ((HS / 2) % 8) return -1;
+        long long work = static_cast<long long>(B) * T * H * (HS / 2 / 8);
+        int g = grid_for(work, 256, num_sms);
+        if (backward) rope_kernel<bf16, true><<<g, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
+        else rope_kernel<bf16, false><<<g, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
+    } else if (dtype == 3) {
+        if ((HS / 2) % 4) return -1;
+        long long work = static_cast<long long>(B) * T * H * (HS / 2 / 4);
+        int g = grid_for(work, 256, num_sms);
+        if (backward) rope_kernel<float, true><<<g, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
+        else rope_kernel<float, false><<<g, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
+    } else return -10;
+    return LLMQ_LAUNCH_CHECK();
+}
+
+extern "C" int llmq_rope_table(float* freqs, int T, int HS, float theta, cudaStream_t s) {
+    int n = T * (HS / 2);
+    if (n <= 0) return 0;
+    rope_table_kernel<<<ceil_div_i(n, 256), 256, 0, s>>>(freqs, T, HS / 2, theta);
+    return LLMQ_LAUNCH_CHECK();
+}

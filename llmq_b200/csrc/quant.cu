@@ -1,0 +1,212 @@
+// abs-max reduction, per-tensor fp8 quantisation, transposes, dtype conversion, fill and normal init.
+// Behavioural counterparts of src/kernels/{quant,transpose,convert,fill,random}.cu of the reference.
+// Recipe: q = sat_fp8(x * QMAX / max(absmax, 1e-10)), dequant factor absmax / QMAX is written next to it.
+// QMAX is 448 for e4m3 and 57344 for e5m2 (the reference uses 448 for both, which wastes the e5m2 range).
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+int grid_for(long long work_items, int threads, int num_sms) {
+    long long blocks = ceil_div_ll(work_items, threads);
+    long long cap = static_cast<long long>(num_sms) * 8;
+    return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) absmax_kernel(float* __restrict__ out, const T* __restrict__ x, long long n) {
+    __shared__ float scratch[32];
+    using V = Vec16<T>;
+    float tmax = 0.f;
+    const long long nvec = n / V::N;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        V v = V::load(x + i * V::N);
+#pragma unroll
+        for (int k = 0; k < V::N; ++k) tmax = fmaxf(tmax, fabsf(to_float(v.v[k])));
+    }
+    if (blockIdx.x == 0) {
+        for (long long i = nvec * V::N + threadIdx.x; i < n; i += blockDim.x) tmax = fmaxf(tmax, fabsf(to_float(x[i])));
+    }
+    block_absmax_commit(out, tmax, scratch);
+}
+
+template <typename Q> struct QMax;
+template <> struct QMax<e4m3> { static constexpr float value = 448.f; };
+template <> struct QMax<e5m2> { static constexpr float value = 57344.f; };
+template <> struct QMax<bf16> { static constexpr float value = 1.f; };
+
+template <typename T, typename Q>
+__global__ void __launch_bounds__(512)
+quantize_kernel(Q* __restrict__ out, float* __restrict__ scale_out, const T* __restrict__ x, const float* __restrict__ absmax, long long n) {
+    using V = Vec16<T>;
+    float mul = 1.f;
+    if constexpr (sizeof(Q) == 1) {
+        float am = fmaxf(*absmax, 1e-10f);
+        mul = QMax<Q>::value / am;
+        if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = am / QMax<Q>::value;
+    } else {
+        if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = 1.f;
+    }
+    const long long nvec = n / V::N;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        V v = V::load_stream(x + i * V::N);
+        alignas(16) Q q[V::N];
+#pragma unroll
+        for (int k = 0; k < V::N; ++k) q[k] = from_float<Q>(to_float(v.v[k]) * mul);
+        constexpr int bytes = V::N * sizeof(Q);
+        if constexpr (bytes == 16) *reinterpret_cast<uint4*>(out + i * V::N) = *reinterpret_cast<uint4*>(q);
+        else if constexpr (bytes == 8) *reinterpret_cast<uint2*>(out + i * V::N) = *reinterpret_cast<uint2*>(q);
+        else *reinterpret_cast<uint32_t*>(out + i * V::N) = *reinterpret_cast<uint32_t*>(q);
+    }
+    if (blockIdx.x == 0) {
+        for (long long i = nvec * V::N + threadIdx.x; i < n; i += blockDim.x) out[i] = from_float<Q>(to_float(x[i]) * mul);
+    }
+}
+
+// out[c][r] = f(in[r][c]) through a padded shared-memory tile; optionally quantises on the way.
+template <typename T, typename Q, bool Quant>
+__global__ void __launch_bounds__(256)
+transpose_kernel(Q* __restrict__ out, float* __restrict__ scale_out, const T* __restrict__ in, const float* __restrict__ absmax,
+                 int rows, int cols) {
+    __shared__ float tile[32][33];
+    float mul = 1.f;
+    if constexpr (Quant) {
+        float am = fmaxf(*absmax, 1e-10f);
+        mul = QMax<Q>::value / am;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0 && scale_out) *scale_out = am / QMax<Q>::value;
+    }
+    int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        int r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[j][threadIdx.x] = to_float(in[static_cast<long long>(r) * cols + c]);
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        int c = c0 + j, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) out[static_cast<long long>(c) * rows + r] = from_float<Q>(tile[threadIdx.x][j] * mul);
+    }
+}
+
+template <typename S, typename D>
+__global__ void __launch_bounds__(512) convert_kernel(D* __restrict__ out, const S* __restrict__ in, long long n) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = from_float<D>(to_float(in[i]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) fill_kernel(T* __restrict__ out, float value, long long n) {
+    T v = from_float<T>(value);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[i] = v;
+}
+
+// N(mean, std) from a counter-based generator: element i of stream (seed, subsequence) gets the same value
+// whatever the launch geometry or the sharding of the tensor (offset = index of out[0] in the full tensor).
+template <typename T>
+__global__ void __launch_bounds__(256)
+normal_kernel(T* __restrict__ out, long long n, float mean, float std, unsigned long long seed, unsigned long long subsequence,
+              long long offset) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        unsigned long long ctr = static_cast<unsigned long long>(i + offset);
+        uint32_t s0 = static_cast<uint32_t>(seed) ^ hash_u32(static_cast<uint32_t>(subsequence) * 0x9e3779b9u + static_cast<uint32_t>(seed >> 32));
+        uint32_t a = rng_u32(ctr * 2ull, s0), b = rng_u32(ctr * 2ull + 1ull, s0 ^ static_cast<uint32_t>(subsequence >> 32));
+        float u1 = (a >> 8) * (1.0f / 16777216.0f) + (0.5f / 16777216.0f);
+        float u2 = (b >> 8) * (1.0f / 16777216.0f);
+        float z = sqrtf(-2.f * logf(u1)) * cospif(2.f * u2);
+        out[i] = from_float<T>(mean + std * z);
+    }
+}
+
+}  // namespace
+
+extern "C" int llmq_abs_max(float* out, const void* x, long long n, int dtype, int num_sms, cudaStream_t s) {
+    if (n <= 0) return 0;
+    if (dtype == 0) absmax_kernel<bf16><<<grid_for(n / 8 + 1, 512, num_sms), 512, 0, s>>>(out, static_cast<const bf16*>(x), n);
+    else if (dtype == 3) absmax_kernel<float><<<grid_for(n / 4 + 1, 512, num_sms), 512, 0, s>>>(out, static_cast<const float*>(x), n);
+    else return -10;
+    return LLMQ_LAUNCH_CHECK();
+}
+
+extern "C" int llmq_quantize(void* out, float* scale_out, const void* x, const float* absmax, long long n, int in_dtype,
+                             int out_dtype, int num_sms, cudaStream_t s) {
+    if (n <= 0) return 0;
+#define Q_CASE(T, TC, Q, QC, VN)                                                                                   \
+    if (in_dtype == TC && out_dtype == QC) {                                                                       \
+        quantize_kernel<T, Q><<<grid_for(n / VN + 1, 512, num_sms), 512, 0, s>>>(static_cast<Q*>(out), scale_out,  \
+                                                                                 static_cast<const T*>(x), absmax, n); \
+        return LLMQ_LAUNCH_CHECK();                                                                                \
+    }
+    Q_CASE(bf16, 0, e4m3, 1, 8)
+    Q_CASE(bf16, 0, e5m2, 2, 8)
+    Q_CASE(bf16, 0, bf16, 0, 8)
+    Q_CASE(float, 3, e4m3, 1, 4)
+    Q_CASE(float, 3, e5m2, 2, 4)
+    Q_CASE(float, 3, bf16, 0, 4)
+#undef Q_CASE
+    return -10;
+}
+
+extern "C" int llmq_transpose(void* out, float* scale_out, const void* in, const float* absmax, int rows, int cols,
+                              int in_dtype, int out_dtype, cudaStream_t s) {
+    if (rows <= 0 || cols <= 0) return 0;
+    dim3 grid(ceil_div_i(cols, 32), ceil_div_i(rows, 32)), block(32, 8);
+#define T_CASE(T, TC, Q, QC, QUANT)                                                                                \
+    if (in_dtype == TC && out_dtype == QC && (absmax != nullptr) == QUANT) {                                       \
+        transpose_kernel<T, Q, QUANT><<<grid, block, 0, s>>>(static_cast<Q*>(out), scale_out, static_cast<const T*>(in), absmax, rows, cols); \
+        return LLMQ_LAUNCH_CHECK();                                                                                \
+    }
+    T_CASE(bf16, 0, bf16, 0, false)
+    T_CASE(float, 3, float, 3, false)
+    T_CASE(e4m3, 1, e4m3, 1, false)
+    T_CASE(e5m2, 2, e5m2, 2, false)
+    T_CASE(bf16, 0, e4m3, 1, true)
+    T_CASE(bf16, 0, e5m2, 2, true)
+    T_CASE(float, 3, e4m3, 1, true)
+#undef T_CASE
+    return -10;
+}
+
+extern "C" int llmq_convert(void* out, const void* in, long long n, int in_dtype, int out_dtype, int num_sms, cudaStream_t s) {
+    if (n <= 0) return 0;
+    int g = grid_for(n, 512, num_sms);
+#define C_CASE(S, SC, D, DC)                                                                        \
+    if (in_dtype == SC && out_dtype == DC) {                                                        \
+        convert_kernel<S, D><<<g, 512, 0, s>>>(static_cast<D*>(out), static_cast<const S*>(in), n); \
+        return LLMQ_LAUNCH_CHECK();                                                                 \
+    }
+    C_CASE(float, 3, bf16, 0)
+    C_CASE(bf16, 0, float, 3)
+    C_CASE(__half, 4, bf16, 0)
+    C_CASE(__half, 4, float, 3)
+    C_CASE(float, 3, __half, 4)
+    C_CASE(bf16, 0, __half, 4)
+    C_CASE(e4m3, 1, bf16, 0)
+    C_CASE(e4m3, 1, float, 3)
+    C_CASE(e5m2, 2, bf16, 0)
+#undef C_CASE
+    return -10;
+}
+
+extern "C" int llmq_fill(void* out, float value, long long n, int dtype, int num_sms, cudaStream_t s) {
+    if (n <= 0) return 0;
+    int g = grid_for(n, 512, num_sms);
+    if (dtype == 0) fill_kernel<bf16><<<g, 512, 0, s>>>(static_cast<bf16*>(out), value, n);
+    else if (dtype == 3) fill_kernel<float><<<g, 512, 0, s>>>(static_cast<float*>(out), value, n);
+    else return -10;
+    return LLMQ_LAUNCH_CHECK();
+}
+
+extern "C" int llmq_fill_normal(void* out, long long n, float mean, float std, unsigned long long seed,
+                                unsigned long long subsequence, long long offset, int dtype, int num_sms, cudaStream_t s) {
+    if (n <= 0) return 0;
+    int g = grid_for(n, 256, num_sms);
+    if (dtype == 0) normal_kernel<bf16><<<g, 256, 0, s>>>(static_cast<bf16*>(out), n, mean, std, seed, subsequence, offset);
+    else if (dtype == 3) normal_kernel<float><<<g, 256, 0, s>>>(static_cast<float*>(out), n, mean, std, seed, subsequence, offset);
+    else return -10;
+    return LLMQ_LAUNCH_CHECK();
+}

@@ -1,0 +1,614 @@
+"""Tensor-level entry points of every kernel.
+
+Each function works on pre-allocated ``torch`` tensors (no allocation on the hot path) and launches
+on the current CUDA stream.  CUDA tensors always go to the hand-written sm_100a kernels of
+``libllmq_b200_kernels.so``; a missing library is an error, never a silent fallback.  CPU tensors take
+a plain PyTorch implementation of the same mathematics, which is what the CPU test-suite, the gloo
+multi-rank tests and the numerics oracles run on.
+
+The set of operations mirrors the kernel API of the reference (src/kernels/kernels.h:25-295).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import lib as L
+
+F8 = torch.float8_e4m3fn
+F8_E5 = torch.float8_e5m2
+_FP8_MAX = {F8: 448.0, F8_E5: 57344.0}
+
+_state = {}
+
+
+def _dev_state(device: torch.device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _state.get(idx)
+    if st is None:
+        with torch.cuda.device(idx):
+            props = torch.cuda.get_device_properties(idx)
+            st = {
+                "sms": props.multi_processor_count,
+                "status": torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}"),
+            }
+        _state[idx] = st
+    return st
+
+
+def num_sms(device) -> int:
+    return _dev_state(device)["sms"]
+
+
+def status_word(device) -> torch.Tensor:
+    """Device word into which kernels OR an error code when one of their bounded waits runs out."""
+    return _dev_state(device)["status"]
+
+
+def check_status(device) -> None:
+    """Raises if any kernel reported a timed-out wait since the last check (synchronises)."""
+    st = _dev_state(device)["status"]
+    v = int(st.item())
+    if v != 0:
+        st.zero_()
+        raise L.KernelError(f"a device-side wait timed out (status 0x{v:x}); the step result is invalid")
+
+
+def _ll(v):
+    return ctypes.c_longlong(int(v))
+
+
+def _f(v):
+    return ctypes.c_float(float(v))
+
+
+def _is_f8(dt):
+    return dt in (F8, F8_E5)
+
+
+# =====================================================================================================
+# GEMM
+def gemm(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         bias: Optional[torch.Tensor] = None, accumulate: bool = False, scale_a: Optional[torch.Tensor] = None,
+         scale_b: Optional[torch.Tensor] = None, alpha: float = 1.0, absmax: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] (+)= alpha * scale_a * scale_b * A @ B^T + bias.
+
+    ``a`` holds the logical [M,K] operand either as [M,K] (K-major) or, with ``a_mn``, as [K,M];
+    likewise ``b`` holds logical [N,K] as [N,K] or, with ``b_mn``, as [K,N].  2-D, last dim contiguous.
+    """
+    M, N = out.shape
+    K = a.shape[0] if a_mn else a.shape[1]
+    assert (a.shape[1] if a_mn else a.shape[0]) == M, (a.shape, out.shape, a_mn)
+    assert (b.shape == (K, N)) if b_mn else (b.shape == (N, K)), (b.shape, (N, K), b_mn)
+    if out.is_cuda:
+        st = _dev_state(out.device)
+        assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+        rc = L.kernels().llmq_gemm(
+            L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(bias), M, N, K, L.dtype_code(a.dtype), L.dtype_code(b.dtype),
+            int(a_mn), int(b_mn), _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
+            0 if out.dtype == torch.bfloat16 else 1, 0 if (bias is None or bias.dtype == torch.bfloat16) else 1,
+            int(accumulate), L.ptr(scale_a), L.ptr(scale_b), _f(alpha), L.ptr(absmax), L.ptr(st["status"]), st["sms"],
+            L.stream_ptr())
+        L.check(rc, "gemm")
+        return
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    r = af @ bf
+    s = alpha
+    if scale_a is not None:
+        s = s * scale_a.float()
+    if scale_b is not None:
+        s = s * scale_b.float()
+    r = r * s
+    if bias is not None:
+        r = r + bias.float()
+    if accumulate:
+        r = r + out.float()
+    out.copy_(r.to(out.dtype))
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, out.float().abs().max().reshape_as(absmax)))
+
+
+# =====================================================================================================
+# RMSNorm
+def rmsnorm_forward(y: Optional[torch.Tensor], rstd: Optional[torch.Tensor], inp: torch.Tensor, weight: torch.Tensor, eps: float,
+                    *, residual_out: Optional[torch.Tensor] = None, inp2: Optional[torch.Tensor] = None,
+                    absmax: Optional[torch.Tensor] = None, q_out: Optional[torch.Tensor] = None,
+                    known_absmax: Optional[torch.Tensor] = None, q_scale: Optional[torch.Tensor] = None) -> None:
+    """(residual_out = inp + inp2;) y = T(x * rstd) * weight with x the (summed) input.
+
+    ``q_out`` (e4m3) together with ``known_absmax`` emits the quantised result directly.
+    """
+    C = inp.shape[-1]
+    rows = inp.numel() // C
+    if inp.is_cuda:
+        rc = L.kernels().llmq_rmsnorm_forward(
+            L.ptr(residual_out), L.ptr(y), L.ptr(q_out), L.ptr(rstd), L.ptr(inp), L.ptr(inp2), L.ptr(weight), _f(eps), rows, C,
+            L.dtype_code(inp.dtype), L.ptr(absmax), L.ptr(known_absmax), L.ptr(q_scale), L.stream_ptr())
+        L.check(rc, "rmsnorm_forward")
+        return
+    x = inp.float()
+    if inp2 is not None:
+        x = (x + inp2.float()).to(inp.dtype)
+        if residual_out is not None:
+            residual_out.copy_(x)
+        x = x.float()
+    rs = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    n = (x * rs).to(inp.dtype)
+    out = (n.float() * weight.float()).to(inp.dtype)
+    if rstd is not None:
+        rstd.copy_(rs.reshape(rstd.shape))
+    if y is not None:
+        y.copy_(out)
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, out.float().abs().max().reshape_as(absmax)))
+    if q_out is not None:
+        am = known_absmax.float().clamp_min(1e-10)
+        q_out.copy_((out.float() * (448.0 / am)).clamp(-448, 448).to(q_out.dtype))
+        if q_scale is not None:
+            q_scale.copy_((am / 448.0).reshape_as(q_scale))
+
+
+def rmsnorm_backward_scratch_elems(C: int, device) -> int:
+    blocks = 2 * num_sms(device) if torch.device(device).type == "cuda" else 1
+    return blocks * C
+
+
+def rmsnorm_backward(dinp: torch.Tensor, dweight: torch.Tensor, scratch: Optional[torch.Tensor], dout: torch.Tensor,
+                     inp: torch.Tensor, weight: torch.Tensor, rstd: torch.Tensor, *, absmax: Optional[torch.Tensor] = None,
+                     accumulate_dweight: bool = True) -> None:
+    """dinp += d(rmsnorm)/d(inp) * dout;  dweight (+)= sum_rows dout * xhat."""
+    C = inp.shape[-1]
+    rows = inp.numel() // C
+    if inp.is_cuda:
+        blocks = 2 * num_sms(inp.device)
+        assert scratch is not None and scratch.numel() >= blocks * C and scratch.dtype == torch.float32
+        rc = L.kernels().llmq_rmsnorm_backward(
+            L.ptr(dinp), L.ptr(dweight), L.ptr(scratch), L.ptr(dout), L.ptr(inp), L.ptr(weight), L.ptr(rstd), rows, C,
+            L.dtype_code(inp.dtype), L.ptr(absmax), int(accumulate_dweight), blocks, L.stream_ptr())
+        L.check(rc, "rmsnorm_backward")
+        return
+    x = inp.float().reshape(rows, C)
+    dy = dout.float().reshape(rows, C)
+    rs = rstd.float().reshape(rows, 1)
+    xh = x * rs
+    w = weight.float()
+    dot = (w * dy * xh).mean(-1, keepdim=True)
+    g = (w * dy - xh * dot) * rs
+    res = (dinp.float().reshape(rows, C) + g).to(dinp.dtype)
+    dinp.copy_(res.reshape(dinp.shape))
+    dw = (dy * xh).sum(0)
+    if accumulate_dweight:
+        dw = dw + dweight.float()
+    dweight.copy_(dw.to(dweight.dtype))
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, dinp.float().abs().max().reshape_as(absmax)))
+
+
+# =====================================================================================================
+# SwiGLU
+def swiglu_forward(out: Optional[torch.Tensor], inp: torch.Tensor, *, absmax: Optional[torch.Tensor] = None,
+                   q_out: Optional[torch.Tensor] = None, known_absmax: Optional[torch.Tensor] = None,
+                   q_scale: Optional[torch.Tensor] = None) -> None:
+    """inp rows are [up | gate]; out = up * gate * sigmoid(gate)."""
+    D = inp.shape[-1] // 2
+    rows = inp.numel() // (2 * D)
+    if inp.is_cuda:
+        rc = L.kernels().llmq_swiglu_forward(L.ptr(out), L.ptr(q_out), L.ptr(inp), _ll(rows), D, L.dtype_code(inp.dtype),
+                                             L.ptr(absmax), L.ptr(known_absmax), L.ptr(q_scale), num_sms(inp.device), L.stream_ptr())
+        L.check(rc, "swiglu_forward")
+        return
+    x = inp.float().reshape(rows, 2 * D)
+    up, gate = x[:, :D], x[:, D:]
+    r = (up * gate * torch.sigmoid(gate)).to(inp.dtype)
+    if out is not None:
+        out.copy_(r.reshape(out.shape))
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, r.float().abs().max().reshape_as(absmax)))
+    if q_out is not None:
+        am = known_absmax.float().clamp_min(1e-10)
+        q_out.copy_((r.float() * (448.0 / am)).clamp(-448, 448).to(q_out.dtype).reshape(q_out.shape))
+        if q_scale is not None:
+            q_scale.copy_((am / 448.0).reshape_as(q_scale))
+
+
+def swiglu_backward(dinp: torch.Tensor, dout: torch.Tensor, inp: torch.Tensor, *, absmax: Optional[torch.Tensor] = None) -> None:
+    """dinp = [d_up | d_gate]; may alias ``inp``."""
+    D = inp.shape[-1] // 2
+    rows = inp.numel() // (2 * D)
+    if inp.is_cuda:
+        rc = L.kernels().llmq_swiglu_backward(L.ptr(dinp), L.ptr(dout), L.ptr(inp), _ll(rows), D, L.dtype_code(inp.dtype),
+                                              L.ptr(absmax), num_sms(inp.device), L.stream_ptr())
+        L.check(rc, "swiglu_backward")
+        return
+    x = inp.float().reshape(rows, 2 * D)
+    up, gate = x[:, :D], x[:, D:]
+    d = dout.float().reshape(rows, D)
+    s = torch.sigmoid(gate)
+    du = d * gate * s
+    dg = d * up * s * (1 + gate * (1 - s))
+    r = torch.cat([du, dg], -1).to(dinp.dtype)
+    dinp.copy_(r.reshape(dinp.shape))
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, r.float().abs().max().reshape_as(absmax)))
+
+
+# =====================================================================================================
+# RoPE
+def rope_table(T: int, HS: int, theta: float, device) -> torch.Tensor:
+    """(T, HS/2, 2) fp32 table of {cos, sin}."""
+    device = torch.device(device)
+    if device.type == "cuda":
+        out = torch.empty(T, HS // 2, 2, dtype=torch.float32, device=device)
+        with torch.cuda.device(device):
+            L.check(L.kernels().llmq_rope_table(L.ptr(out), T, HS, _f(theta), L.stream_ptr()), "rope_table")
+        return out
+    d = torch.arange(HS // 2, dtype=torch.float64)
+    inv = theta ** (-2.0 * d / HS)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * inv[None, :]
+    return torch.stack([ang.cos(), ang.sin()], -1).float()
+
+
+def rope(out: torch.Tensor, inp: torch.Tensor, freqs: torch.Tensor, Hq: int, Hkv: int, *, backward: bool = False,
+         absmax: Optional[torch.Tensor] = None) -> None:
+    """Rotates the q and k heads of packed (B, T, Hq+2Hkv, HS); ``out`` may be ``inp``."""
+    B, T, H, HS = inp.shape
+    assert H == Hq + 2 * Hkv
+    if inp.is_cuda:
+        rc = L.kernels().llmq_rope(L.ptr(out), L.ptr(inp), L.ptr(freqs), B, T, Hq, Hkv, HS, L.dtype_code(inp.dtype), int(backward),
+                                   L.ptr(absmax), num_sms(inp.device), L.stream_ptr())
+        L.check(rc, "rope")
+        return
+    x = inp.float()
+    cos = freqs[:T, :, 0][None, :, None, :]
+    sin = freqs[:T, :, 1][None, :, None, :]
+    if backward:
+        sin = -sin
+    h = HS // 2
+    x1, x2 = x[..., :h], x[..., h:]
+    r1 = x1 * cos - x2 * sin
+    r2 = x2 * cos + x1 * sin
+    rot = torch.cat([r1, r2], -1)
+    res = x.clone()
+    res[:, :, :Hq + Hkv] = rot[:, :, :Hq + Hkv]
+    res = res.to(out.dtype)
+    out.copy_(res)
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, res.float().abs().max().reshape_as(absmax)))
+
+
+# =====================================================================================================
+# abs-max / quantisation / transposes / conversion / fill
+def abs_max(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out = max(out, max|x|)  (``out`` is normally zeroed first)."""
+    if x.is_cuda:
+        L.check(L.kernels().llmq_abs_max(L.ptr(out), L.ptr(x), _ll(x.numel()), L.dtype_code(x.dtype), num_sms(x.device),
+                                         L.stream_ptr()), "abs_max")
+        return
+    out.copy_(torch.maximum(out, x.float().abs().max().reshape_as(out)))
+
+
+def quantize(out: torch.Tensor, scale_out: Optional[torch.Tensor], x: torch.Tensor, absmax: Optional[torch.Tensor]) -> None:
+    """out = sat(x * QMAX / max(absmax, 1e-10)); scale_out = absmax / QMAX (1 when out is not an fp8 type)."""
+    if x.is_cuda:
+        L.check(L.kernels().llmq_quantize(L.ptr(out), L.ptr(scale_out), L.ptr(x), L.ptr(absmax), _ll(x.numel()), L.dtype_code(x.dtype),
+                                          L.dtype_code(out.dtype), num_sms(x.device), L.stream_ptr()), "quantize")
+        return
+    if _is_f8(out.dtype):
+        qm = _FP8_MAX[out.dtype]
+        am = absmax.float().clamp_min(1e-10)
+        out.copy_((x.float() * (qm / am)).clamp(-qm, qm).to(out.dtype).reshape(out.shape))
+        if scale_out is not None:
+            scale_out.copy_((am / qm).reshape_as(scale_out))
+    else:
+        out.copy_(x.to(out.dtype).reshape(out.shape))
+        if scale_out is not None:
+            scale_out.fill_(1.0)
+
+
+def transpose(out: torch.Tensor, x: torch.Tensor, *, absmax: Optional[torch.Tensor] = None,
+              scale_out: Optional[torch.Tensor] = None) -> None:
+    """out[c, r] = x[r, c]; with ``absmax`` the values are quantised to ``out.dtype`` on the way."""
+    rows, cols = x.shape
+    if x.is_cuda:
+        L.check(L.kernels().llmq_transpose(L.ptr(out), L.ptr(scale_out), L.ptr(x), L.ptr(absmax), rows, cols, L.dtype_code(x.dtype),
+                                           L.dtype_code(out.dtype), L.stream_ptr()), "transpose")
+        return
+    if absmax is not None:
+        tmp = torch.empty(rows, cols, dtype=out.dtype)
+        quantize(tmp, scale_out, x, absmax)
+        out.copy_(tmp.view(torch.uint8).t().contiguous().view(out.dtype) if _is_f8(out.dtype) else tmp.t())
+    else:
+        out.copy_(x.view(torch.uint8).t().contiguous().view(x.dtype) if _is_f8(x.dtype) else x.t())
+
+
+def convert(out: torch.Tensor, x: torch.Tensor) -> None:
+    if x.is_cuda:
+        L.check(L.kernels().llmq_convert(L.ptr(out), L.ptr(x), _ll(x.numel()), L.dtype_code(x.dtype), L.dtype_code(out.dtype),
+                                         num_sms(x.device), L.stream_ptr()), "convert")
+        return
+    out.copy_(x.to(out.dtype).reshape(out.shape))
+
+
+def fill(out: torch.Tensor, value: float) -> None:
+    if out.is_cuda and out.dtype in (torch.bfloat16, torch.float32):
+        L.check(L.kernels().llmq_fill(L.ptr(out), _f(value), _ll(out.numel()), L.dtype_code(out.dtype), num_sms(out.device),
+                                      L.stream_ptr()), "fill")
+        return
+    out.fill_(value)
+
+
+def fill_normal(out: torch.Tensor, mean: float, std: float, seed: int, subsequence: int = 0, offset: int = 0) -> None:
+    """Counter-based N(mean, std): element i gets the value of counter ``offset + i`` of stream (seed, subsequence)."""
+    if out.is_cuda:
+        L.check(L.kernels().llmq_fill_normal(L.ptr(out), _ll(out.numel()), _f(mean), _f(std), ctypes.c_ulonglong(seed),
+                                             ctypes.c_ulonglong(subsequence), _ll(offset), L.dtype_code(out.dtype),
+                                             num_sms(out.device), L.stream_ptr()), "fill_normal")
+        return
+    # CPU: independent generator per (seed, subsequence); offset skips values so shards agree with the full tensor
+    g = torch.Generator().manual_seed((seed * 1000003 + subsequence) % (2 ** 63))
+    full = torch.randn(offset + out.numel(), generator=g, dtype=torch.float32)
+    out.copy_((mean + std * full[offset:]).to(out.dtype).reshape(out.shape))
+
+
+# =====================================================================================================
+# Loss
+def fused_classifier(logits: torch.Tensor, losses: torch.Tensor, lse: Optional[torch.Tensor], targets: torch.Tensor, dloss: float,
+                     z_reg: float = 0.0, write_dlogits: bool = True) -> None:
+    """Cross-entropy over rows of ``logits`` (rows, V): losses += lse - logit[target]; logits <- gradient in place."""
+    rows, V = logits.shape
+    if logits.is_cuda:
+        L.check(L.kernels().llmq_fused_classifier(L.ptr(logits), L.ptr(losses), L.ptr(lse), L.ptr(targets), _f(dloss), _f(z_reg), rows, V,
+                                                  _ll(logits.stride(0)), L.dtype_code(logits.dtype), int(write_dlogits),
+                                                  L.stream_ptr()), "fused_classifier")
+        return
+    x = logits.float()
+    tg = targets.reshape(rows).long()
+    valid = tg != -100
+    l = torch.logsumexp(x, -1)
+    safe = tg.clamp_min(0)
+    picked = x.gather(1, safe[:, None])[:, 0]
+    losses.reshape(rows).add_(torch.where(valid, l - picked, torch.zeros_like(l)))
+    if lse is not None:
+        lse.reshape(rows).copy_(torch.where(valid, l, torch.zeros_like(l)))
+    if write_dlogits:
+        p = torch.softmax(x, -1)
+        g = p * (dloss + z_reg * l)[:, None]
+        g[torch.arange(rows), safe] -= dloss
+        g = torch.where(valid[:, None], g, torch.zeros_like(g))
+        logits.copy_(g.to(logits.dtype))
+
+
+def lse_stats(out: torch.Tensor, lse: torch.Tensor, accumulate: bool = False) -> None:
+    """out = {max, sum} of the per-token log-sum-exp values."""
+    if lse.is_cuda:
+        L.check(L.kernels().llmq_lse_stats(L.ptr(out), L.ptr(lse), _ll(lse.numel()), int(accumulate), L.stream_ptr()), "lse_stats")
+        return
+    m, s = lse.float().max(), lse.float().sum()
+    if accumulate:
+        out[0] = torch.maximum(out[0], m)
+        out[1] += s
+    else:
+        out[0], out[1] = m, s
+
+
+def grouped_loss_sum(out: torch.Tensor, losses: torch.Tensor, group: int = 512) -> None:
+    """out[g] = sum of losses(B, T) over the batch and positions [g*group, (g+1)*group)."""
+    B, T = losses.shape
+    if losses.is_cuda:
+        L.check(L.kernels().llmq_grouped_loss_sum(L.ptr(out), L.ptr(losses), B, T, group, L.stream_ptr()), "grouped_loss_sum")
+        return
+    for g in range((T + group - 1) // group):
+        out[g] = losses[:, g * group:(g + 1) * group].float().sum()
+
+
+# =====================================================================================================
+# Optimiser
+def _sr_cpu(x: torch.Tensor, dtype: torch.dtype, gen: torch.Generator) -> torch.Tensor:
+    if dtype == torch.float32:
+        return x
+    bits = x.contiguous().view(torch.int32)
+    rnd = torch.randint(0, 1 << 16, bits.shape, generator=gen, dtype=torch.int32)
+    return ((bits + rnd) & -65536).view(torch.float32).to(dtype)
+
+
+def adamw(param: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *, lr: float, beta1: float, beta2: float,
+          step: int, eps: float, weight_decay: float, grad_scale: Optional[torch.Tensor] = None,
+          absmax: Optional[torch.Tensor] = None, m_scales: Optional[torch.Tensor] = None, seed: int = 0,
+          elem_offset: int = 0, stochastic: bool = True) -> None:
+    """In-place AdamW on flat shards; fp32 math, stochastic rounding when storing to bf16 / e4m3."""
+    n = param.numel()
+    if param.is_cuda:
+        L.check(L.kernels().llmq_adamw(L.ptr(param), L.ptr(grad), L.ptr(m), L.ptr(v), L.ptr(m_scales), _ll(n), _f(lr), _f(beta1), _f(beta2),
+                                       int(step), _f(eps), _f(weight_decay), L.ptr(grad_scale), L.ptr(absmax),
+                                       ctypes.c_uint(seed & 0xFFFFFFFF), _ll(elem_offset), L.dtype_code(param.dtype),
+                                       L.dtype_code(grad.dtype), L.dtype_code(m.dtype), L.dtype_code(v.dtype), num_sms(param.device),
+                                       L.stream_ptr()), "adamw")
+        return
+    gen = torch.Generator().manual_seed((seed * 2654435761 + elem_offset) % (2 ** 63))
+    g = grad.float().reshape(-1)
+    if grad_scale is not None:
+        g = g * grad_scale.float()
+    p = param.float().reshape(-1)
+    mf = m.float().reshape(-1)
+    if _is_f8(m.dtype):
+        mf = mf * m_scales.float().repeat_interleave(128)[:n]
+    vf = v.float().reshape(-1)
+    mf = beta1 * mf + (1 - beta1) * g
+    vf = beta2 * vf + (1 - beta2) * g * g
+    mh = mf / (1 - beta1 ** step)
+    vh = vf / (1 - beta2 ** step)
+    p = p - lr * (mh / (vh.sqrt() + eps) + weight_decay * p)
+    rnd = (lambda x, dt: _sr_cpu(x, dt, gen)) if stochastic else (lambda x, dt: x.to(dt))
+    param.copy_(rnd(p, param.dtype).reshape(param.shape))
+    v.copy_(rnd(vf, v.dtype).reshape(v.shape))
+    if _is_f8(m.dtype):
+        blocks = mf.reshape(-1, 128)
+        sc = blocks.abs().amax(-1).clamp_min(1e-30) / 448.0
+        m.copy_((blocks / sc[:, None]).clamp(-448, 448).to(m.dtype).reshape(m.shape))
+        m_scales.copy_(sc.reshape(m_scales.shape))
+    else:
+        m.copy_(rnd(mf, m.dtype).reshape(m.shape))
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, param.float().abs().max().reshape_as(absmax)))
+
+
+NORM_PARTIALS = 512
+
+
+def norm_squared(partials: torch.Tensor, x: torch.Tensor) -> None:
+    """partials[b] += partial sum of squares of x (deterministic per-block slots)."""
+    if x.is_cuda:
+        L.check(L.kernels().llmq_norm_squared(L.ptr(partials), L.ptr(x), _ll(x.numel()), L.dtype_code(x.dtype), partials.numel(),
+                                              L.stream_ptr()), "norm_squared")
+        return
+    partials[0] += x.float().pow(2).sum()
+
+
+def deterministic_sum(out: torch.Tensor, x: torch.Tensor) -> None:
+    if x.is_cuda:
+        L.check(L.kernels().llmq_deterministic_sum(L.ptr(out), L.ptr(x), x.numel(), L.stream_ptr()), "deterministic_sum")
+        return
+    out.copy_(x.float().sum().reshape_as(out))
+
+
+def norm_finish(io: torch.Tensor, clip: float, host_norm: Optional[torch.Tensor] = None) -> None:
+    """io[0]: squared norm -> norm; io[1] <- clip multiplier (min(1, clip / norm); 0 for a non-finite norm)."""
+    if io.is_cuda:
+        L.check(L.kernels().llmq_norm_finish(L.ptr(io), _f(clip), L.ptr(host_norm), L.stream_ptr()), "norm_finish")
+        return
+    norm = io[0].sqrt()
+    scale = torch.ones(())
+    if clip > 0 and norm > clip:
+        scale = clip / norm
+    if not torch.isfinite(norm):
+        scale = torch.zeros(())
+    io[0] = norm
+    io[1] = scale
+    if host_norm is not None:
+        host_norm.copy_(norm.reshape_as(host_norm))
+
+
+def vector_add_sr(dst: torch.Tensor, a: torch.Tensor, b: torch.Tensor, scale: float = 1.0, seed: int = 0) -> None:
+    """dst = SR(scale * (a + b))."""
+    if dst.is_cuda:
+        L.check(L.kernels().llmq_vector_add_sr(L.ptr(dst), L.ptr(a), L.ptr(b), _f(scale), _ll(dst.numel()), ctypes.c_uint(seed & 0xFFFFFFFF),
+                                               L.dtype_code(dst.dtype), num_sms(dst.device), L.stream_ptr()), "vector_add_sr")
+        return
+    gen = torch.Generator().manual_seed(seed)
+    r = scale * (a.float() + b.float())
+    dst.copy_(_sr_cpu(r.reshape(-1), dst.dtype, gen).reshape(dst.shape))
+
+
+def vector_reduce_sr(dst: torch.Tensor, src: torch.Tensor, scale: float, n_shards: int, *, skip: int = -1,
+                     accumulate: bool = False, seed: int = 0) -> None:
+    """dst = SR(scale * (sum_{k != skip} src[k] (+ dst))), src is (n_shards, dst.numel())."""
+    n = dst.numel()
+    if dst.is_cuda:
+        L.check(L.kernels().llmq_vector_reduce_sr(L.ptr(dst), L.ptr(src), _f(scale), n_shards, skip, _ll(n), int(accumulate), _ll(n),
+                                                  ctypes.c_uint(seed & 0xFFFFFFFF), L.dtype_code(dst.dtype), num_sms(dst.device),
+                                                  L.stream_ptr()), "vector_reduce_sr")
+        return
+    gen = torch.Generator().manual_seed(seed)
+    s = src.float().reshape(n_shards, n)
+    acc = dst.float().reshape(-1).clone() if accumulate else torch.zeros(n)
+    for k in range(n_shards):
+        if k != skip:
+            acc = acc + s[k]
+    dst.copy_(_sr_cpu(acc * scale, dst.dtype, gen).reshape(dst.shape))
+
+
+# =====================================================================================================
+# Embedding / bias
+def encoder_forward(out: torch.Tensor, tokens: torch.Tensor, wte: torch.Tensor) -> None:
+    V, C = wte.shape
+    if out.is_cuda:
+        L.check(L.kernels().llmq_encoder_forward(L.ptr(out), L.ptr(tokens), L.ptr(wte), _ll(tokens.numel()), C, V, L.dtype_code(wte.dtype),
+                                                 num_sms(out.device), L.stream_ptr()), "encoder_forward")
+        return
+    out.copy_(wte[tokens.reshape(-1).long().clamp(0, V - 1)].reshape(out.shape))
+
+
+def encoder_backward(dwte: torch.Tensor, dout: torch.Tensor, tokens: torch.Tensor) -> None:
+    """dwte[tok] += sum of dout rows with that token; deterministic (positions are summed in ascending order)."""
+    V, C = dwte.shape
+    flat = tokens.reshape(-1)
+    if dwte.is_cuda:
+        sorted_tok, sorted_pos = torch.sort(flat, stable=True)
+        uniq, counts = torch.unique_consecutive(sorted_tok, return_counts=True)
+        seg_start = torch.zeros(uniq.numel() + 1, dtype=torch.int32, device=dwte.device)
+        seg_start[1:] = torch.cumsum(counts, 0)
+        L.check(L.kernels().llmq_encoder_backward(L.ptr(dwte), L.ptr(dout), L.ptr(sorted_pos.int()), L.ptr(seg_start), L.ptr(uniq.int()),
+                                                  int(uniq.numel()), C, L.dtype_code(dwte.dtype), L.stream_ptr()), "encoder_backward")
+        return
+    acc = dwte.float()
+    acc.index_add_(0, flat.long(), dout.float().reshape(-1, C))
+    dwte.copy_(acc.to(dwte.dtype))
+
+
+def bias_backward(dbias: torch.Tensor, dout: torch.Tensor, scratch: Optional[torch.Tensor], *, scale_a: Optional[torch.Tensor] = None,
+                  scale_b: Optional[torch.Tensor] = None, accumulate: bool = True) -> None:
+    """dbias (+)= scale * sum_rows dout (dout may be fp8 with a dequantisation factor)."""
+    C = dout.shape[-1]
+    rows = dout.numel() // C
+    if dout.is_cuda:
+        slices = 64
+        assert scratch is not None and scratch.numel() >= slices * C
+        L.check(L.kernels().llmq_bias_backward(L.ptr(dbias), L.ptr(scratch), L.ptr(dout), _ll(rows), C, slices, L.ptr(scale_a), L.ptr(scale_b),
+                                               int(accumulate), L.dtype_code(dout.dtype), L.dtype_code(dbias.dtype), L.stream_ptr()),
+                "bias_backward")
+        return
+    s = dout.float().reshape(rows, C).sum(0)
+    if scale_a is not None:
+        s = s * scale_a.float()
+    if scale_b is not None:
+        s = s * scale_b.float()
+    if accumulate:
+        s = s + dbias.float()
+    dbias.copy_(s.to(dbias.dtype))
+
+
+# =====================================================================================================
+# Attention
+def attention_forward(out: torch.Tensor, lse: torch.Tensor, qkv: torch.Tensor, Hq: int, Hkv: int) -> None:
+    """Causal GQA attention on packed qkv (B,T,Hq+2Hkv,HS): out (B,T,Hq,HS), lse (B,Hq,T) natural log."""
+    B, T, H, HS = qkv.shape
+    if qkv.is_cuda:
+        L.check(L.kernels().llmq_attention_forward(L.ptr(out), L.ptr(lse), L.ptr(qkv), B, T, Hq, Hkv, HS,
+                                                   L.ptr(status_word(qkv.device)), L.stream_ptr()), "attention_forward")
+        return
+    o, l = _attention_ref(qkv.float(), Hq, Hkv)
+    out.copy_(o.to(out.dtype))
+    lse.copy_(l)
+
+
+def _attention_ref(qkv: torch.Tensor, Hq: int, Hkv: int):
+    B, T, H, HS = qkv.shape
+    q = qkv[:, :, :Hq].permute(0, 2, 1, 3)
+    k = qkv[:, :, Hq:Hq + Hkv].permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
+    v = qkv[:, :, Hq + Hkv:].permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, 1)
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(HS)
+    mask = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    l = torch.logsumexp(s, -1)
+    p = torch.exp(s - l[..., None])
+    o = (p @ v).permute(0, 2, 1, 3)
+    return o, l
+
+
+def attention_backward(dqkv: torch.Tensor, scratch: Optional[torch.Tensor], dout: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                       qkv: torch.Tensor, Hq: int, Hkv: int) -> None:
+    """Packed gradient of :func:`attention_forward`; ``scratch`` holds B*Hq*T floats."""
+    B, T, H, HS = qkv.shape
+    if qkv.is_cuda:
+        assert scratch is not None and scratch.numel() >= B * Hq * T
+        L.check(L.kernels().llmq_attention_backward(L.ptr(dqkv), L.ptr(scratch), L.ptr(dout), L.ptr(out), L.ptr(lse), L.ptr(qkv), B, T, Hq, Hkv,
+                                                    HS, L.ptr(status_word(qkv.device)), L.stream_ptr()), "attention_backward")
+        return
+    x = qkv.float().detach().requires_grad_(True)
+    o, _ = _attention_ref(x, Hq, Hkv)
+    (g,) = torch.autograd.grad(o, x, dout.float())
+    dqkv.copy_(g.to(dqkv.dtype))

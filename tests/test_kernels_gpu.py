@@ -1,0 +1,309 @@
+"""Every CUDA kernel against the plain PyTorch fp32 implementation of the same operation (the CPU path
+of llmq_b200.ops.kernels), at small and odd shapes."""
+import math
+
+import pytest
+import torch
+
+from llmq_b200.ops import kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+F8 = torch.float8_e4m3fn
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float().cpu(), b.float().cpu()
+    assert a.shape == b.shape
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"max err {err} vs ref scale {ref}"
+
+
+@pytest.fixture(autouse=True)
+def _check_status():
+    yield
+    torch.cuda.synchronize()
+    K.check_status(torch.device(DEV, 0))
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (384, 272, 192), (1008, 896, 1024)])
+@pytest.mark.parametrize("dt", ["bf16", "fp8"])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+def test_gemm(M, N, Kd, dt, a_mn, b_mn):
+    torch.manual_seed(1)
+    A = torch.randn(M, Kd)
+    B = torch.randn(N, Kd)
+    A, B = (A.to(BF), B.to(BF)) if dt == "bf16" else (A.to(F8), B.to(F8))
+    As = A.float().t().contiguous().to(A.dtype) if a_mn else A
+    Bs = B.float().t().contiguous().to(B.dtype) if b_mn else B
+    out = torch.zeros(M, N, dtype=BF, device=DEV)
+    K.gemm(out, As.to(DEV), Bs.to(DEV), a_mn=bool(a_mn), b_mn=bool(b_mn))
+    close(out, A.float() @ B.float().t(), rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_epilogue():
+    torch.manual_seed(2)
+    M, N, Kd = 256, 512, 256
+    A, B = torch.randn(M, Kd).to(BF), torch.randn(N, Kd).to(BF)
+    bias = torch.randn(N).to(BF)
+    C0 = torch.randn(M, N).to(BF)
+    sa, sb = torch.tensor([0.5]), torch.tensor([0.25])
+    ref = C0.clone()
+    am_ref = torch.zeros(1)
+    K.gemm(ref, A, B, bias=bias, accumulate=True, scale_a=sa, scale_b=sb, alpha=2.0, absmax=am_ref)
+    out = C0.to(DEV)
+    am = torch.zeros(1, device=DEV)
+    K.gemm(out, A.to(DEV), B.to(DEV), bias=bias.to(DEV), accumulate=True, scale_a=sa.to(DEV), scale_b=sb.to(DEV), alpha=2.0, absmax=am)
+    close(out, ref)
+    close(am, am_ref)
+    outf = torch.zeros(M, N, device=DEV)
+    K.gemm(outf, A.to(DEV), B.to(DEV))
+    close(outf, A.float() @ B.float().t(), rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("C", [64, 896, 3584])
+@pytest.mark.parametrize("fused", [False, True])
+def test_rmsnorm_forward(C, fused):
+    torch.manual_seed(3)
+    rows = 37
+    a, b, w = torch.randn(rows, C).to(BF), torch.randn(rows, C).to(BF), (1 + 0.1 * torch.randn(C)).to(BF)
+    outs = []
+    for dev in ("cpu", DEV):
+        y = torch.zeros(rows, C, dtype=BF, device=dev)
+        res = torch.zeros(rows, C, dtype=BF, device=dev)
+        rstd = torch.zeros(rows, device=dev)
+        am = torch.zeros(1, device=dev)
+        K.rmsnorm_forward(y, rstd, a.to(dev), w.to(dev), 1e-6, residual_out=res if fused else None,
+                          inp2=b.to(dev) if fused else None, absmax=am)
+        q = torch.zeros(rows, C, dtype=F8, device=dev)
+        qs = torch.zeros(1, device=dev)
+        K.rmsnorm_forward(None, None, a.to(dev), w.to(dev), 1e-6, residual_out=res if fused else None,
+                          inp2=b.to(dev) if fused else None, q_out=q, known_absmax=am, q_scale=qs)
+        outs.append((y, res, rstd, am, q, qs))
+    for g, r in zip(outs[1], outs[0]):
+        close(g, r, rtol=1e-2, atol=1e-2 if g.dtype != F8 else 0.07 * 448)
+
+
+@pytest.mark.parametrize("C", [64, 896, 3584])
+def test_rmsnorm_backward(C):
+    torch.manual_seed(4)
+    rows = 300
+    x, dy, w = torch.randn(rows, C).to(BF), torch.randn(rows, C).to(BF), (1 + 0.1 * torch.randn(C)).to(BF)
+    dres = torch.randn(rows, C).to(BF)
+    dw0 = torch.randn(C).to(BF)
+    res = []
+    for dev in ("cpu", DEV):
+        rstd = torch.zeros(rows, device=dev)
+        K.rmsnorm_forward(None, rstd, x.to(dev), w.to(dev), 1e-6)
+        dinp = dres.clone().to(dev)
+        dw = dw0.clone().to(dev)
+        am = torch.zeros(1, device=dev)
+        scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), device=dev)
+        K.rmsnorm_backward(dinp, dw, scratch, dy.to(dev), x.to(dev), w.to(dev), rstd, absmax=am, accumulate_dweight=True)
+        res.append((dinp, dw, am))
+    close(res[1][0], res[0][0])
+    close(res[1][1], res[0][1], rtol=2e-2, atol=0.3)
+    close(res[1][2], res[0][2])
+
+
+@pytest.mark.parametrize("D", [8, 172 * 2, 4864])
+def test_swiglu(D):
+    torch.manual_seed(5)
+    rows = 33
+    x = torch.randn(rows, 2 * D).to(BF)
+    dy = torch.randn(rows, D).to(BF)
+    res = []
+    for dev in ("cpu", DEV):
+        out = torch.zeros(rows, D, dtype=BF, device=dev)
+        am = torch.zeros(1, device=dev)
+        K.swiglu_forward(out, x.to(dev), absmax=am)
+        q = torch.zeros(rows, D, dtype=F8, device=dev)
+        qs = torch.zeros(1, device=dev)
+        K.swiglu_forward(None, x.to(dev), q_out=q, known_absmax=am, q_scale=qs)
+        dx = x.clone().to(dev)
+        am2 = torch.zeros(1, device=dev)
+        K.swiglu_backward(dx, dy.to(dev), dx, absmax=am2)
+        res.append((out, am, q, qs, dx, am2))
+    for g, r in zip(res[1], res[0]):
+        close(g, r, rtol=1e-2, atol=1e-2 if g.dtype != F8 else 0.07 * 448)
+
+
+@pytest.mark.parametrize("HS", [16, 64, 128])
+def test_rope(HS):
+    torch.manual_seed(6)
+    B, T, Hq, Hkv = 2, 48, 4, 2
+    x = torch.randn(B, T, Hq + 2 * Hkv, HS).to(BF)
+    res = []
+    for dev in ("cpu", DEV):
+        f = K.rope_table(T, HS, 1e6, dev)
+        y = x.clone().to(dev)
+        K.rope(y, y, f, Hq, Hkv)
+        z = torch.zeros_like(y)
+        am = torch.zeros(1, device=dev)
+        K.rope(z, y, f, Hq, Hkv, backward=True, absmax=am)
+        res.append((f, y, z, am))
+    for g, r in zip(res[1], res[0]):
+        close(g, r, rtol=1e-2, atol=1e-2)
+    close(res[1][2], x, rtol=2e-2, atol=3e-2)          # backward(forward(x)) == x
+
+
+def test_quant_transpose_convert_fill():
+    torch.manual_seed(7)
+    x = (torch.randn(130, 72) * 3).to(BF)
+    for dev in (DEV,):
+        xd = x.to(dev)
+        am = torch.zeros(1, device=dev)
+        K.abs_max(am, xd)
+        assert am.item() == x.float().abs().max().item()
+        for qdt in (F8, torch.float8_e5m2):
+            q = torch.zeros(130, 72, dtype=qdt, device=dev)
+            sc = torch.zeros(1, device=dev)
+            K.quantize(q, sc, xd, am)
+            qr = torch.zeros(130, 72, dtype=qdt)
+            scr = torch.zeros(1)
+            K.quantize(qr, scr, x, am.cpu())
+            close(q.float() * sc, qr.float() * scr, rtol=0.13, atol=0)
+            close(q.float() * sc, x, rtol=0.13, atol=0)
+            qt = torch.zeros(72, 130, dtype=qdt, device=dev)
+            K.transpose(qt, xd, absmax=am, scale_out=sc)
+            assert torch.equal(qt.float().t().cpu(), q.float().cpu())
+        t = torch.zeros(72, 130, dtype=BF, device=dev)
+        K.transpose(t, xd)
+        assert torch.equal(t.cpu(), x.t())
+        f = torch.zeros(130, 72, device=dev)
+        K.convert(f, xd)
+        assert torch.equal(f.cpu(), x.float())
+        K.fill(f, 1.5)
+        assert (f == 1.5).all()
+        n = torch.zeros(1 << 20, dtype=BF, device=dev)
+        K.fill_normal(n, 0.5, 0.02, seed=42, subsequence=3)
+        assert abs(n.float().mean().item() - 0.5) < 1e-3 and abs(n.float().std().item() - 0.02) < 1e-3
+        part = torch.zeros(1 << 10, dtype=BF, device=dev)
+        K.fill_normal(part, 0.5, 0.02, seed=42, subsequence=3, offset=4096)
+        assert torch.equal(part, n[4096:4096 + 1024])
+        other = torch.zeros(1 << 10, dtype=BF, device=dev)
+        K.fill_normal(other, 0.5, 0.02, seed=42, subsequence=4)
+        assert not torch.equal(other, n[:1024])
+
+
+@pytest.mark.parametrize("V", [512, 1000, 151936])
+def test_fused_classifier(V):
+    torch.manual_seed(8)
+    rows = 24
+    logits = (torch.randn(rows, V) * 2).to(BF)
+    tg = torch.randint(0, V, (rows,), dtype=torch.int32)
+    tg[3] = -100
+    res = []
+    for dev in ("cpu", DEV):
+        lg = logits.clone().to(dev)
+        losses = torch.zeros(rows, device=dev)
+        lse = torch.zeros(rows, device=dev)
+        K.fused_classifier(lg, losses, lse, tg.to(dev), 1.0 / rows, z_reg=1e-4)
+        st = torch.zeros(2, device=dev)
+        K.lse_stats(st, lse)
+        res.append((lg, losses, lse, st))
+    close(res[1][1], res[0][1], rtol=1e-3, atol=1e-3)
+    close(res[1][2], res[0][2], rtol=1e-3, atol=1e-3)
+    close(res[1][3], res[0][3], rtol=1e-3, atol=1e-3)
+    close(res[1][0], res[0][0], rtol=2e-2, atol=1e-5)
+    assert res[1][0][3].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("combo", [(BF, BF, BF), (BF, torch.float32, torch.float32), (BF, F8, BF), (torch.float32,) * 3])
+def test_adamw(combo):
+    torch.manual_seed(9)
+    pd, md, vd = combo
+    n = 128 * 37
+    p0 = torch.randn(n).to(pd)
+    g = (torch.randn(n) * 0.1).to(pd)
+    res = []
+    for dev in ("cpu", DEV):
+        p = p0.clone().to(dev)
+        m = torch.zeros(n, dtype=md, device=dev)
+        v = torch.zeros(n, dtype=vd, device=dev)
+        ms = torch.ones(n // 128, device=dev) if md == F8 else None
+        gs = torch.tensor([0.5], device=dev)
+        am = torch.zeros(1, device=dev)
+        for step in (1, 2, 3):
+            K.adamw(p, g.to(dev), m, v, lr=1e-2, beta1=0.9, beta2=0.95, step=step, eps=1e-8, weight_decay=0.1, grad_scale=gs,
+                    absmax=am, m_scales=ms, seed=step, stochastic=True)
+        mm = m.float() * ms.repeat_interleave(128) if md == F8 else m.float()
+        res.append((p, mm, v, am))
+    close(res[1][0], res[0][0], rtol=1e-2, atol=1e-2)
+    close(res[1][1], res[0][1], rtol=8e-2, atol=1e-3)
+    close(res[1][2], res[0][2], rtol=2e-2, atol=1e-5)
+    close(res[1][3], res[0][3], rtol=1e-2, atol=1e-2)
+
+
+def test_sr_unbiased_and_reduce():
+    n = 1 << 16
+    a = torch.full((n,), 1.0, dtype=BF, device=DEV)
+    b = torch.full((n,), 2.0 ** -10, dtype=BF, device=DEV)        # far below bf16 resolution at 1.0
+    dst = torch.zeros(n, dtype=BF, device=DEV)
+    K.vector_add_sr(dst, a, b, 1.0, seed=5)
+    mean = dst.float().mean().item()
+    assert abs(mean - (1 + 2.0 ** -10)) < 2e-4, mean
+    dst2 = torch.zeros(n, dtype=BF, device=DEV)
+    K.vector_add_sr(dst2, a, b, 1.0, seed=5)
+    assert torch.equal(dst, dst2)
+    src = torch.randn(4, n, device=DEV).to(BF)
+    out = torch.ones(n, dtype=BF, device=DEV)
+    K.vector_reduce_sr(out, src, 0.25, 4, skip=1, accumulate=True, seed=1)
+    ref = 0.25 * (src.float()[[0, 2, 3]].sum(0) + 1)
+    close(out, ref, rtol=1e-2, atol=1e-2)
+
+
+def test_global_norm():
+    torch.manual_seed(10)
+    xs = [torch.randn(1000, 37).to(BF).to(DEV), torch.randn(12345, device=DEV)]
+    part = torch.zeros(K.NORM_PARTIALS, device=DEV)
+    for x in xs:
+        K.norm_squared(part, x)
+    io = torch.zeros(2, device=DEV)
+    K.deterministic_sum(io[:1], part)
+    K.norm_finish(io, 1.0)
+    ref = math.sqrt(sum(x.float().pow(2).sum().item() for x in xs))
+    assert abs(io[0].item() - ref) / ref < 1e-4
+    assert abs(io[1].item() - 1.0 / ref) / (1.0 / ref) < 1e-4
+
+
+def test_encoder_and_bias():
+    torch.manual_seed(11)
+    V, C, B, T = 512, 64, 4, 96
+    wte = torch.randn(V, C).to(BF)
+    tok = torch.randint(0, 40, (B, T), dtype=torch.int32)
+    res = []
+    dout = torch.randn(B, T, C).to(BF)
+    for dev in ("cpu", DEV):
+        out = torch.zeros(B, T, C, dtype=BF, device=dev)
+        K.encoder_forward(out, tok.to(dev), wte.to(dev))
+        dw = torch.zeros(V, C, dtype=BF, device=dev)
+        K.encoder_backward(dw, dout.to(dev), tok.to(dev))
+        db = torch.ones(C, dtype=BF, device=dev)
+        K.bias_backward(db, dout.to(dev), torch.zeros(64 * C, device=dev), accumulate=True)
+        res.append((out, dw, db))
+    assert torch.equal(res[1][0].cpu(), res[0][0])
+    close(res[1][1], res[0][1], rtol=1e-2, atol=5e-2)
+    close(res[1][2], res[0][2], rtol=1e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("HS,Hq,Hkv,T", [(64, 4, 2, 256), (128, 4, 1, 384), (64, 14, 2, 128), (128, 7, 1, 200)])
+def test_attention(HS, Hq, Hkv, T):
+    torch.manual_seed(12)
+    B = 2
+    qkv = torch.randn(B, T, Hq + 2 * Hkv, HS).to(BF)
+    dout = torch.randn(B, T, Hq, HS).to(BF)
+    res = []
+    for dev in ("cpu", DEV):
+        out = torch.zeros(B, T, Hq, HS, dtype=BF, device=dev)
+        lse = torch.zeros(B, Hq, T, device=dev)
+        K.attention_forward(out, lse, qkv.to(dev), Hq, Hkv)
+        dqkv = torch.zeros_like(qkv, device=dev)
+        scratch = torch.zeros(B * Hq * T, device=dev)
+        K.attention_backward(dqkv, scratch, dout.to(dev), out, lse, qkv.to(dev), Hq, Hkv)
+        res.append((out, lse, dqkv))
+    close(res[1][0], res[0][0], rtol=2e-2, atol=2e-2)
+    close(res[1][1], res[0][1], rtol=1e-3, atol=1e-2)
+    close(res[1][2], res[0][2], rtol=3e-2, atol=3e-2)
