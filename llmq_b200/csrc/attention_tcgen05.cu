@@ -52,7 +52,7 @@ int encode_btw(CUtensorMap* out, const void* base, int B, int T, long long W, in
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+    return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 
 // Writes 32 consecutive bf16 values (columns c0 .. c0+31 of row `row`) into a [rows][64] K-major tile with
@@ -164,6 +164,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv, k_bar, kcol + c * 64, (j + 1) * BKV, b);
         }
         float s[64];
+        __syncwarp();
         {
             uint32_t r[32];
             tmem_ld_32x32b_x32(tS + lane_off, r);
@@ -220,6 +221,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_expect_tx(v_bar, KV_BYTES);
             for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv, v_bar, vcol + c * 64, (j + 1) * BKV, b);
         }
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < HS / 32; ++c) {
             uint32_t r[32];
@@ -386,6 +388,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
         if (!mbar_wait(sp_bar, par, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const bool diag = qb * BQ < kv0 + BKV;                      // some (kv, q) pairs have q < kv
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < BQ / 32; ++c) {
             uint32_t rs[32], rp[32];
@@ -428,38 +431,35 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     }
     if (!ok && tid == 0) atomicOr(p.status, kErrOther);
 
-    if (ok && n_it > 0 && kv_row < p.T) {
+    if (ok && n_it > 0) {
+        // The TMEM loads are warp-collective: every lane executes them, only the stores are predicated.
+        const bool row_ok = kv_row < p.T;
         const int H = p.Hq + 2 * p.Hkv;
-        bf16* dk = p.dqkv + ((static_cast<long long>(b) * p.T + kv_row) * H + p.Hq + kvh) * HS;
-        bf16* dv = p.dqkv + ((static_cast<long long>(b) * p.T + kv_row) * H + p.Hq + p.Hkv + kvh) * HS;
+        const long long rbase = (static_cast<long long>(b) * p.T + (row_ok ? kv_row : 0)) * H;
+        bf16* dk = p.dqkv + (rbase + p.Hq + kvh) * HS;
+        bf16* dv = p.dqkv + (rbase + p.Hq + p.Hkv + kvh) * HS;
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < HS / 32; ++c) {
             uint32_t rk[32], rv[32];
             tmem_ld_32x32b_x32(tdK + lane_off + c * 32, rk);
             tmem_ld_32x32b_x32(tdV + lane_off + c * 32, rv);
             tmem_ld_wait();
+            if (row_ok) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                uint4 ok4, ov4;
-                __nv_bfloat162* kb2 = reinterpret_cast<__nv_bfloat162*>(&ok4);
-                __nv_bfloat162* vb2 = reinterpret_cast<__nv_bfloat162*>(&ov4);
+                for (int g = 0; g < 4; ++g) {
+                    uint4 ok4, ov4;
+                    __nv_bfloat162* kb2 = reinterpret_cast<__nv_bfloat162*>(&ok4);
+                    __nv_bfloat162* vb2 = reinterpret_cast<__nv_bfloat162*>(&ov4);
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    kb2[jj] = __floats2bfloat162_rn(__uint_as_float(rk[g * 8 + 2 * jj]), __uint_as_float(rk[g * 8 + 2 * jj + 1]));
-                    vb2[jj] = __floats2bfloat162_rn(__uint_as_float(rv[g * 8 + 2 * jj]), __uint_as_float(rv[g * 8 + 2 * jj + 1]));
+                    for (int jj = 0; jj < 4; ++jj) {
+                        kb2[jj] = __floats2bfloat162_rn(__uint_as_float(rk[g * 8 + 2 * jj]), __uint_as_float(rk[g * 8 + 2 * jj + 1]));
+                        vb2[jj] = __floats2bfloat162_rn(__uint_as_float(rv[g * 8 + 2 * jj]), __uint_as_float(rv[g * 8 + 2 * jj + 1]));
+                    }
+                    *reinterpret_cast<uint4*>(dk + c * 32 + g * 8) = ok4;
+                    *reinterpret_cast<uint4*>(dv + c * 32 + g * 8) = ov4;
                 }
-                *reinterpret_cast<uint4*>(dk + c * 32 + g * 8) = ok4;
-                *reinterpret_cast<uint4*>(dv + c * 32 + g * 8) = ov4;
             }
-        }
-    } else if (ok && n_it > 0) {
-        // rows beyond T: still take part in the (warp-collective) TMEM loads
-#pragma unroll
-        for (int c = 0; c < HS / 32; ++c) {
-            uint32_t rk[32];
-            tmem_ld_32x32b_x32(tdK + lane_off + c * 32, rk);
-            tmem_ld_32x32b_x32(tdV + lane_off + c * 32, rk);
-            tmem_ld_wait();
         }
     }
     tc_fence_before_sync();
@@ -564,6 +564,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
             for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv64, v_bar, vcol + c * 64, (j + 1) * BKV, b);
         }
         const bool diag = (j + 1) * BKV > q0;
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < BKV / 32; ++c) {
             uint32_t rs[32], rp[32];
@@ -604,6 +605,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
     if (ok) {
         const int H = p.Hq + 2 * p.Hkv;
         bf16* dq = p.dqkv + ((static_cast<long long>(b) * p.T + row) * H + h) * HS;
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < HS / 32; ++c) {
             uint32_t r[32];
@@ -628,14 +630,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
     if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-template <typename K>
+// Tag makes the static flag unique per kernel instantiation (several kernels share one signature).
+template <int Tag, typename K>
 int set_smem(K kernel, int bytes) {
     static bool done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!done[dev & 63]) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        if (e != cudaSuccess) return static_cast<int>(e);
+        if (e != cudaSuccess) return 2000 + static_cast<int>(e);
         done[dev & 63] = true;
     }
     return 0;
@@ -650,7 +653,7 @@ int fwd_impl(void* out, float* lse, const void* qkv, int B, int T, int Hq, int H
     rc = encode_btw(&tkv, qkv, B, T, static_cast<long long>(H) * HS, 64);
     if (rc) return rc;
     constexpr int smem = 128 * HS * 2 + 2 * 64 * HS * 2 + 128 * 64 * 2 + 128;
-    rc = set_smem(attn_fwd_kernel<HS>, smem);
+    rc = set_smem<HS>(attn_fwd_kernel<HS>, smem);
     if (rc) return rc;
     AttnParams p{};
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.scale = 1.f / sqrtf(static_cast<float>(HS));
@@ -682,7 +685,7 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
     p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = static_cast<bf16*>(dqkv); p.status = status;
     {
         constexpr int smem = 2 * 128 * HS * 2 + 4 * 64 * HS * 2 + 2 * 128 * 64 * 2 + 2 * 64 * 4 + 128;
-        rc = set_smem(attn_bwd_dkdv_kernel<HS>, smem);
+        rc = set_smem<1000 + HS>(attn_bwd_dkdv_kernel<HS>, smem);
         if (rc) return rc;
         dim3 grid((T + 127) / 128, Hkv, B);
         attn_bwd_dkdv_kernel<HS><<<grid, 128, smem, s>>>(t128, t64, tdo64, p);
@@ -691,7 +694,7 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
     }
     {
         constexpr int smem = 2 * 128 * HS * 2 + 2 * 64 * HS * 2 + 128 * 64 * 2 + 128;
-        rc = set_smem(attn_bwd_dq_kernel<HS>, smem);
+        rc = set_smem<2000 + HS>(attn_bwd_dq_kernel<HS>, smem);
         if (rc) return rc;
         dim3 grid((T + 127) / 128, Hq, B);
         attn_bwd_dq_kernel<HS><<<grid, 128, smem, s>>>(t128, t64, tdo128, p);

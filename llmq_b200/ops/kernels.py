@@ -25,7 +25,8 @@ _FP8_MAX = {F8: 448.0, F8_E5: 57344.0}
 _state = {}
 
 
-def _dev_state(device: torch.device):
+def _dev_state(device):
+    device = torch.device(device)
     idx = device.index if device.index is not None else torch.cuda.current_device()
     st = _state.get(idx)
     if st is None:
