@@ -1,0 +1,458 @@
+"""Llama / Qwen2 decoder with hand-scheduled forward, backward and optimizer step (no autograd).
+
+The step structure follows the reference model (src/models/llama_model.cpp:73-894): ``forward`` runs the
+blocks and the final norm, ``backward`` runs the (chunked) LM head with the fused classifier, then the blocks
+in reverse with optional recomputation, and ``update`` clips by the global gradient norm and applies AdamW to
+the local shards.  What differs is how the work is mapped to the hardware: every GEMM is the tcgen05 kernel
+reading operands in their natural layout (MN-major descriptors take the place of the transpose kernels of the
+fp8 backward recipe, llama_model.cpp:309-339), attention is the tcgen05 flash kernel on the packed QKV
+tensor, and quantisation uses per-tensor just-in-time scaling with abs-max values produced by the preceding
+kernel's epilogue.
+
+Weight layout (llama_weights.cpp:915-938): q/k/v are fused row-wise into ``qkv_w`` [QC, C] (+ ``qkv_b``), up and
+gate into ``up_w`` [2D, C] (up first), embeddings may be tied to the LM head.
+"""
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import TransformerConfig
+from ..ops import kernels as K
+from ..options import LLamaOptions
+from ..parallel.comm import Communicator, LocalComm
+from ..parallel.zero import F8_TYPES, MATRICES, GradientManager, OptimizerStateManager, WeightsManager
+
+# abs-max slots per layer: index -> (absmax, scale)
+S_LN1, S_ATT, S_LN2, S_SWIGLU, S_DRESFFN, S_DMLPUP, S_DRESATT, S_DQKV = range(8)
+N_SLOTS = 16
+
+
+class LlamaModel:
+    def __init__(self, cfg: TransformerConfig, opts: LLamaOptions, comm: Optional[Communicator] = None,
+                 device: Optional[torch.device] = None, batch_size: int = 1, seq_len: int = 128):
+        cfg.validate()
+        self.cfg, self.opts = cfg, opts
+        self.comm = comm or LocalComm()
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        if opts.model_type is None:
+            opts.model_type = cfg.dtype
+        self.dtype = opts.model_type
+        self.B, self.T = batch_size, seq_len
+        self.quant = opts.matmul_dtype() in F8_TYPES
+        self.qdtype = opts.matmul_dtype()
+        self.gdtype = opts.grad_dtype() if self.quant else self.dtype
+        if seq_len > cfg.max_position_embeddings:
+            raise ValueError("sequence length exceeds max_position_embeddings")
+        self.weights = WeightsManager(cfg, opts, self.comm, self.device)
+        self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
+        self.opt_state = OptimizerStateManager(cfg, opts, self.comm, self.device, self.weights)
+        self._alloc_run_state()
+        self.adam_seed = 42
+        self.rng_state = 42                       # advanced every optimizer step; saved in checkpoints
+
+    # ================================================================================== run state
+    def _alloc_run_state(self) -> None:
+        cfg, o, dev, dt = self.cfg, self.opts, self.device, self.dtype
+        B, T, C, D, QC, V, L = self.B, self.T, cfg.hidden_size, cfg.intermediate_size, cfg.qkv_channels, cfg.vocab_size, cfg.num_hidden_layers
+        Hq, HS = cfg.num_attention_heads, cfg.head_size
+        BT = B * T
+        z = lambda *shape, dtype=dt: torch.zeros(*shape, dtype=dtype, device=dev)
+        q = self.quant
+        self.inputs = torch.zeros(B, T, dtype=torch.int32, device=dev)
+        self.targets = torch.zeros(B, T, dtype=torch.int32, device=dev)
+        self.losses = torch.zeros(B, T, dtype=torch.float32, device=dev)
+        self.lse_tok = torch.zeros(B, T, dtype=torch.float32, device=dev)
+        self.lse_stats = torch.zeros(2, dtype=torch.float32, device=dev)
+        self.group_losses = torch.zeros((T + 511) // 512, dtype=torch.float32, device=dev)
+        self.norm_io = torch.zeros(2, dtype=torch.float32, device=dev)
+        self.norm_partials = torch.zeros(K.NORM_PARTIALS, dtype=torch.float32, device=dev)
+        self.stats = torch.zeros(L, N_SLOTS, 2, dtype=torch.float32, device=dev)
+        self.freqs = K.rope_table(T, HS, cfg.rope_theta, dev)
+
+        def per_layer(shared: bool, *shape, dtype=dt):
+            if shared:
+                t = z(*shape, dtype=dtype)
+                return [t] * L
+            return [z(*shape, dtype=dtype) for _ in range(L)]
+
+        a = SimpleNamespace()
+        a.x = [z(BT, C) for _ in range(L + 1)]                         # residual stream entering each layer (+ final)
+        a.rstd1 = per_layer(False, BT, dtype=torch.float32)
+        a.rstd2 = per_layer(False, BT, dtype=torch.float32)
+        a.lse = per_layer(False, B, Hq, T, dtype=torch.float32)
+        re_ln1 = o.recompute_rms_norm or o.recompute_att or o.recompute_block
+        re_qkv = o.recompute_qkv or o.recompute_att or o.recompute_block
+        re_att = o.recompute_att or o.recompute_block
+        re_ln2 = o.recompute_rms_norm or o.recompute_ffn or o.recompute_block
+        re_up = o.recompute_ffn
+        re_sw = o.recompute_swiglu or o.recompute_ffn or o.recompute_block
+        self.re = SimpleNamespace(ln1=re_ln1, qkv=re_qkv, att=re_att, ln2=re_ln2, up=re_up, sw=re_sw, block=o.recompute_block)
+        # bf16 values of the quantised GEMM inputs are only needed until they are quantised
+        a.ln1 = per_layer(re_ln1 or q, BT, C)
+        a.ln2 = per_layer(re_ln2 or q, BT, C)
+        a.swiglu = per_layer(re_sw or q, BT, D)
+        a.qkv = per_layer(re_qkv, B, T, QC // HS, HS)
+        a.att = per_layer(re_att, BT, C)
+        a.res_att = per_layer(o.recompute_block, BT, C)
+        a.up = per_layer(re_up, BT, 2 * D)
+        if q:
+            a.ln1_q = per_layer(re_ln1, BT, C, dtype=self.qdtype)
+            a.ln2_q = per_layer(re_ln2, BT, C, dtype=self.qdtype)
+            a.swiglu_q = per_layer(re_sw, BT, D, dtype=self.qdtype)
+            a.att_q = per_layer(True, BT, C, dtype=self.qdtype)
+        self.acts = a
+        self.lnf = z(BT, C)
+        self.rstd_f = torch.zeros(BT, dtype=torch.float32, device=dev)
+        # temporaries shared by all layers
+        t = SimpleNamespace()
+        t.proj = z(BT, C)                 # attention-out / mlp-down results, folded into the next residual add
+        t.d_res = z(BT, C)                # gradient of the residual stream
+        t.d_ln = z(BT, C)                 # gradient wrt a norm output / attention output
+        t.d_sw = z(BT, D)
+        t.d_qkv = z(B, T, QC // HS, HS)
+        if q:
+            t.d_res_q = z(BT, C, dtype=self.gdtype)
+            t.d_up_q = z(BT, 2 * D, dtype=self.gdtype)
+            t.d_qkv_q = z(BT, QC, dtype=self.gdtype)
+        chunks = max(1, o.lmhead_chunks)
+        if BT % chunks:
+            raise ValueError("lmhead_chunks must divide batch * seq_len")
+        t.logits = z(BT // chunks, V)
+        t.att_scratch = torch.zeros(B * Hq * T, dtype=torch.float32, device=dev)
+        t.norm_scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32, device=dev)
+        t.bias_scratch = torch.zeros(64 * QC, dtype=torch.float32, device=dev)
+        self.tmp = t
+        self.host_scalars = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
+
+    def _slot(self, l: int, s: int):
+        st = self.stats[l, s]
+        return st[0:1], st[1:2]
+
+    # ================================================================================== init / import
+    def init_weights(self, seed: int = 42) -> None:
+        """N(0, 0.02) for qkv / up / embeddings / head, N(0, 0.02/sqrt(2L)) for the two output projections,
+        ones for norms, zeros for biases.  The stream of a tensor depends only on (seed, tensor index) and the
+        element index, so every world size produces the same model."""
+        w = self.weights
+        for idx, (name, master, spec, l) in enumerate(w.master_items()):
+            rows_per = master.shape[0]
+            offset = self.comm.rank * rows_per * (master.numel() // max(rows_per, 1))
+            dev_t = master if master.device.type == self.device.type else torch.empty(master.shape, dtype=master.dtype, device=self.device)
+            if spec.init_std < 0:
+                dev_t.fill_(1.0)
+            elif spec.init_std == 0:
+                dev_t.zero_()
+            else:
+                K.fill_normal(dev_t, 0.0, spec.init_std, seed, subsequence=idx, offset=offset)
+            if dev_t is not master:
+                master.copy_(dev_t)
+        self.on_weights_changed()
+
+    def on_weights_changed(self) -> None:
+        """After init / import / checkpoint restore: refresh abs-max values and invalidate the work copies."""
+        self.weights.sync_absmax(recompute=True)
+        self.weights.invalidate()
+
+    # ================================================================================== quantised matmuls
+    def _fwd_mm(self, out, act, act_q, slot, W, w_scale, bias=None):
+        if not self.quant:
+            K.gemm(out, act, W, bias=bias)
+            return
+        am, sc = slot
+        if act is not None:
+            K.quantize(act_q, sc, act, am)
+        K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale)
+
+    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate):
+        """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
+        W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second."""
+        if not self.quant:
+            if dinp is not None:
+                K.gemm(dinp, dout, W, b_mn=True)
+            K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate)
+            if dbias is not None:
+                K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
+            return
+        am, sc = slot
+        K.quantize(dout_q, sc, dout, am)
+        if dinp is not None:
+            K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale)
+        K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
+        if dbias is not None:
+            K.bias_backward(dbias, dout_q, self.tmp.bias_scratch, scale_a=sc, accumulate=True)
+
+    # ================================================================================== forward
+    def forward(self, inputs: torch.Tensor, micro_step: int = 0) -> None:
+        """inputs: int32 (B, T) on any device.  Activations stay in the run state for ``backward``."""
+        cfg, a, w = self.cfg, self.acts, self.weights
+        L = cfg.num_hidden_layers
+        self.inputs.copy_(inputs.reshape(self.B, self.T), non_blocking=True)
+        K.encoder_forward(a.x[0], self.inputs, w.get_embeddings())
+        self.stats.zero_()
+        w.gather_block(0)
+        for l in range(L):
+            if l + 1 < L:
+                w.gather_block(l + 1)
+            p = w.get_block(l)
+            am, _ = self._slot(l, S_LN1)
+            if l == 0:
+                K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.x[0], p.ln1_w, cfg.rms_norm_eps, absmax=am)
+            else:
+                K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.res_att[l - 1], p.ln1_w, cfg.rms_norm_eps, residual_out=a.x[l],
+                                  inp2=self.tmp.proj, absmax=am)
+            self._forward_block(l, p)
+            w.release_block(l)
+        K.rmsnorm_forward(self.lnf, self.rstd_f, a.res_att[L - 1], w.get_lnf(), cfg.rms_norm_eps, residual_out=a.x[L],
+                          inp2=self.tmp.proj)
+
+    def _forward_block(self, l: int, p) -> None:
+        cfg, a, t = self.cfg, self.acts, self.tmp
+        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        BT = self.B * self.T
+        qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
+        self._fwd_mm(qkv2d, a.ln1[l], a.ln1_q[l] if self.quant else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b)
+        K.rope(a.qkv[l], a.qkv[l], self.freqs, Hq, Hkv)
+        att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
+        K.attention_forward(att4, a.lse[l], a.qkv[l], Hq, Hkv)
+        if self.quant:
+            K.abs_max(self._slot(l, S_ATT)[0], a.att[l])
+        self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"])
+        K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
+                          absmax=self._slot(l, S_LN2)[0])
+        self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"])
+        K.swiglu_forward(a.swiglu[l], a.up[l], absmax=self._slot(l, S_SWIGLU)[0])
+        self._fwd_mm(t.proj, a.swiglu[l], a.swiglu_q[l] if self.quant else None, self._slot(l, S_SWIGLU), p.down_w, p.scales["down_w"])
+
+    # ================================================================================== validation
+    @torch.no_grad()
+    def validate(self, inputs: torch.Tensor, targets: torch.Tensor):
+        """Returns (mean loss, mean loss over the first 1024 positions) of one batch, averaged over ranks."""
+        self.forward(inputs)
+        self.targets.copy_(targets.reshape(self.B, self.T), non_blocking=True)
+        self.losses.zero_()
+        self._lmhead(write_grads=False, dloss=0.0, z_loss=0.0, accumulate_dw=False)
+        return self._reduce_loss(None)
+
+    def _reduce_loss(self, positions_per_rank: Optional[float]):
+        """Mean loss and mean loss over the first 1024 positions.  ``positions_per_rank`` is the number of
+        target positions behind ``self.losses`` on each rank (None: count the unmasked targets)."""
+        K.grouped_loss_sum(self.group_losses, self.losses)
+        gl = self.group_losses.clone()
+        if positions_per_rank is None:
+            cnt = (self.targets != -100).sum().float().reshape(1)
+            if self.comm.world > 1:
+                self.comm.all_reduce(cnt, "avg").wait()
+        else:
+            cnt = torch.full((1,), float(positions_per_rank), device=self.device)
+        if self.comm.world > 1:
+            self.comm.all_reduce(gl, "avg").wait()
+        cnt = cnt.clamp_min(1)
+        total = gl.sum() / cnt
+        n1k = min(self.T, 1024)
+        first = gl[: (n1k + 511) // 512].sum() / (cnt * n1k / self.T)
+        return float(total.item()), float(first.item())
+
+    # ================================================================================== LM head
+    def _lmhead(self, write_grads: bool, dloss: float, z_loss: float, accumulate_dw: bool) -> None:
+        cfg, t = self.cfg, self.tmp
+        BT, C, V = self.B * self.T, cfg.hidden_size, cfg.vocab_size
+        chunks = max(1, self.opts.lmhead_chunks)
+        n = BT // chunks
+        W = self.weights.get_head()
+        head_name = "embed" if cfg.tie_word_embeddings else "lm_head"
+        dW = self.grads.nb_full[head_name] if write_grads else None
+        tg = self.targets.view(BT)
+        losses, lse = self.losses.view(BT), self.lse_tok.view(BT)
+        for c in range(chunks):
+            sl = slice(c * n, (c + 1) * n)
+            K.gemm(t.logits, self.lnf[sl], W)
+            K.fused_classifier(t.logits, losses[sl], lse[sl], tg[sl], dloss, z_reg=z_loss * dloss, write_dlogits=write_grads)
+            if write_grads:
+                K.gemm(dW, t.logits, self.lnf[sl], a_mn=True, b_mn=True, accumulate=accumulate_dw or c > 0)
+                if c == chunks - 1 and not cfg.tie_word_embeddings:
+                    self.grads.notify_non_block(head_name)
+                K.gemm(t.d_ln[sl], t.logits, W, b_mn=True)
+        K.lse_stats(self.lse_stats, self.lse_tok.view(-1), accumulate=False)
+
+    # ================================================================================== backward
+    def backward(self, inputs: torch.Tensor, targets: torch.Tensor, z_loss: float = 0.0, grad_accum: int = 1,
+                 micro_step: int = 0) -> None:
+        cfg, a, t, w, g = self.cfg, self.acts, self.tmp, self.weights, self.grads
+        L, C = cfg.num_hidden_layers, cfg.hidden_size
+        self.targets.copy_(targets.reshape(self.B, self.T), non_blocking=True)
+        if micro_step == 0:
+            g.begin_step()
+            self.losses.zero_()
+        g.start_micro_step(micro_step, grad_accum)
+        dloss = 1.0 / (self.B * self.T * grad_accum)
+        self._lmhead(write_grads=True, dloss=dloss, z_loss=z_loss, accumulate_dw=micro_step > 0)
+        # final norm: t.d_ln holds d(lnf); produce d(residual stream) in t.d_res
+        t.d_res.zero_()
+        K.rmsnorm_backward(t.d_res, g.nb_full["lnf_w"], t.norm_scratch, t.d_ln, a.x[L], w.get_lnf(), self.rstd_f,
+                           absmax=self._slot(L - 1, S_DRESFFN)[0], accumulate_dweight=True)
+        g.notify_non_block("lnf_w")
+        w.gather_block(L - 1)
+        for l in range(L - 1, -1, -1):
+            dw, acc = g.get_block_full(l)
+            if l > 0:
+                w.gather_block(l - 1)
+            p = w.get_block(l)
+            self._recompute_block(l, p)
+            self._backward_block(l, p, dw, acc)
+            # LN1 backward adds into the residual gradient, which then belongs to layer l-1 (or the embedding)
+            slot = self._slot(l - 1, S_DRESFFN)[0] if l > 0 else None
+            K.rmsnorm_backward(t.d_res, dw["ln1_w"], t.norm_scratch, t.d_ln, a.x[l], p.ln1_w, a.rstd1[l], absmax=slot,
+                               accumulate_dweight=True)
+            w.release_block(l)
+            g.notify_block(l)
+        if not cfg.tie_word_embeddings and micro_step == 0:
+            g.nb_full["embed"].zero_()             # untied: nothing has written this buffer yet in this step
+        K.encoder_backward(g.nb_full["embed"], t.d_res, self.inputs)
+        g.notify_non_block("embed")
+        g.end_micro_step()
+
+    def _recompute_block(self, l: int, p) -> None:
+        cfg, a, t, re = self.cfg, self.acts, self.tmp, self.re
+        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        BT = self.B * self.T
+        q = self.quant
+
+        def renorm(y, yq, slot_id, x, wt, rstd):
+            am, sc = self._slot(l, slot_id)
+            if q:
+                K.rmsnorm_forward(None, None, x, wt, cfg.rms_norm_eps, q_out=yq, known_absmax=am, q_scale=sc)
+            else:
+                K.rmsnorm_forward(y, None, x, wt, cfg.rms_norm_eps)
+
+        if re.ln1:
+            renorm(a.ln1[l], a.ln1_q[l] if q else None, S_LN1, a.x[l], p.ln1_w, a.rstd1[l])
+        if re.qkv:
+            qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
+            self._fwd_mm(qkv2d, None if q else a.ln1[l], a.ln1_q[l] if q else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b)
+            if not q:
+                pass
+            K.rope(a.qkv[l], a.qkv[l], self.freqs, Hq, Hkv)
+        if re.att:
+            K.attention_forward(a.att[l].view(self.B, self.T, Hq, cfg.head_size), a.lse[l], a.qkv[l], Hq, Hkv)
+        if q:
+            # the fp8 copy of the attention output lives in a buffer shared by all layers
+            am, sc = self._slot(l, S_ATT)
+            K.quantize(a.att_q[l], sc, a.att[l], am)
+        if re.block:
+            self._fwd_mm(t.proj, None if q else a.att[l], a.att_q[l] if q else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"])
+            am, sc = self._slot(l, S_LN2)
+            if q:
+                K.rmsnorm_forward(None, None, a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
+                                  q_out=a.ln2_q[l], known_absmax=am, q_scale=sc)
+            else:
+                K.rmsnorm_forward(a.ln2[l], None, a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj)
+        elif re.ln2:
+            renorm(a.ln2[l], a.ln2_q[l] if q else None, S_LN2, a.res_att[l], p.ln2_w, a.rstd2[l])
+        if re.up:
+            self._fwd_mm(a.up[l], None if q else a.ln2[l], a.ln2_q[l] if q else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"])
+        if re.sw:
+            am, sc = self._slot(l, S_SWIGLU)
+            if q:
+                K.swiglu_forward(None, a.up[l], q_out=a.swiglu_q[l], known_absmax=am, q_scale=sc)
+            else:
+                K.swiglu_forward(a.swiglu[l], a.up[l])
+
+    def _backward_block(self, l: int, p, dw: Dict[str, torch.Tensor], acc: bool) -> None:
+        cfg, a, t = self.cfg, self.acts, self.tmp
+        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        BT, q = self.B * self.T, self.quant
+        sc_of = lambda s: self._slot(l, s)[1]
+        # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
+        self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
+                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc)
+        # ---- SwiGLU backward, in place over the saved up-projection
+        K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
+        # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
+        self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
+                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc)
+        # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
+        K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],
+                           absmax=self._slot(l, S_DRESATT)[0], accumulate_dweight=True)
+        # ---- attention out projection
+        self._bwd_mm(t.d_ln, dw["o_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESATT),
+                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc)
+        # ---- attention core
+        att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
+        K.attention_backward(t.d_qkv, t.att_scratch, t.d_ln.view(self.B, self.T, Hq, cfg.head_size), att4, a.lse[l], a.qkv[l], Hq, Hkv)
+        K.rope(t.d_qkv, t.d_qkv, self.freqs, Hq, Hkv, backward=True, absmax=self._slot(l, S_DQKV)[0])
+        # ---- QKV projection
+        dqkv2d = t.d_qkv.view(BT, cfg.qkv_channels)
+        self._bwd_mm(t.d_ln, dw["qkv_w"], dw.get("qkv_b"), dqkv2d, t.d_qkv_q if q else None, self._slot(l, S_DQKV),
+                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc)
+
+    # ================================================================================== optimizer
+    def update(self, lr: float, beta1: float = 0.9, beta2: float = 0.95, step: int = 1, eps: float = 1e-8,
+               weight_decay: float = 0.1, grad_clip: float = 1.0, grad_accum: int = 1) -> Dict[str, float]:
+        """Clips by the global norm, applies AdamW to the local shards, returns {loss, loss_1k, norm, z_max, z_mean}."""
+        w, g, o = self.weights, self.grads, self.opt_state
+        g.wait_all()
+        # ---- global gradient norm over the local shards
+        self.norm_partials.zero_()
+        shard_of = {}
+        for name, master, spec, l in w.master_items():
+            gs = g.get_block_shard(l)[spec.name] if l is not None else g.get_nb_shard(spec.name)
+            shard_of[name] = gs
+            gd = gs if gs.device.type == self.device.type else gs.to(self.device, non_blocking=True)
+            K.norm_squared(self.norm_partials, gd)
+        K.deterministic_sum(self.norm_io[0:1], self.norm_partials)
+        if self.comm.world > 1:
+            self.comm.all_reduce(self.norm_io[0:1], "sum").wait()
+        K.norm_finish(self.norm_io, grad_clip)
+        scale = self.norm_io[1:2]
+        # ---- AdamW on every shard
+        w.zero_absmax()
+        seed_base = (self.rng_state * 1000003) & 0x7FFFFFFF
+        for idx, (name, master, spec, l) in enumerate(w.master_items()):
+            gs = shard_of[name]
+            m, v, ms = o.m[name], o.v[name], o.m_scales.get(name)
+            wd = weight_decay if spec.matrix else 0.0
+            am = w._stat(l, spec.name)[0:1] if (l is not None and spec.name in MATRICES and w.quantized) else None
+            self._adam_one(master, gs, m, v, ms, lr, beta1, beta2, step, eps, wd, scale, am, seed_base + idx * 7919, name)
+        w.sync_absmax(recompute=False)
+        w.invalidate()
+        g.end_step()
+        self.rng_state = (self.rng_state * 48271) % 2147483647
+        loss, loss1k = self._reduce_loss(self.B * self.T * grad_accum)
+        ntok = float(self.B * self.T)
+        hs = self.host_scalars
+        hs[0:2].copy_(self.norm_io, non_blocking=True)
+        hs[2:4].copy_(self.lse_stats, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        return {"loss": loss, "loss_1k": loss1k, "norm": float(hs[0]), "z_max": float(hs[2]), "z_mean": float(hs[3]) / ntok}
+
+    def _adam_one(self, master, grad, m, v, ms, lr, b1, b2, step, eps, wd, scale, absmax, seed, name) -> None:
+        """One tensor; host-resident pieces are staged through the device (H2D, update, D2H)."""
+        dev = self.device
+
+        def stage(t):
+            return t if t.device.type == dev.type else t.to(dev, non_blocking=True)
+
+        pm, gm, mm, vm = stage(master), stage(grad), stage(m), stage(v)
+        offset = self.comm.rank * master.numel()
+        n = pm.numel()
+        if n % 8 == 0:
+            K.adamw(pm.view(-1), gm.view(-1), mm.view(-1), vm.view(-1), lr=lr, beta1=b1, beta2=b2, step=step, eps=eps,
+                    weight_decay=wd, grad_scale=scale, absmax=absmax, m_scales=ms, seed=seed, elem_offset=offset)
+        else:
+            raise ValueError(f"parameter shard {name} has {n} elements; shard sizes must be multiples of 8")
+        for src, dst in ((pm, master), (mm, m), (vm, v)):
+            if src is not dst:
+                dst.copy_(src, non_blocking=True)
+
+    # ================================================================================== introspection
+    def get_gradients(self) -> Dict[str, torch.Tensor]:
+        """Local gradient shards by checkpoint name (for tests and the Python API)."""
+        out = {}
+        for name, master, spec, l in self.weights.master_items():
+            out[name] = self.grads.get_block_shard(l)[spec.name] if l is not None else self.grads.get_nb_shard(spec.name)
+        return out

@@ -1,0 +1,439 @@
+"""ZeRO-style state managers: weights (master / work / quantised copies), gradients and AdamW moments.
+
+Everything is sharded by contiguous row blocks of each tensor (dimension 0 must divide by the world size), the
+layout used by the reference (src/utilities/tensor.cpp:113-120).  Capabilities mirror
+
+* LLamaWeightsManager: gather / get / release with a versioned cache, unsharded (all layers resident) and
+  sharded (two block buffers, ZeRO-3) flavours, quantise-before-gather, persistent quantised shards,
+  master weights in pinned host memory (src/models/llama_weights.h:101-226, llama_weights.cpp);
+* the gradient managers: full-replica gradients reduce-scattered on the last micro-step (ZeRO-1) or two block
+  buffers reduce-scattered every micro-step and accumulated into per-layer shards with stochastic rounding
+  (ZeRO-2) (src/training/gradients.cpp, src/models/llama_gradients.cpp);
+* AdamWStateManager: 1/world shards of m and v, optionally in pinned host memory, with block scales for e4m3
+  first moments (src/training/adamw_optimizer.cpp:161-221).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from types import SimpleNamespace
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import TransformerConfig
+from ..ops import kernels as K
+from ..options import LLamaOptions
+from .comm import Communicator, _WorkList
+
+F8_TYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+MATRICES = ("qkv_w", "o_w", "up_w", "down_w")
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: tuple
+    matrix: bool          # 2-D GEMM operand (quantised in fp8 mode, weight decay applies)
+    init_std: float       # 0 -> zeros, <0 -> ones
+
+
+def block_param_specs(cfg: TransformerConfig, opts: LLamaOptions) -> List[ParamSpec]:
+    C, D, QC, L = cfg.hidden_size, cfg.intermediate_size, cfg.qkv_channels, cfg.num_hidden_layers
+    proj_std = 0.0 if opts.init_projections_to_zero else 0.02 / (2 * L) ** 0.5
+    specs = [ParamSpec("ln1_w", (C,), False, -1.0), ParamSpec("qkv_w", (QC, C), True, 0.02)]
+    if cfg.use_qkv_bias:
+        specs.append(ParamSpec("qkv_b", (QC,), False, 0.0))
+    specs += [ParamSpec("o_w", (C, C), True, proj_std), ParamSpec("ln2_w", (C,), False, -1.0),
+              ParamSpec("up_w", (2 * D, C), True, 0.02), ParamSpec("down_w", (C, D), True, proj_std)]
+    return specs
+
+
+def nonblock_param_specs(cfg: TransformerConfig) -> List[ParamSpec]:
+    V, C = cfg.vocab_size, cfg.hidden_size
+    specs = [ParamSpec("embed", (V, C), True, 0.02), ParamSpec("lnf_w", (C,), False, -1.0)]
+    if not cfg.tie_word_embeddings:
+        specs.append(ParamSpec("lm_head", (V, C), True, 0.02))
+    return specs
+
+
+def _alloc(shape, dtype, device, pinned=False):
+    if pinned:
+        return torch.zeros(shape, dtype=dtype, pin_memory=torch.cuda.is_available())
+    return torch.zeros(shape, dtype=dtype, device=device)
+
+
+def _rows(shape, world):
+    if shape[0] % world:
+        raise ValueError(f"dimension 0 of a tensor of shape {shape} does not divide by the world size {world}")
+    return (shape[0] // world,) + tuple(shape[1:])
+
+
+class _Buf:
+    """One work buffer (a full transformer block) with its cache state."""
+
+    def __init__(self):
+        self.t: Dict[str, torch.Tensor] = {}
+        self.layer = -1
+        self.version = -1
+        self.pending = None
+        self.in_use = False
+
+
+class WeightsManager:
+    def __init__(self, cfg: TransformerConfig, opts: LLamaOptions, comm: Communicator, device: torch.device):
+        self.cfg, self.opts, self.comm, self.device = cfg, opts, comm, device
+        self.model_dtype = opts.model_type or cfg.dtype
+        self.matmul_dtype = opts.matmul_dtype()
+        self.master_dtype = opts.master()
+        self.quantized = self.matmul_dtype in F8_TYPES
+        self.sharded = bool(opts.shard_weights)
+        self.block_specs = block_param_specs(cfg, opts)
+        self.nonblock_specs = nonblock_param_specs(cfg)
+        self.version = 0
+        L, w = cfg.num_hidden_layers, comm.world
+        host_master = opts.offload_master and device.type == "cuda"
+
+        def work_dtype(s):
+            return self.matmul_dtype if (s.matrix and s.name in MATRICES) else self.model_dtype
+
+        # ---- work buffers
+        n_bufs = 2 if self.sharded else L
+        self.bufs = [_Buf() for _ in range(n_bufs)]
+        for b in self.bufs:
+            for s in self.block_specs:
+                b.t[s.name] = _alloc(s.shape, work_dtype(s), device)
+        self.nb_work: Dict[str, torch.Tensor] = {}
+        for s in self.nonblock_specs:
+            if self.sharded and s.name == "lm_head":
+                continue                      # embedding and head share one gather buffer under ZeRO-3
+            self.nb_work[s.name] = _alloc(s.shape, self.model_dtype, device)
+        self.nb_state = {"embed": [-1, None], "lnf_w": [-1, None], "emb_slot_holds": None}
+
+        # ---- master shards
+        self.master_blocks: List[Dict[str, torch.Tensor]] = []
+        for l in range(L):
+            d = {}
+            for s in self.block_specs:
+                alias = (not self.sharded) and work_dtype(s) == self.master_dtype and not host_master
+                if alias:
+                    d[s.name] = comm.local_shard(self.bufs[l].t[s.name])
+                else:
+                    d[s.name] = _alloc(_rows(s.shape, w), self.master_dtype, device, pinned=host_master)
+            self.master_blocks.append(d)
+        self.master_nb: Dict[str, torch.Tensor] = {}
+        for s in self.nonblock_specs:
+            alias = (not self.sharded) and self.model_dtype == self.master_dtype and not host_master
+            if alias:
+                self.master_nb[s.name] = comm.local_shard(self.nb_work[s.name])
+            else:
+                self.master_nb[s.name] = _alloc(_rows(s.shape, w), self.master_dtype, device, pinned=host_master)
+
+        # ---- persistent quantised shards (ZeRO-3 option)
+        self.quant_shards: Optional[List[Dict[str, torch.Tensor]]] = None
+        self.quant_version = [-1] * L
+        if self.sharded and opts.persistent_quants and self.quantized:
+            pin = opts.offload_quants and device.type == "cuda"
+            self.quant_shards = [{n: _alloc(_rows(s.shape, w), self.matmul_dtype, device, pinned=pin)
+                                  for s in self.block_specs if (n := s.name) in MATRICES} for _ in range(L)]
+
+        # ---- abs-max / dequant-scale table: [layer, matrix, {absmax, scale}]
+        self.w_stats = torch.zeros(L, len(MATRICES), 2, dtype=torch.float32, device=device)
+        self._staging: Dict[str, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ helpers
+    def _stat(self, l, name):
+        return self.w_stats[l, MATRICES.index(name)]
+
+    def _to_device(self, t: torch.Tensor, key: str) -> torch.Tensor:
+        """Pinned-host tensors are staged through a reusable device buffer (H2D on the current stream)."""
+        if t.device.type == self.device.type:
+            return t
+        st = self._staging.get(key)
+        if st is None or st.shape != t.shape or st.dtype != t.dtype:
+            st = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+            self._staging[key] = st
+        st.copy_(t, non_blocking=True)
+        return st
+
+    def invalidate(self) -> None:
+        """Called after the optimizer changed the master weights: cached work copies are stale."""
+        self.version += 1
+
+    # ------------------------------------------------------------------ blocks
+    def _buf_for(self, l) -> _Buf:
+        return self.bufs[l % 2] if self.sharded else self.bufs[l]
+
+    def gather_block(self, l: int) -> None:
+        buf = self._buf_for(l)
+        if buf.layer == l and buf.version == self.version:
+            return
+        if buf.in_use:
+            raise RuntimeError(f"weight buffer for layer {l} is still in use by layer {buf.layer}")
+        works = []
+        for s in self.block_specs:
+            full = buf.t[s.name]
+            local = self.comm.local_shard(full)
+            master = self.master_blocks[l][s.name]
+            if s.name in MATRICES and self.quantized:
+                st = self._stat(l, s.name)
+                if self.quant_shards is not None:
+                    q = self.quant_shards[l][s.name]
+                    if self.quant_version[l] != self.version:
+                        K.quantize(local, st[1:2], self._to_device(master, "m_" + s.name), st[0:1])
+                        q.copy_(local, non_blocking=True)      # kept (device or pinned host) for later gathers
+                    else:
+                        local.copy_(q, non_blocking=True)
+                else:
+                    K.quantize(local, st[1:2], self._to_device(master, "m_" + s.name), st[0:1])
+            elif master.data_ptr() != local.data_ptr():
+                local.copy_(self._to_device(master, "m_" + s.name))
+            if self.comm.world > 1:
+                works.append(self.comm.all_gather(full, local))
+        if self.quant_shards is not None:
+            self.quant_version[l] = self.version
+        buf.pending = _WorkList(works)
+        buf.layer, buf.version = l, self.version
+
+    def get_block(self, l: int) -> SimpleNamespace:
+        buf = self._buf_for(l)
+        if buf.layer != l or buf.version != self.version:
+            raise RuntimeError(f"gathered data is not for the requested layer {l} (have {buf.layer})")
+        if buf.pending is not None:
+            buf.pending.wait()
+            buf.pending = None
+        buf.in_use = True
+        ns = SimpleNamespace(**buf.t)
+        ns.scales = {n: self._stat(l, n)[1:2] for n in MATRICES} if self.quantized else {n: None for n in MATRICES}
+        if not hasattr(ns, "qkv_b"):
+            ns.qkv_b = None
+        return ns
+
+    def release_block(self, l: int) -> None:
+        self._buf_for(l).in_use = False
+
+    # ------------------------------------------------------------------ non-block tensors
+    def _gather_nb(self, name: str, slot: str) -> torch.Tensor:
+        full = self.nb_work[slot]
+        st = self.nb_state.setdefault(slot, [-1, None])
+        holds = self.nb_state.get("holds_" + slot, slot)
+        if st[0] == self.version and holds == name:
+            return full
+        local = self.comm.local_shard(full)
+        master = self.master_nb[name]
+        if master.data_ptr() != local.data_ptr():
+            local.copy_(self._to_device(master, "nb_" + name))
+        if self.comm.world > 1:
+            st[1] = self.comm.all_gather(full, local)
+        st[0] = self.version
+        self.nb_state["holds_" + slot] = name
+        return full
+
+    def _wait_nb(self, slot):
+        st = self.nb_state.get(slot)
+        if st and st[1] is not None:
+            st[1].wait()
+            st[1] = None
+
+    def get_embeddings(self) -> torch.Tensor:
+        t = self._gather_nb("embed", "embed")
+        self._wait_nb("embed")
+        return t
+
+    def get_head(self) -> torch.Tensor:
+        if self.cfg.tie_word_embeddings:
+            return self.get_embeddings()
+        slot = "embed" if self.sharded else "lm_head"
+        t = self._gather_nb("lm_head", slot)
+        self._wait_nb(slot)
+        return t
+
+    def get_lnf(self) -> torch.Tensor:
+        t = self._gather_nb("lnf_w", "lnf_w")
+        self._wait_nb("lnf_w")
+        return t
+
+    # ------------------------------------------------------------------ abs-max bookkeeping
+    def zero_absmax(self) -> None:
+        self.w_stats[:, :, 0].zero_()
+
+    def sync_absmax(self, recompute: bool) -> None:
+        """All ranks must quantise a matrix with the same scale: max-reduce the per-shard abs-max values."""
+        if not self.quantized:
+            return
+        if recompute:
+            self.zero_absmax()
+            for l in range(self.cfg.num_hidden_layers):
+                for n in MATRICES:
+                    K.abs_max(self._stat(l, n)[0:1], self._to_device(self.master_blocks[l][n], "m_" + n))
+        if self.comm.world > 1:
+            am = self.w_stats[:, :, 0].contiguous()
+            self.comm.all_reduce(am, "max").wait()
+            self.w_stats[:, :, 0].copy_(am)
+
+    # ------------------------------------------------------------------ iteration (checkpoint / optimizer)
+    def master_items(self):
+        """Yields (checkpoint name, master shard, spec, layer or None) for every parameter."""
+        for l, d in enumerate(self.master_blocks):
+            for s in self.block_specs:
+                yield f"layers.{l}.{s.name}", d[s.name], s, l
+        for s in self.nonblock_specs:
+            yield s.name, self.master_nb[s.name], s, None
+
+
+class GradientManager:
+    """Full or sharded gradient storage plus the reduction protocol
+    start_micro_step -> get_block_full -> notify_block -> end_micro_step -> get_block_shard."""
+
+    def __init__(self, cfg, opts, comm: Communicator, device, weights: WeightsManager, seed: int = 42):
+        self.cfg, self.opts, self.comm, self.device = cfg, opts, comm, device
+        self.dtype = weights.model_dtype
+        self.block_specs, self.nonblock_specs = weights.block_specs, weights.nonblock_specs
+        self.sharded = bool(opts.shard_gradients)
+        self.seed, self.step = seed, 0
+        L, w = cfg.num_hidden_layers, comm.world
+        host = opts.offload_grads and device.type == "cuda" and self.sharded
+        self.micro_step, self.last = 0, False
+        if self.sharded:
+            self.bufs = [{s.name: _alloc(s.shape, self.dtype, device) for s in self.block_specs} for _ in range(2)]
+            self.buf_state = [{"layer": -1, "pending": None, "needs_acc": False} for _ in range(2)]
+            self.shards = [{s.name: _alloc(_rows(s.shape, w), self.dtype, device, pinned=host) for s in self.block_specs}
+                           for _ in range(L)]
+        else:
+            self.full = [{s.name: _alloc(s.shape, self.dtype, device) for s in self.block_specs} for _ in range(L)]
+            self.pending: List = [None] * L
+        self.nb_full = {s.name: _alloc(s.shape, self.dtype, device) for s in self.nonblock_specs}
+        self.nb_pending: Dict[str, object] = {}
+        self._stage: Dict[str, torch.Tensor] = {}
+
+    # -- micro-step protocol
+    def start_micro_step(self, micro_step: int, total: int) -> None:
+        self.micro_step, self.last = micro_step, micro_step == total - 1
+        if micro_step == 0:
+            for s in self.nonblock_specs:
+                if not s.matrix:
+                    self.nb_full[s.name].zero_()
+
+    def get_block_full(self, l: int):
+        """Returns (tensors, accumulate): where layer l's backward writes, and whether it adds to the content."""
+        if not self.sharded:
+            g = self.full[l]
+            acc = self.micro_step > 0
+        else:
+            i = l % 2
+            self._flush(i)
+            g = self.bufs[i]
+            self.buf_state[i]["layer"] = l
+            acc = False
+        if not acc:
+            for s in self.block_specs:
+                if not s.matrix:
+                    g[s.name].zero_()          # vectors are always accumulated into; matrices are overwritten
+        return g, acc
+
+    def notify_block(self, l: int) -> None:
+        if not self.sharded:
+            if self.last and self.comm.world > 1:
+                self.pending[l] = _WorkList([self.comm.reduce_scatter_avg(t) for t in self.full[l].values()])
+            return
+        i = l % 2
+        st = self.buf_state[i]
+        if self.comm.world > 1:
+            st["pending"] = _WorkList([self.comm.reduce_scatter_avg(t) for t in self.bufs[i].values()])
+        st["needs_acc"] = True
+
+    def _flush(self, i: int) -> None:
+        """Accumulates the reduced local slice of buffer i into the persistent shard of its layer."""
+        st = self.buf_state[i]
+        if not st["needs_acc"]:
+            return
+        if st["pending"] is not None:
+            st["pending"].wait()
+            st["pending"] = None
+        l = st["layer"]
+        for k, s in enumerate(self.block_specs):
+            src = self.comm.local_shard(self.bufs[i][s.name])
+            dst = self.shards[l][s.name]
+            on_dev = dst.device.type == self.device.type
+            if self.micro_step_of_layer_first(l):
+                dst.copy_(src, non_blocking=True)
+            else:
+                d = dst if on_dev else self._staged(dst, s.name)
+                seed = (self.seed * 7919 + self.step * 104729 + l * 131 + k * 17 + self._acc_count[l]) & 0x7FFFFFFF
+                if d.numel() % 8 == 0 and d.dtype in (torch.bfloat16, torch.float32):
+                    K.vector_add_sr(d, d, src, 1.0, seed)
+                else:
+                    d.add_(src)
+                if not on_dev:
+                    dst.copy_(d, non_blocking=True)
+        self._acc_count[l] += 1
+        st["needs_acc"] = False
+
+    def _staged(self, host_t, key):
+        st = self._stage.get(key)
+        if st is None or st.shape != host_t.shape:
+            st = torch.empty(host_t.shape, dtype=host_t.dtype, device=self.device)
+            self._stage[key] = st
+        st.copy_(host_t, non_blocking=True)
+        return st
+
+    def micro_step_of_layer_first(self, l: int) -> bool:
+        return self._acc_count[l] == 0
+
+    def begin_step(self) -> None:
+        self._acc_count = [0] * self.cfg.num_hidden_layers
+
+    def notify_non_block(self, name: str) -> None:
+        if self.last and self.comm.world > 1:
+            self.nb_pending[name] = self.comm.reduce_scatter_avg(self.nb_full[name])
+
+    def end_micro_step(self) -> None:
+        if self.sharded:
+            self._flush(0)
+            self._flush(1)
+
+    def end_step(self) -> None:
+        self.step += 1
+
+    # -- optimizer side
+    def wait_all(self) -> None:
+        if not self.sharded:
+            for l, p in enumerate(self.pending):
+                if p is not None:
+                    p.wait()
+                    self.pending[l] = None
+        for n in list(self.nb_pending):
+            self.nb_pending.pop(n).wait()
+
+    def get_block_shard(self, l: int) -> Dict[str, torch.Tensor]:
+        if self.sharded:
+            return self.shards[l]
+        return {n: self.comm.local_shard(t) for n, t in self.full[l].items()}
+
+    def get_nb_shard(self, name: str) -> torch.Tensor:
+        return self.comm.local_shard(self.nb_full[name])
+
+
+class OptimizerStateManager:
+    """AdamW first / second moments as 1/world row shards of every parameter."""
+
+    def __init__(self, cfg, opts: LLamaOptions, comm, device, weights: WeightsManager):
+        self.opts, self.device = opts, device
+        self.m_dtype, self.v_dtype = opts.momentum_type, opts.variance_type
+        self.m: Dict[str, torch.Tensor] = {}
+        self.v: Dict[str, torch.Tensor] = {}
+        self.m_scales: Dict[str, torch.Tensor] = {}
+        pin_m = opts.offload_opt_m and device.type == "cuda"
+        pin_v = opts.offload_opt_v and device.type == "cuda"
+        for name, master, spec, l in weights.master_items():
+            self.m[name] = _alloc(master.shape, self.m_dtype, device, pinned=pin_m)
+            self.v[name] = _alloc(master.shape, self.v_dtype, device, pinned=pin_v)
+            if self.m_dtype in F8_TYPES:
+                n = master.numel()
+                if n % 128:
+                    raise ValueError(f"e4m3 momentum needs shard sizes divisible by 128 (tensor {name} has {n})")
+                # scale blocks are 128 consecutive elements of the flat shard, independent of the world size
+                self.m_scales[name] = torch.ones(n // 128, dtype=torch.float32, device=device)
+
+    def items(self):
+        for name in self.m:
+            yield name, self.m[name], self.v[name], self.m_scales.get(name)
