@@ -1,0 +1,196 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput (tokens/s, whole job) of Qwen2.5-7B-arch with e4m3 matmuls.
+
+    python bench.py --gpus N --steps K --warmup W            (N == 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W               (N > 1, one rank per GPU)
+
+Config (weak scaling, fixed per-GPU work): per-GPU batch 8 x seq 2048 uniform-random tokens, random-init bf16
+master weights, e4m3 matmuls, bf16 AdamW moments, recompute-swiglu; with N > 1 weights, gradients and optimizer
+state are sharded (all-gather before each layer).  A step is forward + backward + clip + AdamW.
+
+Two measurements are reported in one JSON line:
+* ``value``  - device time (CUDA events) of K steps fed from device-resident token tensors, max over ranks;
+* ``e2e``    - the same K steps through the public API (``LLMQTrainer.step`` / ``update``) with, every step, the
+  host->device copy of that step's tokens from pinned memory and the device->host read of loss and norm.
+Every step streams far more than the 126 MB L2 (weights + activations are tens of GB), so no explicit flush is needed.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOKS_PER_GPU = None       # the reference publishes no B200 number
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self):
+        sm = sorted(int(float(s[0])) for s in self.samples if s and s[0].replace(".", "").isdigit())
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            for n, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mx = max((int(float(s[1])) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()), default=None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The unmodified reference cannot be installed offline: its CMake build downloads nlohmann-json,
+    cudnn-frontend, CLI11, nanobind, fmt and Catch2 with FetchContent (CMakeLists.txt:22-70)."""
+    print(json.dumps({"impl": "reference", "unavailable": "reference build needs network: CMake FetchContent of json/cudnn-frontend/CLI11/nanobind/fmt/Catch2 fails offline (pip install --no-index --no-deps exited 1)"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="Qwen2.5-7B")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--grad-accum", type=int, default=1)
+    ap.add_argument("--matmul-dtype", default="e4m3")
+    ap.add_argument("--lmhead-chunks", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (the result is then not the headline metric)")
+    ap.add_argument("--collectives", default="auto")
+    ap.add_argument("--zero-level", type=int, default=0, help="0 = pick from --gpus (1 GPU: unsharded, else 3)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    from llmq_b200 import api
+    from llmq_b200.config import create_config_from_name
+    from llmq_b200.ops import lib as L
+    from llmq_b200.options import LLamaOptions
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py --gpus {args.gpus} must be started with torch.distributed.run (one rank per GPU)", file=sys.stderr)
+            return 2
+    cfg = create_config_from_name(args.model, "bf16")
+    if args.layers:
+        cfg = cfg.replace(num_hidden_layers=args.layers)
+    opts = LLamaOptions(recompute_swiglu=True, matmul_type=args.matmul_dtype, momentum_type="bf16", variance_type="bf16",
+                        lmhead_chunks=args.lmhead_chunks, collectives=args.collectives)
+    zl = args.zero_level or (1 if args.gpus == 1 else 3)
+    opts.set_zero_level(zl)
+    B, T, GA = args.batch, args.seq_len, args.grad_accum
+    trainer = api.LLMQTrainer(ngpu=args.gpus, config=cfg, options=opts, batch_size=B, seq_len=T, grad_accum=GA)
+    trainer.init_weights()
+    dev, comm, rank = trainer.device, trainer.comm, trainer.rank
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_batches = 4
+    host_tokens = [torch.randint(0, cfg.vocab_size, (B, T + 1), generator=gen, dtype=torch.int32) for _ in range(n_batches)]
+    host_in = [t[:, :-1].contiguous().pin_memory() for t in host_tokens]
+    host_tg = [t[:, 1:].contiguous().pin_memory() for t in host_tokens]
+    dev_in = [t.to(dev) for t in host_in]
+    dev_tg = [t.to(dev) for t in host_tg]
+    lr = 1e-5
+
+    def run_step(i, step_no, from_host):
+        for j in range(GA):
+            k = (i * GA + j) % n_batches
+            if from_host:
+                trainer.step(host_in[k], host_tg[k])
+            else:
+                trainer.step(dev_in[k], dev_tg[k])
+        return trainer.update(lr, 0.9, 0.95, step_no, 0.1, 1.0)
+
+    def sync_all():
+        comm.barrier()
+        torch.cuda.synchronize()
+
+    step_no = 0
+    for i in range(args.warmup):
+        step_no += 1
+        res = run_step(i, step_no, False)
+    sync_all()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    # ---- device-timed region
+    l0 = L.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for i in range(args.steps):
+        step_no += 1
+        res = run_step(i, step_no, False)
+    e1.record()
+    sync_all()
+    launches = L.launch_count - l0
+    ms_dev = e0.elapsed_time(e1)
+    # ---- end-to-end region through the public API with pinned-host inputs and host-read results
+    sync_all()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step_no += 1
+        res = run_step(i, step_no, True)
+        loss_host = res["loss"]
+    sync_all()
+    ms_e2e = (time.perf_counter() - t0) * 1e3
+    sampler.stop_flag.set()
+    sampler.join(timeout=3)
+    t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=dev)
+    if comm.world > 1:
+        comm.all_reduce(t, "max").wait()
+    ms_dev, ms_e2e = float(t[0]), float(t[1])
+    from llmq_b200.ops import kernels as K
+    K.check_status(dev)
+    tokens = B * T * GA * comm.world * args.steps
+    value = tokens / (ms_dev / 1e3)
+    e2e = tokens / (ms_e2e / 1e3)
+    if rank == 0:
+        out = {
+            "metric": "train tokens/sec/box Qwen2.5-7B e4m3", "value": value, "unit": "tokens/s", "n_gpus": comm.world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": (value / (BASELINE_TOKS_PER_GPU * comm.world)) if BASELINE_TOKS_PER_GPU else None,
+            "dtype": "bf16 model / e4m3 matmul", "data": "synthetic uniform-random tokens, random-init weights",
+            "config": {"model": args.model + ("" if not args.layers else f"[layers={args.layers}]"), "global_batch": B * comm.world * GA,
+                       "seq_len": T, "per_gpu_batch": B, "grad_accum": GA,
+                       "parallelism": f"dp{comm.world}" + ("" if comm.world == 1 else f"-zero{zl}"), "recompute": "swiglu",
+                       "opt_moments": "bf16", "lmhead_chunks": args.lmhead_chunks,
+                       "l2": "every step streams >60 GB of weights+activations (>> 126 MB L2), no flush needed"},
+            "clocks": sampler.summary(),
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": 2 * B * T * 4 * GA,
+                    "d2h_bytes_per_step": 32, "timing": "host wall clock around K steps incl. pinned H2D token copies and D2H loss/norm"},
+            "gpu_launches": launches, "loss": loss_host, "impl": "ours",
+        }
+        print(json.dumps(out))
+    trainer.comm.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -190,7 +190,8 @@ class LlamaModel:
         """inputs: int32 (B, T) on any device.  Activations stay in the run state for ``backward``."""
         cfg, a, w = self.cfg, self.acts, self.weights
         L = cfg.num_hidden_layers
-        self.inputs.copy_(inputs.reshape(self.B, self.T), non_blocking=True)
+        if inputs is not None:                    # None: the caller already placed the tokens in self.inputs
+            self.inputs.copy_(inputs.reshape(self.B, self.T), non_blocking=True)
         K.encoder_forward(a.x[0], self.inputs, w.get_embeddings())
         self.stats.zero_()
         w.gather_block(0)
@@ -283,7 +284,8 @@ class LlamaModel:
                  micro_step: int = 0) -> None:
         cfg, a, t, w, g = self.cfg, self.acts, self.tmp, self.weights, self.grads
         L, C = cfg.num_hidden_layers, cfg.hidden_size
-        self.targets.copy_(targets.reshape(self.B, self.T), non_blocking=True)
+        if targets is not None:
+            self.targets.copy_(targets.reshape(self.B, self.T), non_blocking=True)
         if micro_step == 0:
             g.begin_step()
             self.losses.zero_()

@@ -85,6 +85,13 @@ class KernelError(RuntimeError):
     pass
 
 
+# Number of device kernels launched through this module (each entry point knows how many it launches).
+_EXTRA_LAUNCHES = {"rmsnorm_backward": 1, "bias_backward": 1, "attention_backward": 2}
+launch_count = 0
+
+
 def check(rc: int, what: str):
+    global launch_count
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
+    launch_count += 1 + _EXTRA_LAUNCHES.get(what, 0)
