@@ -208,3 +208,53 @@ extern "C" int llmq_rmsnorm_backward(void* dinp, void* dweight, float* scratch, 
     if (dtype == 3) return launch_bwd<float>(dinp, dweight, scratch, dout, inp, weight, rstd, rows, C, absmax, accumulate_dweight, num_blocks, stream);
     return -10;
 }
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate (see noalloc.h).
+//
+// The weight-gradient partials live in a file-scope device array instead of a caller-provided buffer.
+// Every GPU that loads this library keeps the array resident until the process exits.
+#include "noalloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_noalloc_norm_scratch[LLMQ_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+std::mutex g_noalloc_mutex;
+float* g_noalloc_scratch_ptr[64] = {};     // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int llmq_rmsnorm_backward_noalloc(void* dinp, void* dweight, const void* dout, const void* inp,
+                                             const void* weight, const float* rstd, int rows, int C, int dtype,
+                                             float* absmax, int accumulate_dweight, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (C <= 0 || C > LLMQ_NOALLOC_MAX_C) return LLMQ_NOALLOC_ERR_TOO_LARGE;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= 64) return LLMQ_NOALLOC_ERR_DEVICE;
+    float* scratch = nullptr;
+    int sms = 0;
+    {
+        // One-time set-up per device, with that device current.  In host code the array's name is only a
+        // handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress.
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_scratch_ptr[dev]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_noalloc_norm_scratch);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            g_noalloc_scratch_ptr[dev] = static_cast<float*>(p);
+        }
+        scratch = g_noalloc_scratch_ptr[dev];
+    }
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    // as many row-walking CTAs as the array can hold partial rows for, at most two per SM
+    long long blocks = 2LL * sms;
+    const long long fit = LLMQ_NOALLOC_SCRATCH_FLOATS / C;
+    if (blocks > fit) blocks = fit;
+    if (blocks < 1) return LLMQ_NOALLOC_ERR_TOO_LARGE;
+    if (dtype == 0) return launch_bwd<bf16>(dinp, dweight, scratch, dout, inp, weight, rstd, rows, C, absmax, accumulate_dweight, static_cast<int>(blocks), stream);
+    if (dtype == 3) return launch_bwd<float>(dinp, dweight, scratch, dout, inp, weight, rstd, rows, C, absmax, accumulate_dweight, static_cast<int>(blocks), stream);
+    return -10;
+}
