@@ -1,0 +1,111 @@
+// Pieces shared by the one-CTA and the two-CTA tcgen05 GEMM kernels: launch parameters and the epilogue that
+// moves one accumulator row block from tensor memory to global memory.
+#pragma once
+#include "ptx_sm100.cuh"
+#include "common.cuh"
+
+struct GemmParams {
+    int M, N, K;
+    int elem_bytes;        // 1 or 2
+    int a_mn_major, b_mn_major;
+    int a_fmt, b_fmt;      // instruction-descriptor format codes
+    void* C;
+    long long ldc;         // elements
+    int c_dtype;           // 0 = bf16, 1 = fp32
+    int accumulate;
+    const void* bias;      // bf16 or fp32 (bias_dtype) or null, indexed by N
+    int bias_dtype;
+    const float* scale_a;  // optional dequant factors
+    const float* scale_b;
+    float alpha;
+    float* absmax_out;     // optional
+    unsigned int* status;  // error word
+};
+
+// Each lane of the calling warp owns one accumulator row (TMEM lane); `t_row` addresses column 0 of that row
+// block.  Applies alpha and bias, optionally adds the previous C, stores bf16 or fp32, tracks abs-max.
+// The TMEM loads are warp-collective, so all lanes run the loop; only the stores are predicated on the row.
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_row, int row, int col_base, int ncols,
+                                              float alpha, float& tmax) {
+    using namespace sm100;
+    const bool row_ok = row < p.M;
+#pragma unroll 1
+    for (int c = 0; c < ncols; c += 32) {
+        const int col0 = col_base + c;
+        if (col0 >= p.N) break;                    // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+        if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                int cj = col0 + j;
+                if (cj < p.N) {
+                    v[j] += p.bias_dtype == 0 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[cj])
+                                              : static_cast<const float*>(p.bias)[cj];
+                }
+            }
+        }
+        if (row_ok) {
+            const bool full = (col0 + 32 <= p.N);
+            if (p.c_dtype == 0) {
+                __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+                if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 o;
+                        if (p.accumulate) {
+                            uint4 old = *reinterpret_cast<const uint4*>(cp + g * 8);
+                            const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float2 f = __bfloat1622float2(oh[j]);
+                                v[g * 8 + 2 * j] += f.x; v[g * 8 + 2 * j + 1] += f.y;
+                            }
+                        }
+                        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+                        *reinterpret_cast<uint4*>(cp + g * 8) = o;
+                    }
+                } else {
+                    for (int j = 0; j < 32; ++j) {
+                        if (col0 + j < p.N) {
+                            if (p.accumulate) v[j] += __bfloat162float(cp[j]);
+                            cp[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                }
+            } else {
+                float* cp = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+                if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                        if (p.accumulate) {
+                            float4 old = *reinterpret_cast<const float4*>(cp + g * 4);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            v[g * 4] = o.x; v[g * 4 + 1] = o.y; v[g * 4 + 2] = o.z; v[g * 4 + 3] = o.w;
+                        }
+                        *reinterpret_cast<float4*>(cp + g * 4) = o;
+                    }
+                } else {
+                    for (int j = 0; j < 32; ++j) {
+                        if (col0 + j < p.N) {
+                            if (p.accumulate) v[j] += cp[j];
+                            cp[j] = v[j];
+                        }
+                    }
+                }
+            }
+            if (p.absmax_out) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N) tmax = fmaxf(tmax, fabsf(v[j]));
+            }
+        }
+    }
+}

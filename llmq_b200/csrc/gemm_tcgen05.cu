@@ -21,6 +21,7 @@
 #include "ptx_sm100.cuh"
 #include "api.h"
 #include "common.cuh"
+#include "gemm_common.cuh"
 
 using namespace sm100;
 
@@ -37,23 +38,6 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;            // two 256-column accumulators
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-struct GemmParams {
-    int M, N, K;
-    int elem_bytes;        // 1 or 2
-    int a_mn_major, b_mn_major;
-    int a_fmt, b_fmt;      // instruction-descriptor format codes
-    void* C;
-    long long ldc;         // elements
-    int c_dtype;           // 0 = bf16, 1 = fp32
-    int accumulate;
-    const void* bias;      // bf16 or fp32 (bias_dtype) or null, indexed by N
-    int bias_dtype;
-    const float* scale_a;  // optional dequant factors
-    const float* scale_b;
-    float alpha;
-    float* absmax_out;     // optional
-    unsigned int* status;  // error word
-};
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
     // Grouped rasterisation: 16 row tiles share every column tile while it is hot in L2.
@@ -196,88 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { if (lane == 0) atomicOr(p.status, kErrTmemFull); ok = false; break; }
             tc_fence_after_sync();
-            const int row = tm * BM + q * 32 + lane;
-            const bool row_ok = row < p.M;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                const int col0 = tn * BN + c;
-                if (col0 >= p.N) break;                    // uniform across the warp
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(t_row + c, r);
-                tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
-                if (p.bias) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        int cj = col0 + j;
-                        if (cj < p.N) {
-                            v[j] += p.bias_dtype == 0 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[cj])
-                                                      : static_cast<const float*>(p.bias)[cj];
-                        }
-                    }
-                }
-                if (row_ok) {
-                    const bool full = (col0 + 32 <= p.N);
-                    if (p.c_dtype == 0) {
-                        __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-                        if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                uint4 o;
-                                if (p.accumulate) {
-                                    uint4 old = *reinterpret_cast<const uint4*>(cp + g * 8);
-                                    const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        float2 f = __bfloat1622float2(oh[j]);
-                                        v[g * 8 + 2 * j] += f.x; v[g * 8 + 2 * j + 1] += f.y;
-                                    }
-                                }
-                                __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
-                                *reinterpret_cast<uint4*>(cp + g * 8) = o;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) {
-                                if (col0 + j < p.N) {
-                                    if (p.accumulate) v[j] += __bfloat162float(cp[j]);
-                                    cp[j] = __float2bfloat16_rn(v[j]);
-                                }
-                            }
-                        }
-                    } else {
-                        float* cp = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-                        if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
-#pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                                if (p.accumulate) {
-                                    float4 old = *reinterpret_cast<const float4*>(cp + g * 4);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                    v[g * 4] = o.x; v[g * 4 + 1] = o.y; v[g * 4 + 2] = o.z; v[g * 4 + 3] = o.w;
-                                }
-                                *reinterpret_cast<float4*>(cp + g * 4) = o;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) {
-                                if (col0 + j < p.N) {
-                                    if (p.accumulate) v[j] += cp[j];
-                                    cp[j] = v[j];
-                                }
-                            }
-                        }
-                    }
-                    if (p.absmax_out) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) tmax = fmaxf(tmax, fabsf(v[j]));
-                    }
-                }
-            }
+            epilogue_rows(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, tm * BM + q * 32 + lane, tn * BN, BN, alpha, tmax);
             tc_fence_before_sync();
             mbar_arrive(tempty_bar(acc));                  // 128 arrivals release the accumulator
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -330,6 +233,12 @@ int llmq_encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, long
     return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream);
+
+// Tile-shape selection: 0 = automatic, 1 = force the one-CTA kernel, 2 = force the CTA-pair kernel.
+static int g_gemm_mode = 0;
+extern "C" void llmq_gemm_set_mode(int mode) { g_gemm_mode = mode; }
+
 extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias,
                          int M, int N, int K,
                          int ab_dtype,            // 0 bf16, 1 e4m3, 2 e5m2 (A), B shares the width
@@ -352,7 +261,9 @@ extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias
     if (!a_mn_major) rc = llmq_encode_tmap_2d(&ta, A, eb, M, K, lda, BM);
     else             rc = llmq_encode_tmap_2d(&ta, A, eb, K, M, lda, bk);
     if (rc) return rc;
-    if (!b_mn_major) rc = llmq_encode_tmap_2d(&tb, B, eb, N, K, ldb, BN);
+    // The CTA-pair kernel stages 128 rows of B per CTA; the one-CTA kernel stages all 256.
+    const bool pair_kernel = g_gemm_mode == 2 || (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32);
+    if (!b_mn_major) rc = llmq_encode_tmap_2d(&tb, B, eb, N, K, ldb, pair_kernel ? 128 : BN);
     else             rc = llmq_encode_tmap_2d(&tb, B, eb, K, N, ldb, bk);
     if (rc) return rc;
 
@@ -365,6 +276,8 @@ extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.scale_a = scale_a; p.scale_b = scale_b; p.alpha = alpha;
     p.absmax_out = absmax_out; p.status = status;
+
+    if (pair_kernel) return llmq_gemm_2cta_launch(ta, tb, p, num_sms, stream);
 
     static bool attr_set[64] = {};          // the attribute is per device
     int dev = 0;

@@ -1,0 +1,217 @@
+// Two-CTA variant of the tcgen05 GEMM: a cluster of two CTAs on neighbouring SMs computes one 256x256 tile.
+//
+// Each CTA stages its own 128 rows of A and only half of the 256 rows of B per K step; tcgen05.mma with
+// cta_group::2 reads both halves of B from the two shared memories, so per multiply-accumulate the pair moves
+// a third less data out of L2 and shared memory than two independent 128x256 CTAs.  That is what lifts the
+// kernel from the shared-memory / L2 limit of the one-CTA version towards the tensor-core limit.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer (both CTAs; completion bytes of both are credited to the
+// leader's "full" barrier), warp 1 = MMA issuer (leader CTA only), warps 2-5 = epilogue of the CTA's own
+// 128x256 accumulator.  Stage release and accumulator-ready signals go to both CTAs with two tcgen05.commit
+// each; the peer's epilogue releases accumulators with a remote mbarrier arrive.  Every wait is bounded.
+#include "ptx_sm100.cuh"
+#include "api.h"
+#include "common.cuh"
+#include "gemm_common.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;              // rows per CTA (256 per pair)
+constexpr int BN = 256;
+constexpr int BN_HALF = 128;         // rows of B staged by each CTA
+constexpr int ROW_BYTES = 128;
+constexpr int STAGES = 6;
+constexpr int A_STAGE_BYTES = BM * ROW_BYTES;        // 16 KiB
+constexpr int B_STAGE_BYTES = BN_HALF * ROW_BYTES;   // 16 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    constexpr int G = 8;             // 8 pair-rows (2048 rows of A) share each B tile while it is hot in L2
+    int per_group = G * tiles_n;
+    int group = t / per_group;
+    int first_m = group * G;
+    int gsz = min(tiles_m - first_m, G);
+    int r = t - group * per_group;
+    tm = first_m + (r % gsz);
+    tn = r / gsz;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    // bars[0..S) full (used in the leader), [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty (leader)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();           // 0 = leader
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int bk = ROW_BYTES / p.elem_bytes;
+    const int k_iters = (p.K + bk - 1) / bk;
+    const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 256); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) {                                   // same warp index in both CTAs, as the pair allocation wants
+        tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_arrive();                                  // barrier inits of both CTAs are visible cluster-wide
+    cluster_wait();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            int stage = 0; uint32_t phase = 0;
+            const int mn_chunk = ROW_BYTES / p.elem_bytes;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+                int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+                const int row0 = (tm * 2 + static_cast<int>(rank)) * BM;               // this CTA's rows of A / C
+                const int brow0 = tn * BN + static_cast<int>(rank) * BN_HALF;          // this CTA's rows of B
+                for (int k = 0; k < k_iters; ++k) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrEmptyWait); ok = false; break; }
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    const uint32_t fb = map_to_cta(full_bar(stage), 0);                 // the leader's barrier
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);     // bytes of both CTAs
+                    if (!p.a_mn_major) {
+                        tma_load_2d_pair(sa, &tmap_a, fb, k * bk, row0);
+                    } else {
+                        int nbox = BM * p.elem_bytes / ROW_BYTES;
+                        for (int b = 0; b < nbox; ++b)
+                            tma_load_2d_pair(sa + b * (A_STAGE_BYTES / nbox), &tmap_a, fb, row0 + b * mn_chunk, k * bk);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_2d_pair(sb, &tmap_b, fb, k * bk, brow0);
+                    } else {
+                        int nbox = BN_HALF * p.elem_bytes / ROW_BYTES;
+                        for (int b = 0; b < nbox; ++b)
+                            tma_load_2d_pair(sb + b * (B_STAGE_BYTES / nbox), &tmap_b, fb, brow0 + b * mn_chunk, k * bk);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_instr_desc(p.a_fmt, p.b_fmt, p.a_mn_major, p.b_mn_major, 2 * BM, BN);
+            const int mma_k = 32 / p.elem_bytes;
+            const uint32_t box_bytes = static_cast<uint32_t>(bk) * ROW_BYTES;
+            const uint32_t a_step = p.a_mn_major ? mma_k * ROW_BYTES : 32;
+            const uint32_t b_step = p.b_mn_major ? mma_k * ROW_BYTES : 32;
+            const uint32_t a_lbo = p.a_mn_major ? box_bytes : 16;
+            const uint32_t b_lbo = p.b_mn_major ? box_bytes : 16;
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrTmemEmpty); ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int k = 0; k < k_iters; ++k) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicOr(p.status, kErrFullWait); ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint64_t ad = make_smem_desc(sa + j * a_step, a_lbo, 1024);
+                        uint64_t bd = make_smem_desc(sb + j * b_step, b_lbo, 1024);
+                        uint32_t accum = (k > 0 || j > 0) ? 1u : 0u;
+                        if (p.elem_bytes == 2) mma_f16_pair(d_tmem, ad, bd, idesc, accum);
+                        else                   mma_f8_pair(d_tmem, ad, bd, idesc, accum);
+                    }
+                    mma_commit_pair(empty_bar(stage));                       // stage free in this CTA ...
+                    mma_commit_pair(map_to_cta(empty_bar(stage), 1));        // ... and in the peer
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                mma_commit_pair(tfull_bar(acc));
+                mma_commit_pair(map_to_cta(tfull_bar(acc), 1));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps, both CTAs)
+        const int q = warp & 3;
+        float alpha = p.alpha;
+        if (p.scale_a) alpha *= *p.scale_a;
+        if (p.scale_b) alpha *= *p.scale_b;
+        float tmax = 0.f;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+            int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { if (lane == 0) atomicOr(p.status, kErrTmemFull); ok = false; break; }
+            tc_fence_after_sync();
+            __syncwarp();
+            const int row = (tm * 2 + static_cast<int>(rank)) * BM + q * 32 + lane;
+            epilogue_rows(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, row, tn * BN, BN, alpha, tmax);
+            tc_fence_before_sync();
+            mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));            // 2 x 128 arrivals at the leader
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (p.absmax_out) {
+            tmax = warp_reduce_max(tmax);
+            if (lane == 0 && tmax > 0.f) atomic_max_float(p.absmax_out, tmax);
+        }
+    }
+
+    // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+    tc_fence_before_sync();
+    __syncthreads();
+    __syncwarp();
+    cluster_arrive();
+    cluster_wait();
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+}  // namespace
+
+// Same contract as llmq_gemm (which dispatches here for problems with at least one full 256-row tile).
+int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        attr_set[dev & 63] = true;
+    }
+    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+    int pairs = num_sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    gemm_tcgen05_2cta_kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,159 @@
+"""Kernel micro-benchmarks: device-timed (CUDA events), warmed up, L2 flushed between iterations.
+
+    python -m llmq_b200.ops.bench gemm --m 16384 --n 37888 --k 3584 --dtype fp8 [--a-mn] [--b-mn] [--mode 0|1|2]
+    python -m llmq_b200.ops.bench attention --b 8 --t 2048 --hq 28 --hkv 4 --hs 128
+    python -m llmq_b200.ops.bench elementwise --rows 16384 --c 3584 --d 18944
+    python -m llmq_b200.ops.bench adamw --n 134217728
+
+Prints achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` is found at the repository root, the
+fraction of the measured cuBLAS bf16 / copy-bandwidth peak.  ``--iters 1 --no-flush`` gives a run that is
+convenient to capture under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import kernels as K
+from . import lib as L
+
+DEV = "cuda"
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class Timer:
+    def __init__(self, iters, warmup, flush):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if flush else None
+
+    def time(self, fn):
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(self.iters):
+            if self.flush is not None:
+                self.flush.zero_()                      # evicts the 126 MB L2
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        K.check_status(torch.device(DEV, torch.cuda.current_device()))
+        return total / self.iters
+
+
+def _rand(shape, dtype):
+    t = torch.randn(*shape, device=DEV)
+    return t.to(dtype)
+
+
+def bench_gemm(a, tm):
+    dt = {"bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn, "e4m3": torch.float8_e4m3fn}[a.dtype]
+    L.kernels().llmq_gemm_set_mode(a.mode)
+    A = _rand((a.k, a.m) if a.a_mn else (a.m, a.k), dt)
+    B = _rand((a.k, a.n) if a.b_mn else (a.n, a.k), dt)
+    C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=DEV)
+    ms = tm.time(lambda: K.gemm(C, A, B, a_mn=a.a_mn, b_mn=a.b_mn, accumulate=a.accumulate))
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    peak, _, src = _peaks()
+    print(json.dumps({"op": "gemm", "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype, "a_mn": a.a_mn, "b_mn": a.b_mn, "mode": a.mode,
+                      "ms": round(ms, 4), "tflops": round(tf, 1), f"frac_of_{src}_bf16_peak": round(tf / peak, 3)}))
+
+
+def bench_attention(a, tm):
+    qkv = _rand((a.b, a.t, a.hq + 2 * a.hkv, a.hs), torch.bfloat16)
+    out = torch.empty(a.b, a.t, a.hq, a.hs, dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty(a.b, a.hq, a.t, device=DEV)
+    dout = _rand((a.b, a.t, a.hq, a.hs), torch.bfloat16)
+    dqkv = torch.empty_like(qkv)
+    scratch = torch.empty(a.b * a.hq * a.t, device=DEV)
+    fwd = tm.time(lambda: K.attention_forward(out, lse, qkv, a.hq, a.hkv))
+    bwd = tm.time(lambda: K.attention_backward(dqkv, scratch, dout, out, lse, qkv, a.hq, a.hkv))
+    flops_fwd = 4.0 * a.b * a.hq * a.t * a.t * a.hs / 2          # causal: half of the score matrix
+    peak, _, src = _peaks()
+    print(json.dumps({"op": "attention", "b": a.b, "t": a.t, "hq": a.hq, "hkv": a.hkv, "hs": a.hs,
+                      "fwd_ms": round(fwd, 4), "fwd_tflops": round(flops_fwd / fwd / 1e9, 1),
+                      "bwd_ms": round(bwd, 4), "bwd_tflops": round(2.5 * flops_fwd / bwd / 1e9, 1),
+                      f"fwd_frac_of_{src}_bf16_peak": round(flops_fwd / fwd / 1e9 / peak, 3)}))
+
+
+def bench_elementwise(a, tm):
+    _, bw, src = _peaks()
+    rows, C, D = a.rows, a.c, a.d
+    res = {}
+    x, y, w = _rand((rows, C), torch.bfloat16), _rand((rows, C), torch.bfloat16), _rand((C,), torch.bfloat16)
+    o, r = torch.empty_like(x), torch.empty_like(x)
+    rstd, am = torch.empty(rows, device=DEV), torch.zeros(1, device=DEV)
+    ms = tm.time(lambda: K.rmsnorm_forward(o, rstd, x, w, 1e-6, residual_out=r, inp2=y, absmax=am))
+    res["fused_residual_rmsnorm"] = (ms, 4 * rows * C * 2)
+    scratch = torch.empty(K.rmsnorm_backward_scratch_elems(C, DEV), device=DEV)
+    dw = torch.zeros(C, dtype=torch.bfloat16, device=DEV)
+    ms = tm.time(lambda: K.rmsnorm_backward(o, dw, scratch, y, x, w, rstd, absmax=am))
+    res["rmsnorm_backward"] = (ms, 4 * rows * C * 2)
+    q = torch.empty(rows, C, dtype=torch.float8_e4m3fn, device=DEV)
+    sc = torch.empty(1, device=DEV)
+    am.fill_(4.0)
+    ms = tm.time(lambda: K.quantize(q, sc, x, am))
+    res["quantize_e4m3"] = (ms, rows * C * 3)
+    up, sw = _rand((rows, 2 * D), torch.bfloat16), torch.empty(rows, D, dtype=torch.bfloat16, device=DEV)
+    ms = tm.time(lambda: K.swiglu_forward(sw, up, absmax=am))
+    res["swiglu_forward"] = (ms, rows * D * 6)
+    ms = tm.time(lambda: K.swiglu_backward(up, sw, up, absmax=am))
+    res["swiglu_backward"] = (ms, rows * D * 10)
+    out = {k: {"ms": round(v[0], 4), "gbs": round(v[1] / v[0] / 1e6, 1), f"frac_of_{src}_hbm": round(v[1] / v[0] / 1e6 / bw, 3)} for k, v in res.items()}
+    print(json.dumps({"op": "elementwise", "rows": rows, "c": C, "d": D, **out}))
+
+
+def bench_adamw(a, tm):
+    _, bw, src = _peaks()
+    n = a.n
+    p, g = _rand((n,), torch.bfloat16), _rand((n,), torch.bfloat16)
+    m, v = torch.zeros(n, dtype=torch.bfloat16, device=DEV), torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+    gs, am = torch.ones(1, device=DEV), torch.zeros(1, device=DEV)
+    ms = tm.time(lambda: K.adamw(p, g, m, v, lr=1e-4, beta1=0.9, beta2=0.95, step=3, eps=1e-8, weight_decay=0.1, grad_scale=gs, absmax=am, seed=1))
+    gbs = n * 14 / ms / 1e6
+    print(json.dumps({"op": "adamw_bf16", "n": n, "ms": round(ms, 4), "gbs": round(gbs, 1), f"frac_of_{src}_hbm": round(gbs / bw, 3)}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "adamw"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--dtype", default="fp8")
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--accumulate", action="store_true")
+    ap.add_argument("--mode", type=int, default=0)
+    ap.add_argument("--b", type=int, default=8)
+    ap.add_argument("--t", type=int, default=2048)
+    ap.add_argument("--hq", type=int, default=28)
+    ap.add_argument("--hkv", type=int, default=4)
+    ap.add_argument("--hs", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--c", type=int, default=3584)
+    ap.add_argument("--d", type=int, default=18944)
+    a = ap.parse_args()
+    tm = Timer(a.iters, a.warmup, not a.no_flush)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw}[a.op](a, tm)
+
+
+if __name__ == "__main__":
+    main()
