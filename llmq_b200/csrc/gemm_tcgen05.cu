@@ -51,6 +51,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gsz;
 }
 
+template <bool F8>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -139,6 +140,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t b_step = p.b_mn_major ? mma_k * ROW_BYTES : 32;
             const uint32_t a_lbo = p.a_mn_major ? box_bytes : 16;
             const uint32_t b_lbo = p.b_mn_major ? box_bytes : 16;
+            const uint32_t a_hi = desc_hi(1024), b_hi = desc_hi(1024);
+            const uint32_t a_lo0 = desc_lo(smem_base, a_lbo), b_lo0 = desc_lo(smem_base + A_STAGE_BYTES, b_lbo);
+            const uint32_t a_inc = a_step >> 4, b_inc = b_step >> 4;
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
@@ -149,16 +153,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (int k = 0; k < k_iters; ++k) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicOr(p.status, kErrFullWait); ok = false; break; }
                     tc_fence_after_sync();
-                    uint32_t sa = smem_base + stage * STAGE_BYTES;
-                    uint32_t sb = sa + A_STAGE_BYTES;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint64_t ad = make_smem_desc(sa + j * a_step, a_lbo, 1024);
-                        uint64_t bd = make_smem_desc(sb + j * b_step, b_lbo, 1024);
-                        uint32_t accum = (k > 0 || j > 0) ? 1u : 0u;
-                        if (p.elem_bytes == 2) mma_f16(d_tmem, ad, bd, idesc, accum);
-                        else                   mma_f8(d_tmem, ad, bd, idesc, accum);
-                    }
+                    const uint32_t alo = a_lo0 + stage * (STAGE_BYTES >> 4);
+                    const uint32_t blo = b_lo0 + stage * (STAGE_BYTES >> 4);
+                    mma_issue<F8, false>(d_tmem, alo, a_hi, blo, b_hi, idesc, k > 0 ? 1u : 0u);
+                    mma_issue<F8, false>(d_tmem, alo + a_inc, a_hi, blo + b_inc, b_hi, idesc, 1u);
+                    mma_issue<F8, false>(d_tmem, alo + 2 * a_inc, a_hi, blo + 2 * b_inc, b_hi, idesc, 1u);
+                    mma_issue<F8, false>(d_tmem, alo + 3 * a_inc, a_hi, blo + 3 * b_inc, b_hi, idesc, 1u);
                     mma_commit(empty_bar(stage));          // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -283,12 +283,14 @@ extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
         attr_set[dev & 63] = true;
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (eb == 1) gemm_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    else         gemm_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
     return static_cast<int>(cudaGetLastError());
 }

@@ -41,6 +41,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gsz;
 }
 
+template <bool F8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
@@ -131,6 +132,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const uint32_t b_step = p.b_mn_major ? mma_k * ROW_BYTES : 32;
             const uint32_t a_lbo = p.a_mn_major ? box_bytes : 16;
             const uint32_t b_lbo = p.b_mn_major ? box_bytes : 16;
+            const uint32_t a_hi = desc_hi(1024), b_hi = desc_hi(1024);
+            const uint32_t a_lo0 = desc_lo(smem_base, a_lbo), b_lo0 = desc_lo(smem_base + A_STAGE_BYTES, b_lbo);
+            const uint32_t a_inc = a_step >> 4, b_inc = b_step >> 4;
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
@@ -141,16 +145,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 for (int k = 0; k < k_iters; ++k) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicOr(p.status, kErrFullWait); ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
-                    const uint32_t sb = sa + A_STAGE_BYTES;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint64_t ad = make_smem_desc(sa + j * a_step, a_lbo, 1024);
-                        uint64_t bd = make_smem_desc(sb + j * b_step, b_lbo, 1024);
-                        uint32_t accum = (k > 0 || j > 0) ? 1u : 0u;
-                        if (p.elem_bytes == 2) mma_f16_pair(d_tmem, ad, bd, idesc, accum);
-                        else                   mma_f8_pair(d_tmem, ad, bd, idesc, accum);
-                    }
+                    const uint32_t alo = a_lo0 + stage * (STAGE_BYTES >> 4);
+                    const uint32_t blo = b_lo0 + stage * (STAGE_BYTES >> 4);
+                    mma_issue<F8, true>(d_tmem, alo, a_hi, blo, b_hi, idesc, k > 0 ? 1u : 0u);
+                    mma_issue<F8, true>(d_tmem, alo + a_inc, a_hi, blo + b_inc, b_hi, idesc, 1u);
+                    mma_issue<F8, true>(d_tmem, alo + 2 * a_inc, a_hi, blo + 2 * b_inc, b_hi, idesc, 1u);
+                    mma_issue<F8, true>(d_tmem, alo + 3 * a_inc, a_hi, blo + 3 * b_inc, b_hi, idesc, 1u);
                     mma_commit_pair(empty_bar(stage));                       // stage free in this CTA ...
                     mma_commit_pair(map_to_cta(empty_bar(stage), 1));        // ... and in the peer
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -205,13 +205,15 @@ int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
         attr_set[dev & 63] = true;
     }
     const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
     int pairs = num_sms / 2;
     if (tiles < pairs) pairs = tiles;
-    gemm_tcgen05_2cta_kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (p.elem_bytes == 1) gemm_tcgen05_2cta_kernel<true><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    else                   gemm_tcgen05_2cta_kernel<false><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
     return static_cast<int>(cudaGetLastError());
 }

@@ -303,4 +303,37 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// MMA issue with the descriptors passed as (low, high) 32-bit halves.  The high half (stride / version /
+// swizzle bits) is loop invariant and the low half is "start address | LBO << 16", so stepping through
+// K or through pipeline stages is one 32-bit add per operand.  This keeps the single issuing thread far
+// ahead of the tensor core; rebuilding 64-bit descriptors per MMA costs more cycles than the MMA runs.
+template <bool F8, bool Pair>
+__device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+    if constexpr (F8 && !Pair) {
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+                     "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n}\n"
+                     ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (!F8 && !Pair) {
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+                     ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (F8 && Pair) {
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+                     "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %5, p;\n}\n"
+                     ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+                     "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+                     ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);   // SBO | version 1 (bit 46) | 128-byte swizzle (bits 61-63)
+}
+
 }  // namespace sm100
