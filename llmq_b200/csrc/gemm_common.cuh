@@ -40,12 +40,27 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
         if (p.bias) {
+            // every lane needs the same 32 bias values: vector loads that broadcast out of L1
+            if (p.bias_dtype == 0 && col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(static_cast<const __nv_bfloat16*>(p.bias) + col0) & 15u) == 0)) {
+                const uint4* bp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.bias) + col0);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                int cj = col0 + j;
-                if (cj < p.N) {
-                    v[j] += p.bias_dtype == 0 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[cj])
-                                              : static_cast<const float*>(p.bias)[cj];
+                for (int g = 0; g < 4; ++g) {
+                    uint4 bv = __ldg(bp + g);
+                    const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float2 f = __bfloat1622float2(bh[j]);
+                        v[g * 8 + 2 * j] += f.x; v[g * 8 + 2 * j + 1] += f.y;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    int cj = col0 + j;
+                    if (cj < p.N) {
+                        v[j] += p.bias_dtype == 0 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[cj])
+                                                  : static_cast<const float*>(p.bias)[cj];
+                    }
                 }
             }
         }
