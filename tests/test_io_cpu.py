@@ -1,0 +1,180 @@
+"""Data loader, safetensors, HF import/export and checkpoint round trips (CPU)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from llmq_b200.config import create_config_from_name, load_transformer_config
+from llmq_b200.models.llama import LlamaModel
+from llmq_b200.options import LLamaOptions
+from llmq_b200.training import checkpoint as ck
+from llmq_b200.training.dataloader import DataLoader, TokenFileWriter, write_synthetic_token_file
+from llmq_b200.utils import hf_io
+from llmq_b200.utils.safetensors import SafeTensorsReader, load_file, save_file
+
+
+def test_dataloader_targets_shift_masks_and_state(tmp_path):
+    f1, f2 = str(tmp_path / "a.bin"), str(tmp_path / "b.bin")
+    toks = np.arange(0, 1000, dtype=np.int32)
+    mask = (toks % 3 != 0)
+    with TokenFileWriter(f1, 2048, masking=True) as w:
+        w.add_document(toks[:400], mask[:400])
+        w.add_document(toks[400:], mask[400:])
+    write_synthetic_token_file(f2, 700, 2048, seed=1)
+    dl = DataLoader([f1], 16, seed=3)
+    assert dl.num_tokens == 1000 and dl.num_chunks == 62 and dl.vocab_size == 2048
+    x, y = np.zeros((4, 16), np.int32), np.zeros((4, 16), np.int32)
+    seen = set()
+    while dl.has_next(4):
+        dl.load_batch(x, y)
+        for r in range(4):
+            assert (x[r, 1:] == x[r, :-1] + 1).all() and x[r, 0] % 16 == 0      # whole, non-overlapping chunks
+            want = x[r] + 1
+            assert ((y[r] == want) | (y[r] == -100)).all()
+            assert ((y[r] == -100) == (x[r] % 3 == 0)).all()                    # bit i of the mask governs target i of the chunk
+            seen.add(int(x[r, 0]))
+    assert len(seen) == 60                                                      # every chunk at most once
+    # deterministic, seed-dependent order; state round trip
+    a, b = DataLoader([f1, f2], 16, seed=5), DataLoader([f1, f2], 16, seed=5)
+    xa, ya, xb, yb = (np.zeros((2, 16), np.int32) for _ in range(4))
+    for _ in range(5):
+        a.load_batch(xa, ya)
+    st = a.get_state()
+    a.load_batch(xa, ya)
+    b.set_state(st["seed"], st["epoch"], st["file_index"], st["chunk_index"])
+    b.load_batch(xb, yb)
+    assert (xa == xb).all() and (ya == yb).all()
+    c = DataLoader([f1, f2], 16, seed=6)
+    c.load_batch(xb, yb)
+    a.set_state(5, 0, 0, 0)
+    a.load_batch(xa, ya)
+    assert not (xa == xb).all()
+    # rank-strided assignment: two ranks see disjoint chunks
+    r0, r1 = DataLoader([f1], 16, seed=9, rank=0, world_size=2), DataLoader([f1], 16, seed=9, rank=1, world_size=2)
+    s0, s1 = set(), set()
+    for _ in range(10):
+        r0.load_batch(xa, ya)
+        r1.load_batch(xb, yb)
+        s0 |= set(xa[:, 0].tolist())
+        s1 |= set(xb[:, 0].tolist())
+    assert not (s0 & s1)
+    with pytest.raises(RuntimeError):
+        DataLoader([str(tmp_path / "missing.bin")], 16)
+
+
+def test_safetensors_roundtrip_and_partial_reads(tmp_path):
+    p = str(tmp_path / "t.safetensors")
+    t = {"a": torch.randn(7, 5), "b": torch.randn(12, 3).bfloat16(), "c": torch.arange(10, dtype=torch.int32),
+         "d": torch.randn(16, 4).to(torch.float8_e4m3fn)}
+    save_file(t, p, {"note": "x"})
+    back = load_file(p)
+    for k in t:
+        assert back[k].dtype == t[k].dtype and torch.equal(back[k].view(torch.uint8), t[k].view(torch.uint8))
+    r = SafeTensorsReader(p)
+    assert r.metadata["format"] == "pt" and r.metadata["note"] == "x"
+    part = torch.empty(4, 3, dtype=torch.float32)
+    r.read_into("b", part, elem_offset=6)                    # rows 2..5 with bf16 -> fp32 conversion
+    assert torch.equal(part, t["b"][2:6].float())
+    with pytest.raises(ValueError):
+        r.read_into("a", torch.empty(100))
+    # a truncated file is refused
+    raw = open(p, "rb").read()
+    open(p, "wb").write(raw[:-8])
+    with pytest.raises(ValueError):
+        SafeTensorsReader(p)
+    try:                                                     # the official package reads our files
+        from safetensors.torch import load_file as st_load
+        open(p, "wb").write(raw)
+        off = st_load(p)
+        assert torch.equal(off["a"], t["a"])
+    except ImportError:
+        pass
+
+
+def _model(tied=True, **kw):
+    cfg = create_config_from_name("tiny-qwen2", torch.float32).replace(tie_word_embeddings=tied)
+    m = LlamaModel(cfg, LLamaOptions(**kw), device="cpu", batch_size=2, seq_len=32)
+    m.init_weights(1)
+    return cfg, m
+
+
+@pytest.mark.parametrize("tied", [True, False])
+def test_hf_export_import_roundtrip(tmp_path, tied):
+    cfg, m = _model(tied)
+    out = str(tmp_path / "export")
+    hf_io.export_hf_model(m, out)
+    cfg2 = load_transformer_config(out, torch.float32)
+    assert cfg2.hidden_size == cfg.hidden_size and cfg2.tie_word_embeddings == tied and cfg2.use_qkv_bias
+    r = SafeTensorsReader(out)
+    HS, Hq, Hkv, D = cfg.head_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
+    qkv = m.weights.master_blocks[1]["qkv_w"]
+    assert torch.equal(r.read("model.layers.1.self_attn.q_proj.weight"), qkv[:Hq * HS])
+    assert torch.equal(r.read("model.layers.1.self_attn.v_proj.weight"), qkv[(Hq + Hkv) * HS:])
+    up = m.weights.master_blocks[0]["up_w"]
+    assert torch.equal(r.read("model.layers.0.mlp.gate_proj.weight"), up[D:])
+    assert ("lm_head.weight" in r) == (not tied)
+    _, m2 = _model(tied)
+    m2.init_weights(99)
+    hf_io.import_hf_weights(m2, out)
+    for (n, a, _, _), (_, b, _, _) in zip(m.weights.master_items(), m2.weights.master_items()):
+        assert torch.equal(a, b), n
+    # transformers can run the exported model and agrees with our forward pass
+    try:
+        from transformers import AutoModelForCausalLM
+    except Exception:
+        return
+    hf = AutoModelForCausalLM.from_pretrained(out, torch_dtype=torch.float32)
+    tok = torch.randint(0, 512, (2, 33))
+    with torch.no_grad():
+        hf_loss = hf(input_ids=tok[:, :-1], labels=None).logits
+    loss, _ = m.validate(tok[:, :-1].int(), tok[:, 1:].int())
+    ref = torch.nn.functional.cross_entropy(hf_loss.reshape(-1, 512), tok[:, 1:].reshape(-1))
+    assert abs(loss - ref.item()) < 1e-4
+
+
+def test_checkpoint_resume_is_exact(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, 512, (6, 2, 33), generator=g, dtype=torch.int32)
+
+    def steps(m, lo, hi):
+        out = []
+        for s in range(lo, hi):
+            m.forward(toks[s, :, :-1].contiguous())
+            m.backward(None, toks[s, :, 1:].contiguous(), 0.0, 1, 0)
+            out.append(m.update(lr=1e-3, step=s + 1)["loss"])
+        return out
+
+    _, a = _model(momentum_type="bf16")
+    ref = steps(a, 0, 6)
+    _, b = _model(momentum_type="bf16")
+    first = steps(b, 0, 3)
+    d = str(tmp_path / "ckpt")
+    ck.save_checkpoint(d, 3, b, {"data-loader": {"seed": 1, "epoch": 0, "file_index": 0, "chunk_index": 12}})
+    assert ck.find_latest_checkpoint(d) == 3 and ck.get_all_checkpoints(d) == [3]
+    _, c = _model(momentum_type="bf16")
+    c.init_weights(1234)
+    meta = ck.load_checkpoint(d, 3, c)
+    assert meta["data-loader"]["chunk_index"] == 12 and meta["distributed"]["world"] == 1
+    assert first + steps(c, 3, 6) == ref
+    # retention
+    for s in (4, 5, 6, 8):
+        ck.save_checkpoint(d, s, b)
+    assert ck.clean_old_checkpoints(d, 2, major_every=4) == [3, 5]
+    assert ck.get_all_checkpoints(d) == [4, 6, 8]
+    # damaged checkpoints are refused
+    shard = os.path.join(ck.get_checkpoint_path(d, 8), "adam.v.shard_000_of_001.safetensors")
+    raw = open(shard, "rb").read()
+    open(shard, "wb").write(raw[: len(raw) // 2])
+    with pytest.raises(ValueError):
+        ck.load_checkpoint(d, 8, c)
+    meta_file = os.path.join(ck.get_checkpoint_path(d, 6), "checkpoint.json")
+    meta = json.load(open(meta_file))
+    meta["distributed"]["world"] = 4
+    json.dump(meta, open(meta_file, "w"))
+    with pytest.raises(ValueError, match="world size"):
+        ck.load_checkpoint(d, 6, c)
+    os.remove(os.path.join(ck.get_checkpoint_path(d, 4), "weights.shard_000_of_001.safetensors"))
+    with pytest.raises(FileNotFoundError):
+        ck.load_checkpoint(d, 4, c)
