@@ -1,0 +1,80 @@
+"""The ``train`` and ``export-checkpoint`` entry points end to end on CPU with a tiny model and token files."""
+import json
+import os
+
+import pytest
+import torch
+
+from llmq_b200.cli import export_checkpoint, train
+from llmq_b200.training import checkpoint as ck
+from llmq_b200.training.config import TrainingConfig, parse_training_config
+from llmq_b200.training.dataloader import write_synthetic_token_file
+from llmq_b200.training.schedule import make_schedule
+from llmq_b200.utils.safetensors import SafeTensorsReader
+
+
+def _args(tmp_path, *extra):
+    write_synthetic_token_file(str(tmp_path / "train-0.bin"), 40_000, 512, seed=0)
+    write_synthetic_token_file(str(tmp_path / "eval-0.bin"), 3_000, 512, seed=1)
+    return ["--model", "tiny-qwen2", "--from-scratch", "--model-dtype", "fp32", "--batch", "2", "--seq-len", "32",
+            "--grad-accumulation", "2", "--steps", "6", "--lr", "1e-3", "--train-file", str(tmp_path / "train-*.bin"),
+            "--eval-file", str(tmp_path / "eval-*.bin"), "--eval-every-n-steps", "4", "--eval-num-steps", "2", "--ckpt-interval", "3",
+            "--name", "t", "--out-dir", str(tmp_path / "out/%n"), "--checkpoint-dir", str(tmp_path / "ckpt/%n"),
+            "--log-file", str(tmp_path / "log.json"), "--gpus", "1", "--verbosity", "-2", *extra]
+
+
+def test_flag_surface_and_implications():
+    c = parse_training_config(["--zero-level", "3", "--recompute-block", "--matmul-dtype", "e4m3", "--name", "x", "--opt-m-dtype", "bf16"])
+    assert c.shard_weights and c.shard_gradients and c.out_dir == "output/x" and c.checkpoint_dir == "ckpt/x"
+    o = c.to_options()
+    assert o.recompute_att and o.recompute_ffn and o.recompute_qkv and o.recompute_swiglu and o.matmul_dtype() == torch.float8_e4m3fn
+    assert o.momentum_type == torch.bfloat16 and o.variance_type == torch.float32
+    with pytest.raises(ValueError):
+        parse_training_config(["--zero-level", "2", "--shard-weights"])
+    with pytest.raises(ValueError):
+        parse_training_config(["--offload-quants"])
+    with pytest.raises(ValueError):
+        parse_training_config(["--init-proj-to-zero"])
+    for flag in ["--memcpy-all-gather", "--memcpy-send-recv", "--all-to-all-reduce", "--use-cuda-graphs", "--custom-matmul", "--write-combined",
+                 "--use-zero-copy", "--offload-master", "--offload-opt-m", "--offload-opt-v", "--offload-gradients", "--offload-residual",
+                 "--debug-time-breakdown", "--new-data"]:
+        parse_training_config([flag])
+
+
+def test_schedules():
+    s = make_schedule("cosine", 1.0, 100, warmup=10, final_lr_fraction=0.1)
+    assert s.eval(0) == pytest.approx(0.1) and s.eval(9) == pytest.approx(1.0) and s.eval(100) == pytest.approx(0.1)
+    assert s.eval(55) == pytest.approx(0.55, abs=0.01)
+    l = make_schedule("linear", 1.0, 100, 0, 0.0)
+    assert l.eval(50) == pytest.approx(0.5)
+    w = make_schedule("wsd", 1.0, 100, 5, 1.0, cooldown=20)
+    assert w.eval(50) == 1.0 and w.eval(79) == 1.0 and 0 < w.eval(90) < 1 and w.eval(99) == pytest.approx(0.0)
+
+
+def test_train_resume_and_export(tmp_path):
+    args = _args(tmp_path)
+    res = train.main(args)
+    assert res == 0
+    log = json.load(open(tmp_path / "log.json"))
+    kinds = {e["log"] for e in log}
+    assert {"cmd", "option", "sol", "dataset", "allocator", "step", "eval"} <= kinds
+    steps = [e for e in log if e["log"] == "step"]
+    assert len(steps) == 6 and steps[-1]["loss"] < steps[0]["loss"] + 0.1
+    ckdir = str(tmp_path / "ckpt/t")
+    assert ck.get_all_checkpoints(ckdir) == [3, 6]
+    out = SafeTensorsReader(str(tmp_path / "out/t"))
+    assert "model.layers.1.self_attn.k_proj.bias" in out and os.path.exists(tmp_path / "out/t/config.json")
+    # resume from step 3 and land on the same losses for steps 3..5
+    args2 = _args(tmp_path, "--continue", "3")
+    args2[args2.index("--log-file") + 1] = str(tmp_path / "log2.json")
+    train.main(args2)
+    steps2 = [e for e in json.load(open(tmp_path / "log2.json")) if e["log"] == "step"]
+    assert [e["step"] for e in steps2] == [3, 4, 5]
+    for a, b in zip(steps[3:], steps2):
+        assert a["loss"] == pytest.approx(b["loss"], abs=1e-6) and a["norm"] == pytest.approx(b["norm"], rel=1e-5)
+    # stand-alone export of the latest checkpoint equals the model the run wrote
+    exp = export_checkpoint.export_checkpoint("tiny-qwen2", ckdir, str(tmp_path / "exp"), model_dtype="fp32")
+    a, b = SafeTensorsReader(exp), SafeTensorsReader(str(tmp_path / "out/t"))
+    assert sorted(a.names()) == sorted(b.names())
+    for n in a.names():
+        assert torch.equal(a.read(n), b.read(n)), n
