@@ -71,18 +71,23 @@ class LLMQTrainer:
         self.options.memcpy_all_gather = memcpy_all_gather
         self.options.memcpy_send_recv = memcpy_send_recv
         self.batch_size, self.seq_length, self.grad_accum = batch_size, seq_len, grad_accum
-        env_world = int(os.environ.get("WORLD_SIZE", os.environ.get("OMPI_COMM_WORLD_SIZE", "1")))
+        from .parallel.threads import current_thread_comm
+        tcomm = current_thread_comm()                 # set when this rank runs as a thread of a multi-rank process
+        env_world = tcomm.world if tcomm is not None else int(os.environ.get("WORLD_SIZE", os.environ.get("OMPI_COMM_WORLD_SIZE", "1")))
         self._pool = None
         if ngpu is None or ngpu <= 0:
             ngpu = env_world if env_world > 1 else 1
         self.world_size = ngpu
         if ngpu > 1 and env_world == 1:
             from .parallel.launcher import WorkerPool
-            self._pool = WorkerPool(ngpu, config, self.options, batch_size, seq_len, grad_accum)
+            self._pool = WorkerPool(ngpu, config, self.options, batch_size, seq_len, grad_accum,
+                                    use_cuda=None if device is None else device != "cpu")
             self.model = None
             self.rank = 0
             self._micro = 0
             return
+        if tcomm is not None and device is None:
+            device = str(tcomm.device)
         if device is None:
             if torch.cuda.is_available():
                 local = int(os.environ.get("LOCAL_RANK", os.environ.get("OMPI_COMM_WORLD_LOCAL_RANK", "0")))
@@ -91,7 +96,10 @@ class LLMQTrainer:
             else:
                 device = "cpu"
         self.device = torch.device(device)
-        self.comm = make_communicator(self.device) if env_world > 1 else LocalComm()
+        if tcomm is not None:
+            self.comm = tcomm
+        else:
+            self.comm = make_communicator(self.device) if env_world > 1 else LocalComm()
         if ngpu != self.comm.world:
             raise ValueError(f"ngpu={ngpu} does not match the launcher's world size {self.comm.world}")
         self.rank = self.comm.rank
