@@ -47,12 +47,35 @@ class LlamaModel:
         self.gdtype = opts.grad_dtype() if self.quant else self.dtype
         if seq_len > cfg.max_position_embeddings:
             raise ValueError("sequence length exceeds max_position_embeddings")
-        self.weights = WeightsManager(cfg, opts, self.comm, self.device)
+        self.fused = self._make_fused()
+        self.weights = WeightsManager(cfg, opts, self.comm, self.device, self.fused)
         self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
         self.opt_state = OptimizerStateManager(cfg, opts, self.comm, self.device, self.weights)
         self._alloc_run_state()
         self.adam_seed = 42
         self.rng_state = 42                       # advanced every optimizer step; saved in checkpoints
+
+    def _make_fused(self):
+        """In-kernel NVLink collectives when asked for ("fused") or possible ("auto"): several ranks, one per process,
+        CUDA devices with symmetric-memory support.  "nccl" keeps the library collectives."""
+        mode = self.opts.collectives
+        if mode == "nccl" or self.comm.world == 1 or self.device.type != "cuda" or not hasattr(self.comm, "dist"):
+            if mode == "fused" and self.comm.world > 1:
+                raise RuntimeError("fused collectives need one CUDA rank per process (torch.distributed / NCCL plumbing)")
+            return None
+        try:
+            from ..parallel.fused import FusedCollectives
+            return FusedCollectives(self.comm, self.device)
+        except Exception:
+            if mode == "fused":
+                raise
+            return None
+
+    def _all_reduce_small(self, t: torch.Tensor, op: str) -> None:
+        if self.fused is not None and t.dtype == torch.float32 and t.is_contiguous() and t.numel() * self.comm.world <= 4096:
+            self.fused.all_reduce_small(t, op)
+        else:
+            self.comm.all_reduce(t, op).wait()
 
     # ================================================================================== run state
     def _alloc_run_state(self) -> None:
@@ -246,11 +269,11 @@ class LlamaModel:
         if positions_per_rank is None:
             cnt = (self.targets != -100).sum().float().reshape(1)
             if self.comm.world > 1:
-                self.comm.all_reduce(cnt, "avg").wait()
+                self._all_reduce_small(cnt, "avg")
         else:
             cnt = torch.full((1,), float(positions_per_rank), device=self.device)
         if self.comm.world > 1:
-            self.comm.all_reduce(gl, "avg").wait()
+            self._all_reduce_small(gl, "avg")
         cnt = cnt.clamp_min(1)
         total = gl.sum() / cnt
         n1k = min(self.T, 1024)
@@ -400,14 +423,16 @@ class LlamaModel:
         # ---- global gradient norm over the local shards
         self.norm_partials.zero_()
         shard_of = {}
+        norm_fused = getattr(g, "norm_fused", False)       # the reduce-scatter kernels already summed the squares
         for name, master, spec, l in w.master_items():
             gs = g.get_block_shard(l)[spec.name] if l is not None else g.get_nb_shard(spec.name)
             shard_of[name] = gs
-            gd = gs if gs.device.type == self.device.type else gs.to(self.device, non_blocking=True)
-            K.norm_squared(self.norm_partials, gd)
-        K.deterministic_sum(self.norm_io[0:1], self.norm_partials)
+            if not norm_fused:
+                gd = gs if gs.device.type == self.device.type else gs.to(self.device, non_blocking=True)
+                K.norm_squared(self.norm_partials, gd)
+        K.deterministic_sum(self.norm_io[0:1], g.norm_partials if norm_fused else self.norm_partials)
         if self.comm.world > 1:
-            self.comm.all_reduce(self.norm_io[0:1], "sum").wait()
+            self._all_reduce_small(self.norm_io[0:1], "sum")
         K.norm_finish(self.norm_io, grad_clip)
         scale = self.norm_io[1:2]
         # ---- AdamW on every shard

@@ -1,0 +1,159 @@
+"""In-kernel collectives over NVLink peer memory: the symmetric heap and the calls into ``csrc/p2p_collectives.cu``.
+
+``torch.distributed`` (NCCL) is used only as plumbing here: the rendez-vous that maps every rank's heap segments into
+every peer (``torch.distributed._symmetric_memory``) and a host barrier at set-up.  After that all traffic is
+issued by our own kernels with loads / stores on peer addresses, or with ``multimem`` loads on the NVSwitch
+multicast address when the platform offers one (``LLMQ_P2P_MULTIMEM=0`` forces plain peer loads; the failure
+tests use that).
+
+A tensor that takes part in a fused collective must live in the heap (``heap.empty``): it then has the same
+(segment, offset) on every rank, which is all a kernel needs besides the table of peer base pointers.
+Synchronisation uses flag words in a small heap segment: ``signal(channel)`` release-stores a generation number
+into word [channel][my rank] of every peer, ``wait(channel)`` spins (bounded) on the local words until every
+rank's generation arrived.  A time-out is recorded in the device status word and raised by ``check_status``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import lib as L
+
+F8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+SEGMENT_BYTES = 2 << 30
+MAX_CHANNELS = 4096
+SMALL_SLOTS_FLOATS = 4096              # per rank and per generation parity, for the small all-reduce
+
+
+class _Segment:
+    def __init__(self, nbytes: int, device, group):
+        import torch.distributed._symmetric_memory as symm
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.hdl = symm.rendezvous(self.buf, group)
+        self.nbytes, self.used = nbytes, 0
+        ptrs = list(self.hdl.buffer_ptrs)
+        self.peer_array = (ctypes.c_void_p * 8)(*(ptrs + [0] * (8 - len(ptrs))))
+        mc = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
+        self.multicast = mc if os.environ.get("LLMQ_P2P_MULTIMEM", "1") != "0" else 0
+        self.base = self.buf.data_ptr()
+
+
+class SymmetricHeap:
+    def __init__(self, device: torch.device, group, segment_bytes: int = SEGMENT_BYTES):
+        self.device, self.group, self.segment_bytes = device, group, segment_bytes
+        self.segments: List[_Segment] = []
+
+    def empty(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A zero-initialised tensor at the same (segment, offset) on every rank; collective over the group
+        whenever a new segment has to be mapped, so all ranks must allocate in the same order."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = (n * torch.empty(0, dtype=dtype).element_size() + 255) // 256 * 256
+        seg = next((s for s in self.segments if s.used + nbytes <= s.nbytes), None)
+        if seg is None:
+            seg = _Segment(max(self.segment_bytes, nbytes), self.device, self.group)
+            seg.buf.zero_()
+            self.segments.append(seg)
+        off = seg.used
+        seg.used += nbytes
+        raw = seg.buf[off:off + n * torch.empty(0, dtype=dtype).element_size()]
+        return raw.view(dtype).view(*shape)
+
+    def locate(self, t: torch.Tensor) -> Tuple[_Segment, int]:
+        p = t.data_ptr()
+        for s in self.segments:
+            if s.base <= p < s.base + s.nbytes:
+                return s, p - s.base
+        raise ValueError("tensor does not live in the symmetric heap")
+
+    def contains(self, t: torch.Tensor) -> bool:
+        p = t.data_ptr()
+        return any(s.base <= p < s.base + s.nbytes for s in self.segments)
+
+
+class FusedCollectives:
+    """Per-rank object that launches the peer-memory kernels; one side stream carries gathers and reductions."""
+
+    def __init__(self, comm, device: torch.device, wait_limit_s: float = 20.0):
+        import torch.distributed as dist
+        self.comm, self.device = comm, device
+        self.rank, self.world = comm.rank, comm.world
+        if self.world > 8:
+            raise ValueError("peer-memory collectives support up to 8 ranks (one NVSwitch domain)")
+        group = comm.group if comm.group is not None else dist.group.WORLD
+        self.heap = SymmetricHeap(device, group)
+        self.ctrl = _Segment(1 << 20, device, group)                    # flags + small all-reduce slots
+        self.ctrl.buf.zero_()
+        self.flag_bytes = MAX_CHANNELS * 8 * 4
+        self.slots_offset = self.flag_bytes
+        self.small_channel = MAX_CHANNELS - 1
+        self.gen: Dict[int, int] = {}
+        self.wait_limit_s = wait_limit_s
+        self.stream = torch.cuda.Stream(device)
+        self.sms = K.num_sms(device)
+        self.status = K.status_word(device)
+        self.use_multimem = self.ctrl.multicast != 0
+        torch.cuda.synchronize(device)
+        comm.barrier()
+
+    # ---- flags
+    def _flag_offset(self, channel: int) -> int:
+        return channel * 8 * 4
+
+    def next_gen(self, channel: int) -> int:
+        g = self.gen.get(channel, 0) + 1
+        self.gen[channel] = g
+        return g
+
+    def signal(self, channel: int, gen: Optional[int] = None) -> int:
+        """All earlier work of the current stream is visible to a peer that sees this generation."""
+        gen = self.next_gen(channel) if gen is None else gen
+        L.check(L.kernels().llmq_p2p_signal(self.ctrl.peer_array, ctypes.c_longlong(self._flag_offset(channel)), self.rank, self.world,
+                                            ctypes.c_uint(gen), L.stream_ptr()), "p2p_signal")
+        return gen
+
+    def wait(self, channel: int, gen: int) -> None:
+        """Current stream waits until every rank signalled ``gen`` on ``channel`` (bounded; see check_status)."""
+        flags = ctypes.c_void_p(self.ctrl.base + self._flag_offset(channel))
+        L.check(L.kernels().llmq_p2p_wait(flags, self.world, ctypes.c_uint(gen), L.ptr(self.status), ctypes.c_double(self.wait_limit_s),
+                                          L.stream_ptr()), "p2p_wait")
+
+    # ---- data movement
+    def quant_allgather(self, full: torch.Tensor, shard: torch.Tensor, absmax: Optional[torch.Tensor] = None,
+                        scale_out: Optional[torch.Tensor] = None) -> None:
+        """Stores this rank's shard (quantised to ``full``'s fp8 dtype with the given abs-max, or copied) into the
+        shard's slot of ``full`` on every rank."""
+        seg, off = self.heap.locate(full)
+        quant = full.dtype in F8
+        if shard.dtype != torch.bfloat16 or (not quant and full.dtype != torch.bfloat16):
+            raise TypeError("fused all-gather takes bf16 shards and writes e4m3 or bf16")
+        L.check(L.kernels().llmq_p2p_quant_allgather(seg.peer_array, ctypes.c_longlong(off), L.ptr(shard), ctypes.c_longlong(shard.numel()),
+                                                     self.rank, self.world, L.ptr(absmax), L.ptr(scale_out), 1 if quant else 0, self.sms,
+                                                     L.stream_ptr()), "p2p_quant_allgather")
+
+    def reduce_scatter(self, full: torch.Tensor, dst: torch.Tensor, *, accumulate: bool, scale: float,
+                       norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
+        """dst (+)= scale * sum over ranks of rows [rank*n/w, (rank+1)*n/w) of ``full`` (bf16, in the heap)."""
+        seg, off = self.heap.locate(full)
+        n_shard = full.numel() // self.world
+        mc = ctypes.c_void_p(seg.multicast if (seg.multicast and n_shard % 8 == 0) else 0)
+        L.check(L.kernels().llmq_p2p_reduce_scatter(seg.peer_array, mc, ctypes.c_longlong(off), ctypes.c_longlong(n_shard), self.rank,
+                                                    self.world, L.ptr(dst), int(accumulate), ctypes.c_float(scale), L.ptr(norm_partials),
+                                                    0 if norm_partials is None else norm_partials.numel(), ctypes.c_uint(seed & 0xFFFFFFFF),
+                                                    self.sms, L.stream_ptr()), "p2p_reduce_scatter")
+
+    def all_reduce_small(self, t: torch.Tensor, op: str = "sum") -> None:
+        """In-place sum / max / avg of a few fp32 values across ranks, one kernel, no library call."""
+        n = t.numel()
+        if t.dtype != torch.float32 or not t.is_contiguous() or n > SMALL_SLOTS_FLOATS // self.world:
+            raise ValueError("small all-reduce takes a contiguous fp32 tensor of limited size")
+        gen = self.next_gen(self.small_channel)
+        L.check(L.kernels().llmq_p2p_allreduce_small(self.ctrl.peer_array, ctypes.c_longlong(self.slots_offset),
+                                                     ctypes.c_longlong(self._flag_offset(self.small_channel)), L.ptr(t), n, self.rank, self.world,
+                                                     {"sum": 0, "max": 1, "avg": 2}[op], ctypes.c_uint(gen), L.ptr(self.status),
+                                                     ctypes.c_double(self.wait_limit_s), L.stream_ptr()), "p2p_allreduce_small")

@@ -68,6 +68,23 @@ def _rows(shape, world):
     return (shape[0] // world,) + tuple(shape[1:])
 
 
+# flag channels of the fused collectives (each channel = one word per source rank)
+CH_WEIGHTS, CH_NONBLOCK, CH_GRADS, CH_GRADS_NB = 0, 1024, 1100, 3000
+
+
+class _FusedPending:
+    """Handle of a fused gather / reduction: wait() orders the current stream after the side stream's work and
+    after the arrival of every peer's data flag."""
+
+    def __init__(self, fused, channel, gen, event, device):
+        self.fused, self.channel, self.gen, self.event, self.device = fused, channel, gen, event, device
+
+    def wait(self):
+        torch.cuda.current_stream(self.device).wait_event(self.event)
+        if self.channel is not None:
+            self.fused.wait(self.channel, self.gen)
+
+
 class _Buf:
     """One work buffer (a full transformer block) with its cache state."""
 
@@ -80,8 +97,9 @@ class _Buf:
 
 
 class WeightsManager:
-    def __init__(self, cfg: TransformerConfig, opts: LLamaOptions, comm: Communicator, device: torch.device):
+    def __init__(self, cfg: TransformerConfig, opts: LLamaOptions, comm: Communicator, device: torch.device, fused=None):
         self.cfg, self.opts, self.comm, self.device = cfg, opts, comm, device
+        self.fused = fused                    # FusedCollectives: gathers become in-kernel peer stores
         self.model_dtype = opts.model_type or cfg.dtype
         self.matmul_dtype = opts.matmul_dtype()
         self.master_dtype = opts.master()
@@ -96,17 +114,23 @@ class WeightsManager:
         def work_dtype(s):
             return self.matmul_dtype if (s.matrix and s.name in MATRICES) else self.model_dtype
 
+        # fused gathers need bf16 masters on the device and bf16 / e4m3 work copies
+        if self.fused is not None and not (self.master_dtype == torch.bfloat16 and self.model_dtype == torch.bfloat16 and not host_master
+                                           and self.matmul_dtype in (torch.bfloat16, torch.float8_e4m3fn)
+                                           and not (opts.persistent_quants and self.sharded)):
+            self.fused = None
+        walloc = (lambda shape, dt: self.fused.heap.empty(shape, dt)) if self.fused is not None else (lambda shape, dt: _alloc(shape, dt, device))
         # ---- work buffers
         n_bufs = 2 if self.sharded else L
         self.bufs = [_Buf() for _ in range(n_bufs)]
         for b in self.bufs:
             for s in self.block_specs:
-                b.t[s.name] = _alloc(s.shape, work_dtype(s), device)
+                b.t[s.name] = walloc(s.shape, work_dtype(s))
         self.nb_work: Dict[str, torch.Tensor] = {}
         for s in self.nonblock_specs:
             if self.sharded and s.name == "lm_head":
                 continue                      # embedding and head share one gather buffer under ZeRO-3
-            self.nb_work[s.name] = _alloc(s.shape, self.model_dtype, device)
+            self.nb_work[s.name] = walloc(s.shape, self.model_dtype)
         self.nb_state = {"embed": [-1, None], "lnf_w": [-1, None], "emb_slot_holds": None}
 
         # ---- master shards
@@ -169,6 +193,9 @@ class WeightsManager:
             return
         if buf.in_use:
             raise RuntimeError(f"weight buffer for layer {l} is still in use by layer {buf.layer}")
+        if self.fused is not None and self.comm.world > 1:
+            self._gather_block_fused(l, buf)
+            return
         works = []
         for s in self.block_specs:
             full = buf.t[s.name]
@@ -192,6 +219,30 @@ class WeightsManager:
         if self.quant_shards is not None:
             self.quant_version[l] = self.version
         buf.pending = _WorkList(works)
+        buf.layer, buf.version = l, self.version
+
+    def _gather_block_fused(self, l: int, buf: _Buf) -> None:
+        """Quantise-and-push: every rank stores its (quantised) shard straight into all ranks' buffers over NVLink.
+        Side stream: barrier (all ranks are past the previous user of this buffer) -> pushes -> data flag."""
+        f = self.fused
+        idx = self.bufs.index(buf)
+        ch_free, ch_data = CH_WEIGHTS + 2 * idx, CH_WEIGHTS + 2 * idx + 1
+        main = torch.cuda.current_stream(self.device)
+        f.stream.wait_stream(main)
+        with torch.cuda.stream(f.stream):
+            f.wait(ch_free, f.signal(ch_free))
+            for s in self.block_specs:
+                full = buf.t[s.name]
+                master = self.master_blocks[l][s.name]
+                if s.name in MATRICES and self.quantized:
+                    st = self._stat(l, s.name)
+                    f.quant_allgather(full, master, st[0:1], st[1:2])
+                else:
+                    f.quant_allgather(full, master)
+            gen = f.signal(ch_data)
+            ev = torch.cuda.Event()
+            ev.record(f.stream)
+        buf.pending = _FusedPending(f, ch_data, gen, ev, self.device)
         buf.layer, buf.version = l, self.version
 
     def get_block(self, l: int) -> SimpleNamespace:
@@ -220,10 +271,17 @@ class WeightsManager:
             return full
         local = self.comm.local_shard(full)
         master = self.master_nb[name]
-        if master.data_ptr() != local.data_ptr():
-            local.copy_(self._to_device(master, "nb_" + name))
-        if self.comm.world > 1:
-            st[1] = self.comm.all_gather(full, local)
+        if self.fused is not None and self.comm.world > 1:
+            f = self.fused
+            ch = CH_NONBLOCK + 2 * list(self.nb_work).index(slot)
+            f.wait(ch, f.signal(ch))                     # every rank is done with the slot's previous content
+            f.quant_allgather(full, master)
+            f.wait(ch + 1, f.signal(ch + 1))
+        else:
+            if master.data_ptr() != local.data_ptr():
+                local.copy_(self._to_device(master, "nb_" + name))
+            if self.comm.world > 1:
+                st[1] = self.comm.all_gather(full, local)
         st[0] = self.version
         self.nb_state["holds_" + slot] = name
         return full
@@ -267,7 +325,10 @@ class WeightsManager:
                     K.abs_max(self._stat(l, n)[0:1], self._to_device(self.master_blocks[l][n], "m_" + n))
         if self.comm.world > 1:
             am = self.w_stats[:, :, 0].contiguous()
-            self.comm.all_reduce(am, "max").wait()
+            if self.fused is not None and am.numel() * self.comm.world <= 4096:
+                self.fused.all_reduce_small(am.view(-1), "max")
+            else:
+                self.comm.all_reduce(am, "max").wait()
             self.w_stats[:, :, 0].copy_(am)
 
     # ------------------------------------------------------------------ iteration (checkpoint / optimizer)
@@ -293,21 +354,32 @@ class GradientManager:
         L, w = cfg.num_hidden_layers, comm.world
         host = opts.offload_grads and device.type == "cuda" and self.sharded
         self.micro_step, self.last = 0, False
+        # in-kernel reduce-scatter: bf16 gradients in the symmetric heap, shards on the device
+        self.fused = weights.fused if (weights.fused is not None and self.dtype == torch.bfloat16 and not host and w > 1) else None
+        self.norm_fused = self.fused is not None
+        self.norm_partials = torch.zeros(K.NORM_PARTIALS, dtype=torch.float32, device=device) if self.fused is not None else None
+        self._fdone: Dict[int, tuple] = {}           # channel -> (generation, event) of the last reduction reading a buffer
+        self._fevents: List = []
+        _heap = self.fused.heap if self.fused is not None else None
+        _galloc = (lambda shape: _heap.empty(shape, self.dtype)) if _heap is not None else (lambda shape: _alloc(shape, self.dtype, device))
         if self.sharded:
-            self.bufs = [{s.name: _alloc(s.shape, self.dtype, device) for s in self.block_specs} for _ in range(2)]
+            self.bufs = [{s.name: _galloc(s.shape) for s in self.block_specs} for _ in range(2)]
             self.buf_state = [{"layer": -1, "pending": None, "needs_acc": False} for _ in range(2)]
             self.shards = [{s.name: _alloc(_rows(s.shape, w), self.dtype, device, pinned=host) for s in self.block_specs}
                            for _ in range(L)]
         else:
-            self.full = [{s.name: _alloc(s.shape, self.dtype, device) for s in self.block_specs} for _ in range(L)]
+            self.full = [{s.name: _galloc(s.shape) for s in self.block_specs} for _ in range(L)]
             self.pending: List = [None] * L
-        self.nb_full = {s.name: _alloc(s.shape, self.dtype, device) for s in self.nonblock_specs}
+        self.nb_full = {s.name: _galloc(s.shape) for s in self.nonblock_specs}
         self.nb_pending: Dict[str, object] = {}
         self._stage: Dict[str, torch.Tensor] = {}
 
     # -- micro-step protocol
     def start_micro_step(self, micro_step: int, total: int) -> None:
         self.micro_step, self.last = micro_step, micro_step == total - 1
+        if micro_step == 0 and self.fused is not None:
+            for k in range(len(self.nonblock_specs)):          # peers may still read last step's non-block gradients
+                self._wait_readers(CH_GRADS_NB + 2 * k)
         if micro_step == 0:
             for s in self.nonblock_specs:
                 if not s.matrix:
@@ -315,12 +387,15 @@ class GradientManager:
 
     def get_block_full(self, l: int):
         """Returns (tensors, accumulate): where layer l's backward writes, and whether it adds to the content."""
+        if self.fused is not None:
+            self._wait_readers(CH_GRADS + 2 * (l % 2 if self.sharded else l))
         if not self.sharded:
             g = self.full[l]
             acc = self.micro_step > 0
         else:
             i = l % 2
-            self._flush(i)
+            if self.fused is None:
+                self._flush(i)
             g = self.bufs[i]
             self.buf_state[i]["layer"] = l
             acc = False
@@ -330,7 +405,45 @@ class GradientManager:
                     g[s.name].zero_()          # vectors are always accumulated into; matrices are overwritten
         return g, acc
 
+    # -- fused (in-kernel) reduction -------------------------------------------------------------
+    def _wait_readers(self, ch_ready: int) -> None:
+        """Before a gradient buffer is overwritten: our own reduction and every peer's reads of it are finished."""
+        d = self._fdone.pop(ch_ready, None)
+        if d is not None:
+            gen, ev = d
+            torch.cuda.current_stream(self.device).wait_event(ev)
+            self.fused.wait(ch_ready + 1, gen)
+
+    def _reduce_fused(self, ch_ready: int, pairs, accumulate: bool, seed: int) -> None:
+        """pairs: [(full tensor in the heap, destination shard)].  Main stream: flag "my gradients are complete".
+        Side stream: wait for every rank's flag, pull-and-reduce this rank's rows, flag "done reading"."""
+        f = self.fused
+        main = torch.cuda.current_stream(self.device)
+        gen = f.signal(ch_ready)
+        f.stream.wait_stream(main)
+        with torch.cuda.stream(f.stream):
+            f.wait(ch_ready, gen)
+            for k, (full, dst) in enumerate(pairs):
+                f.reduce_scatter(full, dst, accumulate=accumulate, scale=1.0 / self.comm.world,
+                                 norm_partials=self.norm_partials if self.last else None, seed=seed + 17 * k)
+            done = f.signal(ch_ready + 1)
+            ev = torch.cuda.Event()
+            ev.record(f.stream)
+        self._fdone[ch_ready] = (done, ev)
+        self._fevents.append(ev)
+
     def notify_block(self, l: int) -> None:
+        if self.fused is not None:
+            seed = (self.seed * 7919 + self.step * 104729 + l * 131 + self._acc_count[l] * 7) & 0x7FFFFFFF
+            if not self.sharded:
+                if self.last:
+                    self._reduce_fused(CH_GRADS + 2 * l, [(t, self.comm.local_shard(t)) for t in self.full[l].values()], False, seed)
+            else:
+                i = l % 2
+                pairs = [(self.bufs[i][s.name], self.shards[l][s.name]) for s in self.block_specs]
+                self._reduce_fused(CH_GRADS + 2 * i, pairs, self._acc_count[l] > 0, seed)
+                self._acc_count[l] += 1
+            return
         if not self.sharded:
             if self.last and self.comm.world > 1:
                 self.pending[l] = _WorkList([self.comm.reduce_scatter_avg(t) for t in self.full[l].values()])
@@ -381,13 +494,21 @@ class GradientManager:
 
     def begin_step(self) -> None:
         self._acc_count = [0] * self.cfg.num_hidden_layers
+        if self.norm_partials is not None:
+            self.norm_partials.zero_()
 
     def notify_non_block(self, name: str) -> None:
+        if self.fused is not None:
+            if self.last:
+                k = [s.name for s in self.nonblock_specs].index(name)
+                t = self.nb_full[name]
+                self._reduce_fused(CH_GRADS_NB + 2 * k, [(t, self.comm.local_shard(t))], False, 0)
+            return
         if self.last and self.comm.world > 1:
             self.nb_pending[name] = self.comm.reduce_scatter_avg(self.nb_full[name])
 
     def end_micro_step(self) -> None:
-        if self.sharded:
+        if self.sharded and self.fused is None:
             self._flush(0)
             self._flush(1)
 
@@ -396,6 +517,12 @@ class GradientManager:
 
     # -- optimizer side
     def wait_all(self) -> None:
+        if self.fused is not None:
+            main = torch.cuda.current_stream(self.device)
+            for ev in self._fevents:
+                main.wait_event(ev)
+            self._fevents = []
+            return
         if not self.sharded:
             for l, p in enumerate(self.pending):
                 if p is not None:

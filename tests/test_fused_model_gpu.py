@@ -1,0 +1,82 @@
+"""Training steps on 2+ GPUs: in-kernel (peer-memory) collectives against the NCCL path, ZeRO-1/2/3."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+B, T = 2, 256
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+        from llmq_b200.config import TransformerConfig
+        from llmq_b200.models.llama import LlamaModel
+        from llmq_b200.ops import kernels as K
+        from llmq_b200.options import LLamaOptions
+        from llmq_b200.parallel.comm import TorchDistComm
+        dev = torch.device("cuda", rank)
+        torch.cuda.set_device(dev)
+        comm = TorchDistComm(dev, timeout_s=120)
+        cfg = TransformerConfig("qwen2", 0, 0, None, 256, 512, 1024, 4, 2, 2, 2048, 1e6, 1e-6, False, True, torch.bfloat16)
+        g = torch.Generator().manual_seed(5 + rank)
+        tok = torch.randint(0, 1024, (2, B, T + 1), generator=g, dtype=torch.int32)
+        results = {}
+        for zero in (1, 2, 3):
+            for mode in ("nccl", "fused"):
+                opts = LLamaOptions(matmul_type="e4m3", collectives=mode, momentum_type="bf16", variance_type="bf16")
+                opts.set_zero_level(zero)
+                m = LlamaModel(cfg, opts, comm, dev, B, T)
+                assert (m.fused is not None) == (mode == "fused")
+                m.init_weights(3)
+                out = []
+                for step in range(1, 4):
+                    for j in range(2):
+                        m.forward(tok[j, :, :-1].contiguous(), j)
+                        m.backward(None, tok[j, :, 1:].contiguous(), 0.0, 2, j)
+                    r = m.update(lr=1e-3, step=step, grad_accum=2)
+                    out.append((r["loss"], r["norm"]))
+                torch.cuda.synchronize()
+                K.check_status(dev)
+                results[(zero, mode)] = out
+                del m
+                comm.barrier()
+        q.put((rank, "ok", results))
+        comm.shutdown()
+    except Exception as e:
+        q.put((rank, "error", repr(e) + "\n" + traceback.format_exc()))
+
+
+def test_fused_training_matches_nccl():
+    world = 2 if torch.cuda.device_count() >= 2 else 0
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=400) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():
+            p.kill()
+    assert all(r[1] == "ok" for r in res), res
+    r0 = res[0][2]
+    for zero in (1, 2, 3):
+        a, b = r0[(zero, "nccl")], r0[(zero, "fused")]
+        for (l0, n0), (l1, n1) in zip(a, b):
+            assert abs(l0 - l1) < 5e-3, (zero, a, b)
+            assert abs(n0 - n1) < 2e-2 * max(1.0, n0), (zero, a, b)
+        assert a[-1][0] < a[0][0]
