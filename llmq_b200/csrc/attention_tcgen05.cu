@@ -26,6 +26,10 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+// low descriptor half of (base + byte offset); the base part is loop invariant, the offset a constant after unrolling
+#define DLO(base, lbo, off) (desc_lo((base), (lbo)) + static_cast<uint32_t>((off) >> 4))
+#define kDescHi desc_hi(1024)
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -81,25 +85,29 @@ struct AttnParams {
 };
 
 // ------------------------------------------------------------------------------------------------
-// Forward
+// Forward.  O accumulates in TMEM across all key tiles (tcgen05.mma with accumulate); it is rescaled only when a
+// row maximum moved by more than 2^8 since the last rescale (the stale maximum keeps P <= 256, exact in the
+// final normalisation).  Score tiles are double buffered in TMEM and K / V in shared memory, so the tensor core
+// computes S(j+1) while the threads run the softmax of tile j.
 template <int HS>
 __global__ void __launch_bounds__(128, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv, const AttnParams p) {
     constexpr int BQ = 128, BKV = 64, NCH = HS / 64;
     constexpr int Q_BYTES = BQ * HS * 2, KV_BYTES = BKV * HS * 2, P_BYTES = BQ * BKV * 2;
-    constexpr uint32_t TMEM_COLS = (64 + HS) <= 128 ? 128 : 256;
+    constexpr uint32_t TMEM_COLS = 256;                       // S0 | S1 | O
+    constexpr float kRescaleThreshold = 8.f;                  // in log2 units
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + Q_BYTES;
-    uint8_t* sV = sK + KV_BYTES;
-    uint8_t* sP = sV + KV_BYTES;
+    uint8_t* sK = sQ + Q_BYTES;            // 2 buffers
+    uint8_t* sV = sK + 2 * KV_BYTES;       // 2 buffers
+    uint8_t* sP = sV + 2 * KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }   // swizzled tiles need 1 KiB alignment
-    const int qb = gridDim.x - 1 - blockIdx.x;       // longest rows first
+    const int qb = gridDim.x - 1 - blockIdx.x;                // longest rows first
     const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / (p.Hq / p.Hkv);
     const int q0 = qb * BQ;
@@ -107,9 +115,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int qcol = h * HS, kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_bar = bar0, k_bar = bar0 + 8, v_bar = bar0 + 16, s_bar = bar0 + 24, o_bar = bar0 + 32;
+    const uint32_t q_bar = bar0, o_bar = bar0 + 8;
+    auto k_bar = [&](int i) { return bar0 + 16 + 8 * i; };
+    auto v_bar = [&](int i) { return bar0 + 32 + 8 * i; };
+    auto s_bar = [&](int i) { return bar0 + 48 + 8 * i; };
     if (tid == 0) {
-        for (int i = 0; i < 5; ++i) mbar_init(bar0 + 8 * i, 1);
+        for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8 * i, 1);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -118,60 +129,69 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tS = tmem, tO = tmem + 64;
+    const uint32_t tO = tmem + 128;
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
 
+    auto load_k = [&](int j) {
+        const int bi = j & 1;
+        mbar_expect_tx(k_bar(bi), KV_BYTES);
+        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + bi * KV_BYTES + c * (BKV * 128), &tmap_kv, k_bar(bi), kcol + c * 64, j * BKV, b);
+    };
+    auto load_v = [&](int j) {
+        const int bi = j & 1;
+        mbar_expect_tx(v_bar(bi), KV_BYTES);
+        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + bi * KV_BYTES + c * (BKV * 128), &tmap_kv, v_bar(bi), vcol + c * 64, j * BKV, b);
+    };
+    const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
+    const uint32_t idesc_o = make_instr_desc(1, 1, false, true, BQ, HS);
+    auto issue_s = [&](int j) {                               // S[j&1] = Q K(j)^T
+        const int bi = j & 1;
+#pragma unroll
+        for (int k = 0; k < HS / 16; ++k) {
+            mma_issue<false, false>(tmem + bi * 64, DLO(smem_u32(sQ), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
+                                    DLO(smem_u32(sK), 16, bi * KV_BYTES + (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
+        }
+        mma_commit(s_bar(bi));
+    };
+
+    bool ok = true;
     if (tid == 0) {
         tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_kv);
         mbar_expect_tx(q_bar, Q_BYTES);
         for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sQ) + c * (BQ * 128), &tmap_q, q_bar, qcol + c * 64, q0, b);
-        mbar_expect_tx(k_bar, KV_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv, k_bar, kcol + c * 64, 0, b);
-        mbar_expect_tx(v_bar, KV_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv, v_bar, vcol + c * 64, 0, b);
+        load_k(0); load_v(0);
+        if (n_kv > 1) { load_k(1); load_v(1); }
+        ok = mbar_wait(q_bar, 0, abort_flag) && mbar_wait(k_bar(0), 0, abort_flag);
+        tc_fence_after_sync();
+        if (ok) issue_s(0);
     }
 
-    const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
-    const uint32_t idesc_o = make_instr_desc(1, 1, false, true, BQ, HS);
     const float sl2 = p.scale * kLog2e;
     const int row = q0 + tid;
-    float m = -INFINITY, l = 0.f;
-    float acc[HS];
-#pragma unroll
-    for (int i = 0; i < HS; ++i) acc[i] = 0.f;
-    bool ok = true;
+    float m_ref = -INFINITY, l = 0.f;
 
     for (int j = 0; j < n_kv && ok; ++j) {
-        const uint32_t par = j & 1;
-        if (tid == 0) {
-            if (j == 0) ok = mbar_wait(q_bar, 0, abort_flag);
-            ok = ok && mbar_wait(k_bar, par, abort_flag);
-            tc_fence_after_sync();
-            if (ok) {
-#pragma unroll
-                for (int k = 0; k < HS / 16; ++k) {
-                    uint64_t ad = make_smem_desc(smem_u32(sQ) + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-                    uint64_t bd = make_smem_desc(smem_u32(sK) + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-                    mma_f16(tS, ad, bd, idesc_s, k > 0);
-                }
-                mma_commit(s_bar);
-            }
-        }
-        if (!mbar_wait(s_bar, par, abort_flag)) { ok = false; break; }
+        const int bi = j & 1;
+        const uint32_t par = (j >> 1) & 1;
+        if (!mbar_wait(s_bar(bi), par, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        if (tid == 0 && j + 1 < n_kv) {                       // K tile is free again
-            mbar_expect_tx(k_bar, KV_BYTES);
-            for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv, k_bar, kcol + c * 64, (j + 1) * BKV, b);
+        if (tid == 0) {
+            if (j + 1 < n_kv) {                               // next score tile runs on the tensor core during this softmax
+                ok = mbar_wait(k_bar(bi ^ 1), ((j + 1) >> 1) & 1, abort_flag);
+                tc_fence_after_sync();
+                if (ok) issue_s(j + 1);
+            }
+            if (ok && j + 2 < n_kv) load_k(j + 2);            // K[bi] was released by S(j)
         }
         float s[64];
         __syncwarp();
         {
             uint32_t r[32];
-            tmem_ld_32x32b_x32(tS + lane_off, r);
+            tmem_ld_32x32b_x32(tmem + bi * 64 + lane_off, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
-            tmem_ld_32x32b_x32(tS + lane_off + 32, r);
+            tmem_ld_32x32b_x32(tmem + bi * 64 + lane_off + 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(r[i]);
@@ -180,16 +200,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 64; ++i) if (j * BKV + i > row) s[i] = -INFINITY;
         }
-        float mx = m;
+        float mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 64; ++i) mx = fmaxf(mx, s[i]);
-        const float alpha = exp2f((m - mx) * sl2);            // m = -inf on the first tile -> 0
-        const float moff = mx * sl2;
+        // everything below needs PV(j-1) finished: it read P, and it wrote the O we may rescale
+        if (j > 0) {
+            if (!mbar_wait(o_bar, (j - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            if (tid == 0 && j + 1 < n_kv && j + 1 >= 2) load_v(j + 1);     // V[(j+1)&1] was released by PV(j-1)
+        }
+        const bool need = j == 0 ? true : (mx - m_ref) * sl2 > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+            const float m_new = fmaxf(m_ref, mx);
+            if (j > 0) {
+                const float alpha = exp2f((m_ref - m_new) * sl2);
+                l *= alpha;
+#pragma unroll
+                for (int c = 0; c < HS / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tO + lane_off + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st_32x32b_x32(tO + lane_off + c * 32, r);
+                }
+                tmem_st_wait();
+            }
+            m_ref = m_new;
+        }
+        const float moff = m_ref * sl2;
         float sum = 0.f;
 #pragma unroll
         for (int i = 0; i < 64; ++i) { s[i] = exp2f(s[i] * sl2 - moff); sum += s[i]; }
-        l = l * alpha + sum;
-        m = mx;
+        l += sum;
         {
             float t[32];
 #pragma unroll
@@ -203,48 +246,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tc_fence_before_sync();
         __syncthreads();
         if (tid == 0) {
-            ok = mbar_wait(v_bar, par, abort_flag);
+            ok = mbar_wait(v_bar(bi), par, abort_flag);
             tc_fence_after_sync();
             if (ok) {
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
-                    uint64_t ad = make_smem_desc(smem_u32(sP) + k * 32, 16, 1024);
-                    uint64_t bd = make_smem_desc(smem_u32(sV) + k * (16 * 128), BKV * 128, 1024);
-                    mma_f16(tO, ad, bd, idesc_o, k > 0);
+                    mma_issue<false, false>(tO, DLO(smem_u32(sP), 16, k * 32), kDescHi,
+                                            DLO(smem_u32(sV), BKV * 128, bi * KV_BYTES + k * (16 * 128)), kDescHi, idesc_o, (j > 0 || k > 0));
                 }
                 mma_commit(o_bar);
             }
         }
-        if (!mbar_wait(o_bar, par, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (tid == 0 && j + 1 < n_kv) {                       // V tile is free again
-            mbar_expect_tx(v_bar, KV_BYTES);
-            for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv, v_bar, vcol + c * 64, (j + 1) * BKV, b);
-        }
+    }
+    if (ok && n_kv > 0) ok = mbar_wait(o_bar, (n_kv - 1) & 1, abort_flag);
+    tc_fence_after_sync();
+    if (!ok && tid == 0) atomicOr(p.status, kErrOther);
+
+    if (ok) {
+        const float inv = 1.f / l;
+        bf16* o = p.out + ((static_cast<long long>(b) * p.T + (row < p.T ? row : 0)) * p.Hq + h) * HS;
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < HS / 32; ++c) {
             uint32_t r[32];
             tmem_ld_32x32b_x32(tO + lane_off + c * 32, r);
             tmem_ld_wait();
+            if (row < p.T) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+                for (int g = 0; g < 4; ++g) {
+                    uint4 v;
+                    __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj)
+                        vb[jj] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * jj]) * inv, __uint_as_float(r[g * 8 + 2 * jj + 1]) * inv);
+                    *reinterpret_cast<uint4*>(o + c * 32 + g * 8) = v;
+                }
+            }
         }
-    }
-    if (!ok && tid == 0) atomicOr(p.status, kErrOther);
-
-    if (ok && row < p.T) {
-        const float inv = 1.f / l;
-        bf16* o = p.out + ((static_cast<long long>(b) * p.T + row) * p.Hq + h) * HS;
-#pragma unroll
-        for (int g = 0; g < HS / 8; ++g) {
-            uint4 v;
-            __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) vb[jj] = __floats2bfloat162_rn(acc[g * 8 + 2 * jj] * inv, acc[g * 8 + 2 * jj + 1] * inv);
-            *reinterpret_cast<uint4*>(o + g * 8) = v;
-        }
-        p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + row] = m * p.scale + logf(l);
+        if (row < p.T) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + row] = m_ref * p.scale + logf(l);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -371,15 +410,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
             if (ok) {
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
-                    uint64_t ak = make_smem_desc(smem_u32(sK) + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-                    uint64_t bq = make_smem_desc(smem_u32(sQ) + buf * Q_BYTES + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-                    mma_f16(tS, ak, bq, idesc_st, k > 0);
+                    mma_issue<false, false>(tS, DLO(smem_u32(sK), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi,
+                                            DLO(smem_u32(sQ), 16, buf * Q_BYTES + (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
                 }
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
-                    uint64_t av = make_smem_desc(smem_u32(sV) + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-                    uint64_t bd = make_smem_desc(smem_u32(sdO) + buf * Q_BYTES + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-                    mma_f16(tdP, av, bd, idesc_st, k > 0);
+                    mma_issue<false, false>(tdP, DLO(smem_u32(sV), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi,
+                                            DLO(smem_u32(sdO), 16, buf * Q_BYTES + (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
                 }
                 mma_commit(sp_bar);
             }
@@ -414,15 +451,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
             tc_fence_after_sync();
 #pragma unroll
             for (int k = 0; k < BQ / 16; ++k) {
-                uint64_t ap = make_smem_desc(smem_u32(sPT) + k * 32, 16, 1024);
-                uint64_t bd = make_smem_desc(smem_u32(sdO) + buf * Q_BYTES + k * (16 * 128), BQ * 128, 1024);
-                mma_f16(tdV, ap, bd, idesc_acc, (it > 0 || k > 0));
+                mma_issue<false, false>(tdV, DLO(smem_u32(sPT), 16, k * 32), kDescHi,
+                                        DLO(smem_u32(sdO), BQ * 128, buf * Q_BYTES + k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
             }
 #pragma unroll
             for (int k = 0; k < BQ / 16; ++k) {
-                uint64_t as = make_smem_desc(smem_u32(sdST) + k * 32, 16, 1024);
-                uint64_t bq = make_smem_desc(smem_u32(sQ) + buf * Q_BYTES + k * (16 * 128), BQ * 128, 1024);
-                mma_f16(tdK, as, bq, idesc_acc, (it > 0 || k > 0));
+                mma_issue<false, false>(tdK, DLO(smem_u32(sdST), 16, k * 32), kDescHi,
+                                        DLO(smem_u32(sQ), BQ * 128, buf * Q_BYTES + k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
             }
             mma_commit(acc_bar);
         }
@@ -544,15 +579,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
             if (ok) {
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
-                    uint64_t aq = make_smem_desc(smem_u32(sQ) + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-                    uint64_t bk = make_smem_desc(smem_u32(sK) + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-                    mma_f16(tS, aq, bk, idesc_s, k > 0);
+                    mma_issue<false, false>(tS, DLO(smem_u32(sQ), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
+                                            DLO(smem_u32(sK), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
                 }
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
-                    uint64_t ad = make_smem_desc(smem_u32(sdO) + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-                    uint64_t bv = make_smem_desc(smem_u32(sV) + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-                    mma_f16(tdP, ad, bv, idesc_s, k > 0);
+                    mma_issue<false, false>(tdP, DLO(smem_u32(sdO), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
+                                            DLO(smem_u32(sV), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
                 }
                 mma_commit(sp_bar);
             }
@@ -587,9 +620,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
             tc_fence_after_sync();
 #pragma unroll
             for (int k = 0; k < BKV / 16; ++k) {
-                uint64_t as = make_smem_desc(smem_u32(sdS) + k * 32, 16, 1024);
-                uint64_t bk = make_smem_desc(smem_u32(sK) + k * (16 * 128), BKV * 128, 1024);
-                mma_f16(tdQ, as, bk, idesc_dq, (j > 0 || k > 0));
+                mma_issue<false, false>(tdQ, DLO(smem_u32(sdS), 16, k * 32), kDescHi,
+                                        DLO(smem_u32(sK), BKV * 128, k * (16 * 128)), kDescHi, idesc_dq, (j > 0 || k > 0));
             }
             mma_commit(dq_bar);
         }
@@ -652,7 +684,7 @@ int fwd_impl(void* out, float* lse, const void* qkv, int B, int T, int Hq, int H
     if (rc) return rc;
     rc = encode_btw(&tkv, qkv, B, T, static_cast<long long>(H) * HS, 64);
     if (rc) return rc;
-    constexpr int smem = 128 * HS * 2 + 2 * 64 * HS * 2 + 128 * 64 * 2 + 128;
+    constexpr int smem = 128 * HS * 2 + 4 * 64 * HS * 2 + 128 * 64 * 2 + 128;
     rc = set_smem<HS>(attn_fwd_kernel<HS>, smem);
     if (rc) return rc;
     AttnParams p{};
