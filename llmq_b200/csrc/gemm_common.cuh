@@ -20,6 +20,12 @@ struct GemmParams {
     float alpha;
     float* absmax_out;     // optional
     unsigned int* status;  // error word
+    // Optional: rows of B arrive from other GPUs (fused all-gather).  ready_flags[src] >= ready_gen means the rows
+    // [src * ready_rows_per_src, (src+1) * ready_rows_per_src) of the stored B matrix are complete in local memory.
+    const unsigned int* ready_flags;
+    unsigned int ready_gen;
+    int ready_rows_per_src;
+    unsigned long long ready_limit_ns;
 };
 
 // Each lane of the calling warp owns one accumulator row (TMEM lane); `t_row` addresses column 0 of that row

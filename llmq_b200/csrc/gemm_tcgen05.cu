@@ -239,6 +239,9 @@ int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
 static int g_gemm_mode = 0;
 extern "C" void llmq_gemm_set_mode(int mode) { g_gemm_mode = mode; }
 
+extern "C" int llmq_gemm_ready(const void*, const void*, void*, const void*, int, int, int, int, int, int, int, long long, long long, long long, int, int, int,
+                               const float*, const float*, float, float*, unsigned int*, int, const unsigned int*, unsigned int, int, double, cudaStream_t);
+
 extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias,
                          int M, int N, int K,
                          int ab_dtype,            // 0 bf16, 1 e4m3, 2 e5m2 (A), B shares the width
@@ -248,6 +251,18 @@ extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias
                          int c_dtype, int bias_dtype, int accumulate,
                          const float* scale_a, const float* scale_b, float alpha,
                          float* absmax_out, unsigned int* status, int num_sms, cudaStream_t stream) {
+    return llmq_gemm_ready(A, B, C, bias, M, N, K, ab_dtype, b_dtype, a_mn_major, b_mn_major, lda, ldb, ldc, c_dtype, bias_dtype, accumulate,
+                           scale_a, scale_b, alpha, absmax_out, status, num_sms, nullptr, 0u, 0, 0.0, stream);
+}
+
+// Same, with the fused all-gather hook: rows of the stored B matrix are written by peer GPUs; ready_flags[src]
+// reaching ready_gen marks source src's rows complete.  The producer warps poll the flags tile by tile.
+extern "C" int llmq_gemm_ready(const void* A, const void* B, void* C, const void* bias,
+                               int M, int N, int K, int ab_dtype, int b_dtype, int a_mn_major, int b_mn_major,
+                               long long lda, long long ldb, long long ldc, int c_dtype, int bias_dtype, int accumulate,
+                               const float* scale_a, const float* scale_b, float alpha, float* absmax_out, unsigned int* status,
+                               int num_sms, const unsigned int* ready_flags, unsigned int ready_gen, int ready_rows_per_src,
+                               double ready_limit_s, cudaStream_t stream) {
     const int eb = ab_dtype == 0 ? 2 : 1;
     if ((b_dtype == 0 ? 2 : 1) != eb) return -2;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -262,7 +277,7 @@ extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias
     else             rc = llmq_encode_tmap_2d(&ta, A, eb, K, M, lda, bk);
     if (rc) return rc;
     // The CTA-pair kernel stages 128 rows of B per CTA; the one-CTA kernel stages all 256.
-    const bool pair_kernel = g_gemm_mode == 2 || (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32);
+    const bool pair_kernel = ready_flags != nullptr || g_gemm_mode == 2 || (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32);
     if (!b_mn_major) rc = llmq_encode_tmap_2d(&tb, B, eb, N, K, ldb, pair_kernel ? 128 : BN);
     else             rc = llmq_encode_tmap_2d(&tb, B, eb, K, N, ldb, bk);
     if (rc) return rc;
@@ -276,6 +291,8 @@ extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.scale_a = scale_a; p.scale_b = scale_b; p.alpha = alpha;
     p.absmax_out = absmax_out; p.status = status;
+    p.ready_flags = ready_flags; p.ready_gen = ready_gen; p.ready_rows_per_src = ready_rows_per_src > 0 ? ready_rows_per_src : 1;
+    p.ready_limit_ns = static_cast<unsigned long long>(ready_limit_s * 1e9);
 
     if (pair_kernel) return llmq_gemm_2cta_launch(ta, tb, p, num_sms, stream);
 

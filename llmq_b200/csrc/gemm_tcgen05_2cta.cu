@@ -13,6 +13,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "gemm_common.cuh"
+#include "peer_sync.cuh"
 
 using namespace sm100;
 
@@ -94,11 +95,30 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             int stage = 0; uint32_t phase = 0;
             const int mn_chunk = ROW_BYTES / p.elem_bytes;
             bool ok = true;
+            // Fused all-gather: B rows pushed by peer GPUs are consumed as soon as their source's flag shows the
+            // current generation.  `seen` caches the sources already confirmed.
+            uint32_t seen = 0;
+            auto ensure_src = [&](int src) {
+                if (!(seen >> src & 1u)) {
+                    if (!peer::wait_flag(p.ready_flags + src, p.ready_gen, p.ready_limit_ns)) { atomicOr(p.status, kErrPeerFlag); *abort_flag = 1u; ok = false; }
+                    peer::fence_before_tma_reads();
+                    seen |= 1u << src;
+                }
+            };
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
                 const int row0 = (tm * 2 + static_cast<int>(rank)) * BM;               // this CTA's rows of A / C
                 const int brow0 = tn * BN + static_cast<int>(rank) * BN_HALF;          // this CTA's rows of B
-                for (int k = 0; k < k_iters; ++k) {
+                if (p.ready_flags && !p.b_mn_major && brow0 < p.N) {
+                    const int last = min(brow0 + BN_HALF, p.N) - 1;
+                    for (int src = brow0 / p.ready_rows_per_src; src <= last / p.ready_rows_per_src && ok; ++src) ensure_src(src);
+                }
+                for (int k = 0; k < k_iters && ok; ++k) {
+                    if (p.ready_flags && p.b_mn_major) {
+                        const int last = min(k * bk + bk, p.K) - 1;
+                        for (int src = (k * bk) / p.ready_rows_per_src; src <= last / p.ready_rows_per_src && ok; ++src) ensure_src(src);
+                        if (!ok) break;
+                    }
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrEmptyWait); ok = false; break; }
                     const uint32_t sa = smem_base + stage * STAGE_BYTES;
                     const uint32_t sb = sa + A_STAGE_BYTES;

@@ -19,30 +19,16 @@
 #include "api.h"
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "peer_sync.cuh"
 
 namespace {
 
 constexpr int MAX_PEERS = 8;
 struct PeerTable { void* base[MAX_PEERS]; };
 
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// true when *p >= target was seen within the limit (generation numbers only grow; wrap-around safe compare)
-__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int target, uint64_t limit_ns) {
-    const uint64_t t0 = sm100::globaltimer_ns();
-    unsigned int spins = 0;
-    while (static_cast<int>(ld_acquire_sys(p) - target) < 0) {
-        if ((++spins & 63u) == 0u && sm100::globaltimer_ns() - t0 > limit_ns) return false;
-        __nanosleep(64);
-    }
-    return true;
-}
+using peer::st_release_sys;
+using peer::ld_acquire_sys;
+using peer::wait_flag;
 
 // ------------------------------------------------------------------------------------------------
 // quantise (or copy) the local shard and store it into every rank's gather buffer

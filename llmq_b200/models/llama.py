@@ -181,21 +181,21 @@ class LlamaModel:
         self.weights.invalidate()
 
     # ================================================================================== quantised matmuls
-    def _fwd_mm(self, out, act, act_q, slot, W, w_scale, bias=None):
+    def _fwd_mm(self, out, act, act_q, slot, W, w_scale, bias=None, ready=None):
         if not self.quant:
-            K.gemm(out, act, W, bias=bias)
+            K.gemm(out, act, W, bias=bias, ready=ready)
             return
         am, sc = slot
         if act is not None:
             K.quantize(act_q, sc, act, am)
-        K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale)
+        K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale, ready=ready)
 
-    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate):
+    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None):
         """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
         W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second."""
         if not self.quant:
             if dinp is not None:
-                K.gemm(dinp, dout, W, b_mn=True)
+                K.gemm(dinp, dout, W, b_mn=True, ready=ready)
             K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate)
             if dbias is not None:
                 K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
@@ -203,7 +203,7 @@ class LlamaModel:
         am, sc = slot
         K.quantize(dout_q, sc, dout, am)
         if dinp is not None:
-            K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale)
+            K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
         K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
         if dbias is not None:
             K.bias_backward(dbias, dout_q, self.tmp.bias_scratch, scale_a=sc, accumulate=True)
@@ -238,18 +238,18 @@ class LlamaModel:
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         BT = self.B * self.T
         qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
-        self._fwd_mm(qkv2d, a.ln1[l], a.ln1_q[l] if self.quant else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b)
+        self._fwd_mm(qkv2d, a.ln1[l], a.ln1_q[l] if self.quant else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b, ready=p.ready["qkv_w"])
         K.rope(a.qkv[l], a.qkv[l], self.freqs, Hq, Hkv)
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
         K.attention_forward(att4, a.lse[l], a.qkv[l], Hq, Hkv)
         if self.quant:
             K.abs_max(self._slot(l, S_ATT)[0], a.att[l])
-        self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"])
+        self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
         K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
                           absmax=self._slot(l, S_LN2)[0])
-        self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"])
+        self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
         K.swiglu_forward(a.swiglu[l], a.up[l], absmax=self._slot(l, S_SWIGLU)[0])
-        self._fwd_mm(t.proj, a.swiglu[l], a.swiglu_q[l] if self.quant else None, self._slot(l, S_SWIGLU), p.down_w, p.scales["down_w"])
+        self._fwd_mm(t.proj, a.swiglu[l], a.swiglu_q[l] if self.quant else None, self._slot(l, S_SWIGLU), p.down_w, p.scales["down_w"], ready=p.ready["down_w"])
 
     # ================================================================================== validation
     @torch.no_grad()
@@ -357,7 +357,7 @@ class LlamaModel:
             renorm(a.ln1[l], a.ln1_q[l] if q else None, S_LN1, a.x[l], p.ln1_w, a.rstd1[l])
         if re.qkv:
             qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
-            self._fwd_mm(qkv2d, None if q else a.ln1[l], a.ln1_q[l] if q else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b)
+            self._fwd_mm(qkv2d, None if q else a.ln1[l], a.ln1_q[l] if q else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b, ready=p.ready["qkv_w"])
             if not q:
                 pass
             K.rope(a.qkv[l], a.qkv[l], self.freqs, Hq, Hkv)
@@ -368,7 +368,7 @@ class LlamaModel:
             am, sc = self._slot(l, S_ATT)
             K.quantize(a.att_q[l], sc, a.att[l], am)
         if re.block:
-            self._fwd_mm(t.proj, None if q else a.att[l], a.att_q[l] if q else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"])
+            self._fwd_mm(t.proj, None if q else a.att[l], a.att_q[l] if q else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
             am, sc = self._slot(l, S_LN2)
             if q:
                 K.rmsnorm_forward(None, None, a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
@@ -378,7 +378,7 @@ class LlamaModel:
         elif re.ln2:
             renorm(a.ln2[l], a.ln2_q[l] if q else None, S_LN2, a.res_att[l], p.ln2_w, a.rstd2[l])
         if re.up:
-            self._fwd_mm(a.up[l], None if q else a.ln2[l], a.ln2_q[l] if q else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"])
+            self._fwd_mm(a.up[l], None if q else a.ln2[l], a.ln2_q[l] if q else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
         if re.sw:
             am, sc = self._slot(l, S_SWIGLU)
             if q:
@@ -393,18 +393,18 @@ class LlamaModel:
         sc_of = lambda s: self._slot(l, s)[1]
         # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
-                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc)
+                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"])
         # ---- SwiGLU backward, in place over the saved up-projection
         K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
         # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
-                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc)
+                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"])
         # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
         K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],
                            absmax=self._slot(l, S_DRESATT)[0], accumulate_dweight=True)
         # ---- attention out projection
         self._bwd_mm(t.d_ln, dw["o_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESATT),
-                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc)
+                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc, ready=p.ready["o_w"])
         # ---- attention core
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
         K.attention_backward(t.d_qkv, t.att_scratch, t.d_ln.view(self.B, self.T, Hq, cfg.head_size), att4, a.lse[l], a.qkv[l], Hq, Hkv)
@@ -412,7 +412,7 @@ class LlamaModel:
         # ---- QKV projection
         dqkv2d = t.d_qkv.view(BT, cfg.qkv_channels)
         self._bwd_mm(t.d_ln, dw["qkv_w"], dw.get("qkv_b"), dqkv2d, t.d_qkv_q if q else None, self._slot(l, S_DQKV),
-                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc)
+                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc, ready=p.ready["qkv_w"])
 
     # ================================================================================== optimizer
     def update(self, lr: float, beta1: float = 0.9, beta2: float = 0.95, step: int = 1, eps: float = 1e-8,

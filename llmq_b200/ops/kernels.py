@@ -74,8 +74,12 @@ def _is_f8(dt):
 # GEMM
 def gemm(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          bias: Optional[torch.Tensor] = None, accumulate: bool = False, scale_a: Optional[torch.Tensor] = None,
-         scale_b: Optional[torch.Tensor] = None, alpha: float = 1.0, absmax: Optional[torch.Tensor] = None) -> None:
+         scale_b: Optional[torch.Tensor] = None, alpha: float = 1.0, absmax: Optional[torch.Tensor] = None,
+         ready=None) -> None:
     """out[M,N] (+)= alpha * scale_a * scale_b * A @ B^T + bias.
+
+    ``ready`` = (flag address, generation, rows per source rank, limit in seconds): the rows of the stored ``b`` are
+    being written by peer GPUs (fused all-gather); the kernel's producer polls the flags tile by tile.
 
     ``a`` holds the logical [M,K] operand either as [M,K] (K-major) or, with ``a_mn``, as [K,M];
     likewise ``b`` holds logical [N,K] as [N,K] or, with ``b_mn``, as [K,N].  2-D, last dim contiguous.
@@ -87,12 +91,13 @@ def gemm(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = Fa
     if out.is_cuda:
         st = _dev_state(out.device)
         assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
-        rc = L.kernels().llmq_gemm(
+        rflags, rgen, rrows, rlimit = ready if ready is not None else (0, 0, 0, 0.0)
+        rc = L.kernels().llmq_gemm_ready(
             L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(bias), M, N, K, L.dtype_code(a.dtype), L.dtype_code(b.dtype),
             int(a_mn), int(b_mn), _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
             0 if out.dtype == torch.bfloat16 else 1, 0 if (bias is None or bias.dtype == torch.bfloat16) else 1,
             int(accumulate), L.ptr(scale_a), L.ptr(scale_b), _f(alpha), L.ptr(absmax), L.ptr(st["status"]), st["sms"],
-            L.stream_ptr())
+            ctypes.c_void_p(rflags), ctypes.c_uint(rgen), int(rrows), ctypes.c_double(rlimit), L.stream_ptr())
         L.check(rc, "gemm")
         return
     af = a.float().t() if a_mn else a.float()

@@ -219,6 +219,7 @@ class WeightsManager:
         if self.quant_shards is not None:
             self.quant_version[l] = self.version
         buf.pending = _WorkList(works)
+        buf.ready = None
         buf.layer, buf.version = l, self.version
 
     def _gather_block_fused(self, l: int, buf: _Buf) -> None:
@@ -226,23 +227,32 @@ class WeightsManager:
         Side stream: barrier (all ranks are past the previous user of this buffer) -> pushes -> data flag."""
         f = self.fused
         idx = self.bufs.index(buf)
-        ch_free, ch_data = CH_WEIGHTS + 2 * idx, CH_WEIGHTS + 2 * idx + 1
+        ch_free, ch_vec, ch_mat = CH_WEIGHTS + 3 * idx, CH_WEIGHTS + 3 * idx + 1, CH_WEIGHTS + 3 * idx + 2
         main = torch.cuda.current_stream(self.device)
         f.stream.wait_stream(main)
         with torch.cuda.stream(f.stream):
             f.wait(ch_free, f.signal(ch_free))
+            # the small vectors first: their flag is awaited by a tiny kernel before the layer starts; the matrices'
+            # flags are polled by the consuming GEMMs themselves, tile by tile
             for s in self.block_specs:
-                full = buf.t[s.name]
-                master = self.master_blocks[l][s.name]
-                if s.name in MATRICES and self.quantized:
-                    st = self._stat(l, s.name)
-                    f.quant_allgather(full, master, st[0:1], st[1:2])
-                else:
-                    f.quant_allgather(full, master)
-            gen = f.signal(ch_data)
+                if s.name not in MATRICES:
+                    f.quant_allgather(buf.t[s.name], self.master_blocks[l][s.name])
+            gen_vec = f.signal(ch_vec)
+            for s in self.block_specs:
+                if s.name in MATRICES:
+                    full = buf.t[s.name]
+                    master = self.master_blocks[l][s.name]
+                    if self.quantized:
+                        st = self._stat(l, s.name)
+                        f.quant_allgather(full, master, st[0:1], st[1:2])
+                    else:
+                        f.quant_allgather(full, master)
+            gen_mat = f.signal(ch_mat)
             ev = torch.cuda.Event()
             ev.record(f.stream)
-        buf.pending = _FusedPending(f, ch_data, gen, ev, self.device)
+        buf.pending = _FusedPending(f, ch_vec, gen_vec, ev, self.device)
+        buf.ready = {n: (f.ctrl.base + f._flag_offset(ch_mat), gen_mat, buf.t[n].shape[0] // self.comm.world, f.wait_limit_s)
+                     for n in MATRICES}
         buf.layer, buf.version = l, self.version
 
     def get_block(self, l: int) -> SimpleNamespace:
@@ -254,6 +264,7 @@ class WeightsManager:
             buf.pending = None
         buf.in_use = True
         ns = SimpleNamespace(**buf.t)
+        ns.ready = getattr(buf, "ready", None) or {n: None for n in MATRICES}
         ns.scales = {n: self._stat(l, n)[1:2] for n in MATRICES} if self.quantized else {n: None for n in MATRICES}
         if not hasattr(ns, "qkv_b"):
             ns.qkv_b = None
