@@ -14,6 +14,7 @@ layout used by the reference (src/utilities/tensor.cpp:113-120).  Capabilities m
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from types import SimpleNamespace
 from typing import Dict, List, Optional
@@ -250,9 +251,16 @@ class WeightsManager:
             gen_mat = f.signal(ch_mat)
             ev = torch.cuda.Event()
             ev.record(f.stream)
-        buf.pending = _FusedPending(f, ch_vec, gen_vec, ev, self.device)
-        buf.ready = {n: (f.ctrl.base + f._flag_offset(ch_mat), gen_mat, buf.t[n].shape[0] // self.comm.world, f.wait_limit_s)
-                     for n in MATRICES}
+        if os.environ.get("LLMQ_GEMM_POLL", "0") != "1":
+            # Default: one wait kernel for the whole block in front of the layer.  With the prefetch depth of one layer
+            # the data has long arrived, and polling the flags inside every GEMM measured 30 ms / step slower on
+            # Qwen2.5-7B (571 vs 540 ms, 2 GPUs); LLMQ_GEMM_POLL=1 switches the in-GEMM polling on.
+            buf.pending = _FusedPending(f, ch_mat, gen_mat, ev, self.device)
+            buf.ready = None
+        else:
+            buf.pending = _FusedPending(f, ch_vec, gen_vec, ev, self.device)
+            buf.ready = {n: (f.ctrl.base + f._flag_offset(ch_mat), gen_mat, buf.t[n].shape[0] // self.comm.world, f.wait_limit_s)
+                         for n in MATRICES}
         buf.layer, buf.version = l, self.version
 
     def get_block(self, l: int) -> SimpleNamespace:
