@@ -24,6 +24,7 @@ from ..config import TransformerConfig
 from ..ops import kernels as K
 from ..options import LLamaOptions
 from ..parallel.comm import Communicator, LocalComm
+from ..parallel.offload import ResidualStore, Stager
 from ..parallel.zero import F8_TYPES, MATRICES, GradientManager, OptimizerStateManager, WeightsManager
 
 # abs-max slots per layer: index -> (absmax, scale)
@@ -52,6 +53,7 @@ class LlamaModel:
         self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
         self.opt_state = OptimizerStateManager(cfg, opts, self.comm, self.device, self.weights)
         self._alloc_run_state()
+        self._stager = Stager(self.device)
         self.adam_seed = 42
         self.rng_state = 42                       # advanced every optimizer step; saved in checkpoints
 
@@ -103,7 +105,7 @@ class LlamaModel:
             return [z(*shape, dtype=dtype) for _ in range(L)]
 
         a = SimpleNamespace()
-        a.x = [z(BT, C) for _ in range(L + 1)]                         # residual stream entering each layer (+ final)
+        a.x = ResidualStore(L + 1, (BT, C), dt, dev, o.offload_residual)     # residual stream entering each layer (+ final)
         a.rstd1 = per_layer(False, BT, dtype=torch.float32)
         a.rstd2 = per_layer(False, BT, dtype=torch.float32)
         a.lse = per_layer(False, B, Hq, T, dtype=torch.float32)
@@ -215,7 +217,8 @@ class LlamaModel:
         L = cfg.num_hidden_layers
         if inputs is not None:                    # None: the caller already placed the tokens in self.inputs
             self.inputs.copy_(inputs.reshape(self.B, self.T), non_blocking=True)
-        K.encoder_forward(a.x[0], self.inputs, w.get_embeddings())
+        K.encoder_forward(a.x.write_target(0), self.inputs, w.get_embeddings())
+        a.x.written(0)
         self.stats.zero_()
         w.gather_block(0)
         for l in range(L):
@@ -224,14 +227,16 @@ class LlamaModel:
             p = w.get_block(l)
             am, _ = self._slot(l, S_LN1)
             if l == 0:
-                K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.x[0], p.ln1_w, cfg.rms_norm_eps, absmax=am)
+                K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.x.current(0), p.ln1_w, cfg.rms_norm_eps, absmax=am)
             else:
-                K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.res_att[l - 1], p.ln1_w, cfg.rms_norm_eps, residual_out=a.x[l],
+                K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.res_att[l - 1], p.ln1_w, cfg.rms_norm_eps, residual_out=a.x.write_target(l),
                                   inp2=self.tmp.proj, absmax=am)
+                a.x.written(l)
             self._forward_block(l, p)
             w.release_block(l)
-        K.rmsnorm_forward(self.lnf, self.rstd_f, a.res_att[L - 1], w.get_lnf(), cfg.rms_norm_eps, residual_out=a.x[L],
+        K.rmsnorm_forward(self.lnf, self.rstd_f, a.res_att[L - 1], w.get_lnf(), cfg.rms_norm_eps, residual_out=a.x.write_target(L),
                           inp2=self.tmp.proj)
+        a.x.written(L)
 
     def _forward_block(self, l: int, p) -> None:
         cfg, a, t = self.cfg, self.acts, self.tmp
@@ -245,7 +250,7 @@ class LlamaModel:
         if self.quant:
             K.abs_max(self._slot(l, S_ATT)[0], a.att[l])
         self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
-        K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
+        K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x.current(l), p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
                           absmax=self._slot(l, S_LN2)[0])
         self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
         K.swiglu_forward(a.swiglu[l], a.up[l], absmax=self._slot(l, S_SWIGLU)[0])
@@ -317,12 +322,13 @@ class LlamaModel:
         self._lmhead(write_grads=True, dloss=dloss, z_loss=z_loss, accumulate_dw=micro_step > 0)
         # final norm: t.d_ln holds d(lnf); produce d(residual stream) in t.d_res
         t.d_res.zero_()
-        K.rmsnorm_backward(t.d_res, g.nb_full["lnf_w"], t.norm_scratch, t.d_ln, a.x[L], w.get_lnf(), self.rstd_f,
+        K.rmsnorm_backward(t.d_res, g.nb_full["lnf_w"], t.norm_scratch, t.d_ln, a.x.get(L), w.get_lnf(), self.rstd_f,
                            absmax=self._slot(L - 1, S_DRESFFN)[0], accumulate_dweight=True)
         g.notify_non_block("lnf_w")
         w.gather_block(L - 1)
         for l in range(L - 1, -1, -1):
             dw, acc = g.get_block_full(l)
+            a.x.prefetch(l - 1)
             if l > 0:
                 w.gather_block(l - 1)
             p = w.get_block(l)
@@ -330,7 +336,7 @@ class LlamaModel:
             self._backward_block(l, p, dw, acc)
             # LN1 backward adds into the residual gradient, which then belongs to layer l-1 (or the embedding)
             slot = self._slot(l - 1, S_DRESFFN)[0] if l > 0 else None
-            K.rmsnorm_backward(t.d_res, dw["ln1_w"], t.norm_scratch, t.d_ln, a.x[l], p.ln1_w, a.rstd1[l], absmax=slot,
+            K.rmsnorm_backward(t.d_res, dw["ln1_w"], t.norm_scratch, t.d_ln, a.x.get(l), p.ln1_w, a.rstd1[l], absmax=slot,
                                accumulate_dweight=True)
             w.release_block(l)
             g.notify_block(l)
@@ -354,7 +360,7 @@ class LlamaModel:
                 K.rmsnorm_forward(y, None, x, wt, cfg.rms_norm_eps)
 
         if re.ln1:
-            renorm(a.ln1[l], a.ln1_q[l] if q else None, S_LN1, a.x[l], p.ln1_w, a.rstd1[l])
+            renorm(a.ln1[l], a.ln1_q[l] if q else None, S_LN1, a.x.get(l), p.ln1_w, a.rstd1[l])
         if re.qkv:
             qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
             self._fwd_mm(qkv2d, None if q else a.ln1[l], a.ln1_q[l] if q else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b, ready=p.ready["qkv_w"])
@@ -371,10 +377,10 @@ class LlamaModel:
             self._fwd_mm(t.proj, None if q else a.att[l], a.att_q[l] if q else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
             am, sc = self._slot(l, S_LN2)
             if q:
-                K.rmsnorm_forward(None, None, a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
+                K.rmsnorm_forward(None, None, a.x.get(l), p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
                                   q_out=a.ln2_q[l], known_absmax=am, q_scale=sc)
             else:
-                K.rmsnorm_forward(a.ln2[l], None, a.x[l], p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj)
+                K.rmsnorm_forward(a.ln2[l], None, a.x.get(l), p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj)
         elif re.ln2:
             renorm(a.ln2[l], a.ln2_q[l] if q else None, S_LN2, a.res_att[l], p.ln2_w, a.rstd2[l])
         if re.up:
@@ -438,12 +444,42 @@ class LlamaModel:
         # ---- AdamW on every shard
         w.zero_absmax()
         seed_base = (self.rng_state * 1000003) & 0x7FFFFFFF
-        for idx, (name, master, spec, l) in enumerate(w.master_items()):
-            gs = shard_of[name]
-            m, v, ms = o.m[name], o.v[name], o.m_scales.get(name)
+        items = list(w.master_items())
+        stager = self._stager
+        staged = [None] * len(items)
+
+        def prefetch(i):
+            name, master, spec, l = items[i]
+            par = i & 1
+            staged[i] = (stager.fetch(master, "p", par), stager.fetch(shard_of[name], "g", par),
+                         stager.fetch(o.m[name], "m", par), stager.fetch(o.v[name], "v", par))
+
+        if items:
+            prefetch(0)
+        main = torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
+        for idx, (name, master, spec, l) in enumerate(items):
+            if idx + 1 < len(items):
+                prefetch(idx + 1)                      # H2D of the next tensor's state overlaps this tensor's update
+            (pm, e0), (gm, e1), (mm, e2), (vm, e3) = staged[idx]
+            staged[idx] = None
+            for e in (e0, e1, e2, e3):
+                if e is not None:
+                    main.wait_event(e)
+            ms = o.m_scales.get(name)
             wd = weight_decay if spec.matrix else 0.0
             am = w._stat(l, spec.name)[0:1] if (l is not None and spec.name in MATRICES and w.quantized) else None
-            self._adam_one(master, gs, m, v, ms, lr, beta1, beta2, step, eps, wd, scale, am, seed_base + idx * 7919, name)
+            n = pm.numel()
+            if n % 8:
+                raise ValueError(f"parameter shard {name} has {n} elements; shard sizes must be multiples of 8")
+            K.adamw(pm.view(-1), gm.view(-1), mm.view(-1), vm.view(-1), lr=lr, beta1=beta1, beta2=beta2, step=step, eps=eps,
+                    weight_decay=wd, grad_scale=scale, absmax=am, m_scales=ms, seed=seed_base + idx * 7919,
+                    elem_offset=self.comm.rank * master.numel())
+            par = idx & 1
+            stager.mark_consumed(par)
+            stager.store(pm, master, "p", par)
+            stager.store(mm, o.m[name], "m", par)
+            stager.store(vm, o.v[name], "v", par)
+        stager.finish()
         w.sync_absmax(recompute=False)
         w.invalidate()
         g.end_step()
@@ -456,25 +492,6 @@ class LlamaModel:
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
         return {"loss": loss, "loss_1k": loss1k, "norm": float(hs[0]), "z_max": float(hs[2]), "z_mean": float(hs[3]) / ntok}
-
-    def _adam_one(self, master, grad, m, v, ms, lr, b1, b2, step, eps, wd, scale, absmax, seed, name) -> None:
-        """One tensor; host-resident pieces are staged through the device (H2D, update, D2H)."""
-        dev = self.device
-
-        def stage(t):
-            return t if t.device.type == dev.type else t.to(dev, non_blocking=True)
-
-        pm, gm, mm, vm = stage(master), stage(grad), stage(m), stage(v)
-        offset = self.comm.rank * master.numel()
-        n = pm.numel()
-        if n % 8 == 0:
-            K.adamw(pm.view(-1), gm.view(-1), mm.view(-1), vm.view(-1), lr=lr, beta1=b1, beta2=b2, step=step, eps=eps,
-                    weight_decay=wd, grad_scale=scale, absmax=absmax, m_scales=ms, seed=seed, elem_offset=offset)
-        else:
-            raise ValueError(f"parameter shard {name} has {n} elements; shard sizes must be multiples of 8")
-        for src, dst in ((pm, master), (mm, m), (vm, v)):
-            if src is not dst:
-                dst.copy_(src, non_blocking=True)
 
     # ================================================================================== introspection
     def get_gradients(self) -> Dict[str, torch.Tensor]:

@@ -141,6 +141,8 @@ def allocator_report(model) -> Dict[str, Dict[str, int]]:
     for t in g.nb_full.values():
         _add(rep, "Gradients", t, seen)
     for v in vars(model.acts).values():
+        if hasattr(v, "dev"):                                   # ResidualStore
+            v = list(v.dev) + list(getattr(v, "host", []))
         for t in (v if isinstance(v, list) else [v]):
             if isinstance(t, torch.Tensor):
                 _add(rep, "Activations", t, seen)

@@ -70,7 +70,10 @@ def test_step_matches_oracle(mm, hs, tied):
 
 @pytest.mark.parametrize("mm", [None, "e4m3"])
 @pytest.mark.parametrize("kw", [dict(recompute_swiglu=True), dict(recompute_block=True), dict(recompute_att=True, recompute_ffn=True),
-                                dict(recompute_rms_norm=True, recompute_qkv=True), dict(shard_weights=True, shard_gradients=True)],
+                                dict(recompute_rms_norm=True, recompute_qkv=True), dict(shard_weights=True, shard_gradients=True),
+                                dict(offload_master=True, offload_opt_m=True, offload_opt_v=True),
+                                dict(offload_residual=True, recompute_block=True),
+                                dict(shard_weights=True, persistent_quants=True, offload_quants=True, offload_master=True)],
                          ids=lambda d: "+".join(d))
 def test_variants_bit_identical_on_gpu(kw, mm):
     base = run(LLamaOptions(matmul_type=mm))[2]
