@@ -618,3 +618,50 @@ def attention_backward(dqkv: torch.Tensor, scratch: Optional[torch.Tensor], dout
     o, _ = _attention_ref(x, Hq, Hkv)
     (g,) = torch.autograd.grad(o, x, dout.float())
     dqkv.copy_(g.to(dqkv.dtype))
+
+
+# =====================================================================================================
+# QK-norm (kernel API parity; not used by the Llama / Qwen2 training path)
+def qk_norm_forward(out: torch.Tensor, rstd: torch.Tensor, qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor,
+                    eps: float, Hq: int, Hkv: int) -> None:
+    """Per-head RMSNorm of the q and k heads of packed (B,T,Hq+2Hkv,HS); v heads of ``out`` are left as they are
+    (pass ``out = qkv`` for the in-place form).  rstd: (B*T, Hq+Hkv)."""
+    B, T, H, HS = qkv.shape
+    if qkv.is_cuda:
+        L.check(L.kernels().llmq_qk_norm_forward(L.ptr(out), L.ptr(rstd), L.ptr(qkv), L.ptr(q_weight), L.ptr(k_weight), _f(eps), _ll(B * T),
+                                                 Hq, Hkv, HS, L.dtype_code(qkv.dtype), L.stream_ptr()), "qk_norm_forward")
+        return
+    x = qkv.float()[:, :, :Hq + Hkv]
+    rs = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    w = torch.cat([q_weight.float().expand(Hq, HS), k_weight.float().expand(Hkv, HS)], 0)
+    y = ((x * rs).to(qkv.dtype).float() * w).to(out.dtype)
+    out[:, :, :Hq + Hkv] = y
+    rstd.copy_(rs.reshape(rstd.shape))
+
+
+def qk_norm_backward(dqkv: torch.Tensor, dq_weight: torch.Tensor, dk_weight: torch.Tensor, scratch: Optional[torch.Tensor], dout: torch.Tensor,
+                     qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, rstd: torch.Tensor, Hq: int, Hkv: int,
+                     accumulate: bool = False) -> None:
+    """Gradient of :func:`qk_norm_forward` for the q and k heads (v heads of ``dqkv`` untouched); scratch: 128*2*HS floats."""
+    B, T, H, HS = qkv.shape
+    if qkv.is_cuda:
+        slices = 128
+        assert scratch is not None and scratch.numel() >= slices * 2 * HS
+        L.check(L.kernels().llmq_qk_norm_backward(L.ptr(dqkv), L.ptr(dq_weight), L.ptr(dk_weight), L.ptr(scratch), L.ptr(dout), L.ptr(qkv),
+                                                  L.ptr(q_weight), L.ptr(k_weight), L.ptr(rstd), _ll(B * T), Hq, Hkv, HS, slices,
+                                                  int(accumulate), L.dtype_code(qkv.dtype), L.stream_ptr()), "qk_norm_backward")
+        return
+    HN = Hq + Hkv
+    x = qkv.float()[:, :, :HN]
+    dy = dout.float()[:, :, :HN]
+    rs = rstd.float().reshape(B, T, HN, 1)
+    w = torch.cat([q_weight.float().expand(Hq, HS), k_weight.float().expand(Hkv, HS)], 0)
+    xh = x * rs
+    dot = (w * dy * xh).mean(-1, keepdim=True)
+    dqkv[:, :, :HN] = ((w * dy - xh * dot) * rs).to(dqkv.dtype)
+    dwq = (dy[:, :, :Hq] * xh[:, :, :Hq]).sum((0, 1, 2))
+    dwk = (dy[:, :, Hq:] * xh[:, :, Hq:]).sum((0, 1, 2))
+    if accumulate:
+        dwq, dwk = dwq + dq_weight.float(), dwk + dk_weight.float()
+    dq_weight.copy_(dwq.to(dq_weight.dtype))
+    dk_weight.copy_(dwk.to(dk_weight.dtype))

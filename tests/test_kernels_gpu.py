@@ -307,3 +307,23 @@ def test_attention(HS, Hq, Hkv, T):
     close(res[1][0], res[0][0], rtol=2e-2, atol=2e-2)
     close(res[1][1], res[0][1], rtol=1e-3, atol=1e-2)
     close(res[1][2], res[0][2], rtol=3e-2, atol=3e-2)
+
+
+def test_qk_norm():
+    torch.manual_seed(13)
+    B, T, Hq, Hkv, HS = 2, 40, 4, 2, 64
+    qkv = torch.randn(B, T, Hq + 2 * Hkv, HS).to(BF)
+    dout = torch.randn_like(qkv.float()).to(BF)
+    qw, kw = (1 + 0.1 * torch.randn(HS)).to(BF), (1 + 0.1 * torch.randn(HS)).to(BF)
+    res = []
+    for dev in ("cpu", DEV):
+        out = qkv.clone().to(dev)
+        rstd = torch.zeros(B * T, Hq + Hkv, device=dev)
+        K.qk_norm_forward(out, rstd, qkv.to(dev), qw.to(dev), kw.to(dev), 1e-6, Hq, Hkv)
+        dqkv = torch.zeros_like(out)
+        dqw, dkw = torch.zeros(HS, dtype=BF, device=dev), torch.zeros(HS, dtype=BF, device=dev)
+        K.qk_norm_backward(dqkv, dqw, dkw, torch.zeros(128 * 2 * HS, device=dev), dout.to(dev), qkv.to(dev), qw.to(dev), kw.to(dev), rstd, Hq, Hkv)
+        res.append((out, rstd, dqkv, dqw, dkw))
+    for g, r in zip(res[1], res[0]):
+        close(g, r, rtol=2e-2, atol=2e-2)
+    assert torch.equal(res[1][0][:, :, Hq + Hkv:].cpu(), qkv[:, :, Hq + Hkv:])
