@@ -26,13 +26,30 @@ struct GemmParams {
     unsigned int ready_gen;
     int ready_rows_per_src;
     unsigned long long ready_limit_ns;
+    // Optional: reduce-scatter fused into the kernel (CTA-pair kernel only).  Output row r belongs to rank
+    // r / rs_shard_rows; the epilogue stores it into that rank's landing buffer, slot [this rank], over NVLink and
+    // bumps the owner's arrival counter; after its last tile every CTA helps to sum this rank's `rs_world` slots
+    // into the gradient shard.  rs_world == 0 switches all of this off.
+    int rs_world, rs_rank, rs_shard_rows;
+    void* rs_landing[8];            // landing buffer of every rank: [rs_world][rs_shard_rows][N] bf16
+    unsigned int* rs_counter[8];    // arrival counter word of every rank
+    unsigned int rs_target;         // local counter value once every source delivered all of its tiles
+    void* rs_dst;                   // bf16 shard [rs_shard_rows][N]
+    int rs_accumulate;              // dst += (stochastic rounding) instead of dst =
+    float rs_scale;
+    float* rs_norm_partials;        // optional, rs_num_partials floats: sum of squares of the new shard values
+    int rs_num_partials;
+    unsigned int rs_seed;
+    unsigned long long rs_limit_ns;
 };
 
 // Each lane of the calling warp owns one accumulator row (TMEM lane); `t_row` addresses column 0 of that row
 // block.  Applies alpha and bias, optionally adds the previous C, stores bf16 or fp32, tracks abs-max.
 // The TMEM loads are warp-collective, so all lanes run the loop; only the stores are predicated on the row.
+// `dst_row` (bf16, optional) redirects the stores of this lane's row to another buffer - possibly on a peer GPU -
+// while an accumulating epilogue still reads the previous values from C.
 __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_row, int row, int col_base, int ncols,
-                                              float alpha, float& tmax) {
+                                              float alpha, float& tmax, __nv_bfloat16* dst_row = nullptr) {
     using namespace sm100;
     const bool row_ok = row < p.M;
 #pragma unroll 1
@@ -74,7 +91,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
             const bool full = (col0 + 32 <= p.N);
             if (p.c_dtype == 0) {
                 __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-                if (full && ((reinterpret_cast<uintptr_t>(cp) & 15u) == 0)) {
+                __nv_bfloat16* wp = dst_row ? dst_row + col0 : cp;
+                if (full && (((reinterpret_cast<uintptr_t>(cp) | reinterpret_cast<uintptr_t>(wp)) & 15u) == 0)) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         uint4 o;
@@ -90,13 +108,13 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
                         __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
-                        *reinterpret_cast<uint4*>(cp + g * 8) = o;
+                        *reinterpret_cast<uint4*>(wp + g * 8) = o;
                     }
                 } else {
                     for (int j = 0; j < 32; ++j) {
                         if (col0 + j < p.N) {
                             if (p.accumulate) v[j] += __bfloat162float(cp[j]);
-                            cp[j] = __float2bfloat16_rn(v[j]);
+                            wp[j] = __float2bfloat16_rn(v[j]);
                         }
                     }
                 }

@@ -241,6 +241,9 @@ extern "C" void llmq_gemm_set_mode(int mode) { g_gemm_mode = mode; }
 
 extern "C" int llmq_gemm_ready(const void*, const void*, void*, const void*, int, int, int, int, int, int, int, long long, long long, long long, int, int, int,
                                const float*, const float*, float, float*, unsigned int*, int, const unsigned int*, unsigned int, int, double, cudaStream_t);
+static int gemm_impl(const void*, const void*, void*, const void*, int, int, int, int, int, int, int, long long, long long, long long, int, int, int,
+                     const float*, const float*, float, float*, unsigned int*, int, const unsigned int*, unsigned int, int, double, const GemmParams*,
+                     cudaStream_t);
 
 extern "C" int llmq_gemm(const void* A, const void* B, void* C, const void* bias,
                          int M, int N, int K,
@@ -263,6 +266,40 @@ extern "C" int llmq_gemm_ready(const void* A, const void* B, void* C, const void
                                const float* scale_a, const float* scale_b, float alpha, float* absmax_out, unsigned int* status,
                                int num_sms, const unsigned int* ready_flags, unsigned int ready_gen, int ready_rows_per_src,
                                double ready_limit_s, cudaStream_t stream) {
+    return gemm_impl(A, B, C, bias, M, N, K, ab_dtype, b_dtype, a_mn_major, b_mn_major, lda, ldb, ldc, c_dtype, bias_dtype, accumulate, scale_a,
+                     scale_b, alpha, absmax_out, status, num_sms, ready_flags, ready_gen, ready_rows_per_src, ready_limit_s, nullptr, stream);
+}
+
+// GEMM whose epilogue reduce-scatters the result over the data-parallel ranks (see gemm_tcgen05_2cta.cu).
+// landing / counters: the landing buffer and the arrival counter of every rank (peer addresses); M must split
+// into `world` row shards of a multiple of 32 rows, the output is bf16 with ldc == N.  `counter_target` is the
+// value the local counter reaches after this call: every call adds world * (M / world / 32) * ceil(N / 256).
+extern "C" int llmq_gemm_rs(const void* A, const void* B, void* C, int M, int N, int K, int ab_dtype, int b_dtype, int a_mn_major,
+                            int b_mn_major, long long lda, long long ldb, int accumulate, const float* scale_a, const float* scale_b,
+                            float alpha, unsigned int* status, int num_sms, void* const* landing, void* const* counters, int rank, int world,
+                            unsigned int counter_target, void* shard_dst, int shard_accumulate, float shard_scale, float* norm_partials,
+                            int num_partials, unsigned int seed, double limit_s, cudaStream_t stream) {
+    if (world < 2 || world > 8 || M % world || (M / world) % 32 || M < 256 || N % 8) return -20;
+    GemmParams rs{};
+    rs.rs_world = world; rs.rs_rank = rank; rs.rs_shard_rows = M / world;
+    for (int i = 0; i < world; ++i) { rs.rs_landing[i] = landing[i]; rs.rs_counter[i] = static_cast<unsigned int*>(counters[i]); }
+    rs.rs_target = counter_target; rs.rs_dst = shard_dst; rs.rs_accumulate = shard_accumulate; rs.rs_scale = shard_scale;
+    rs.rs_norm_partials = norm_partials; rs.rs_num_partials = num_partials > 0 ? num_partials : 1; rs.rs_seed = seed;
+    rs.rs_limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
+    return gemm_impl(A, B, C, nullptr, M, N, K, ab_dtype, b_dtype, a_mn_major, b_mn_major, lda, ldb, N, 0, 0, accumulate, scale_a, scale_b, alpha,
+                     nullptr, status, num_sms, nullptr, 0u, 0, 0.0, &rs, stream);
+}
+
+extern "C" unsigned int llmq_gemm_rs_arrivals(int M, int N, int world) {
+    return static_cast<unsigned int>(world) * static_cast<unsigned int>(M / world / 32) * static_cast<unsigned int>((N + BN - 1) / BN);
+}
+
+static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
+                     int M, int N, int K, int ab_dtype, int b_dtype, int a_mn_major, int b_mn_major,
+                     long long lda, long long ldb, long long ldc, int c_dtype, int bias_dtype, int accumulate,
+                     const float* scale_a, const float* scale_b, float alpha, float* absmax_out, unsigned int* status,
+                     int num_sms, const unsigned int* ready_flags, unsigned int ready_gen, int ready_rows_per_src,
+                     double ready_limit_s, const GemmParams* rs, cudaStream_t stream) {
     const int eb = ab_dtype == 0 ? 2 : 1;
     if ((b_dtype == 0 ? 2 : 1) != eb) return -2;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -277,12 +314,12 @@ extern "C" int llmq_gemm_ready(const void* A, const void* B, void* C, const void
     else             rc = llmq_encode_tmap_2d(&ta, A, eb, K, M, lda, bk);
     if (rc) return rc;
     // The CTA-pair kernel stages 128 rows of B per CTA; the one-CTA kernel stages all 256.
-    const bool pair_kernel = ready_flags != nullptr || g_gemm_mode == 2 || (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32);
+    const bool pair_kernel = rs != nullptr || ready_flags != nullptr || g_gemm_mode == 2 || (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32);
     if (!b_mn_major) rc = llmq_encode_tmap_2d(&tb, B, eb, N, K, ldb, pair_kernel ? 128 : BN);
     else             rc = llmq_encode_tmap_2d(&tb, B, eb, K, N, ldb, bk);
     if (rc) return rc;
 
-    GemmParams p;
+    GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.elem_bytes = eb;
     p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
     p.a_fmt = ab_dtype == 0 ? 1 : (ab_dtype == 1 ? 0 : 1);
@@ -293,6 +330,13 @@ extern "C" int llmq_gemm_ready(const void* A, const void* B, void* C, const void
     p.absmax_out = absmax_out; p.status = status;
     p.ready_flags = ready_flags; p.ready_gen = ready_gen; p.ready_rows_per_src = ready_rows_per_src > 0 ? ready_rows_per_src : 1;
     p.ready_limit_ns = static_cast<unsigned long long>(ready_limit_s * 1e9);
+    if (rs) {
+        p.rs_world = rs->rs_world; p.rs_rank = rs->rs_rank; p.rs_shard_rows = rs->rs_shard_rows;
+        for (int i = 0; i < 8; ++i) { p.rs_landing[i] = rs->rs_landing[i]; p.rs_counter[i] = rs->rs_counter[i]; }
+        p.rs_target = rs->rs_target; p.rs_dst = rs->rs_dst; p.rs_accumulate = rs->rs_accumulate; p.rs_scale = rs->rs_scale;
+        p.rs_norm_partials = rs->rs_norm_partials; p.rs_num_partials = rs->rs_num_partials; p.rs_seed = rs->rs_seed;
+        p.rs_limit_ns = rs->rs_limit_ns;
+    }
 
     if (pair_kernel) return llmq_gemm_2cta_launch(ta, tb, p, num_sms, stream);
 

@@ -9,6 +9,15 @@
 // leader's "full" barrier), warp 1 = MMA issuer (leader CTA only), warps 2-5 = epilogue of the CTA's own
 // 128x256 accumulator.  Stage release and accumulator-ready signals go to both CTAs with two tcgen05.commit
 // each; the peer's epilogue releases accumulators with a remote mbarrier arrive.  Every wait is bounded.
+//
+// Fused reduce-scatter (GemmParams::rs_*, used for the weight-gradient GEMMs of data-parallel ranks; takes the
+// place of the reference's dW matmul followed by ncclReduceScatter and vector_add_sr, llama_gradients.cpp:50-77):
+// the epilogue stores every output row straight into the landing buffer of the rank that owns the row, over
+// NVLink, while the tensor core already works on the next tile; tiles are visited owner by owner starting with
+// the right-hand neighbour, so a rank's own rows come last and the peers' contributions have landed by then.
+// Each epilogue warp bumps the owner's arrival counter per tile (release, system scope).  After its last tile a
+// CTA waits (bounded) for the local counter to show all sources, then the epilogue warps of all CTAs sum the
+// `world` slots of this rank's rows, scale, add into the shard with stochastic rounding and collect the norm.
 #include "ptx_sm100.cuh"
 #include "api.h"
 #include "common.cuh"
@@ -31,14 +40,15 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int rot, int& tm, int& tn) {
     constexpr int G = 8;             // 8 pair-rows (2048 rows of A) share each B tile while it is hot in L2
     int per_group = G * tiles_n;
     int group = t / per_group;
     int first_m = group * G;
     int gsz = min(tiles_m - first_m, G);
     int r = t - group * per_group;
-    tm = first_m + (r % gsz);
+    tm = first_m + (r % gsz) + rot;
+    if (tm >= tiles_m) tm -= tiles_m;
     tn = r / gsz;
 }
 
@@ -69,6 +79,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    // fused reduce-scatter: start with the rows owned by the next rank, finish with our own
+    const int rot = p.rs_world > 0 ? static_cast<int>((static_cast<long long>((p.rs_rank + 1) % p.rs_world) * p.rs_shard_rows) / (2 * BM)) : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -106,7 +118,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
             };
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-                int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+                int tm, tn; tile_coords(t, tiles_m, tiles_n, rot, tm, tn);
                 const int row0 = (tm * 2 + static_cast<int>(rank)) * BM;               // this CTA's rows of A / C
                 const int brow0 = tn * BN + static_cast<int>(rank) * BN_HALF;          // this CTA's rows of B
                 if (p.ready_flags && !p.b_mn_major && brow0 < p.N) {
@@ -191,15 +203,83 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-            int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            int tm, tn; tile_coords(t, tiles_m, tiles_n, rot, tm, tn);
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { if (lane == 0) atomicOr(p.status, kErrTmemFull); ok = false; break; }
             tc_fence_after_sync();
             __syncwarp();
             const int row = (tm * 2 + static_cast<int>(rank)) * BM + q * 32 + lane;
-            epilogue_rows(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, row, tn * BN, BN, alpha, tmax);
+            __nv_bfloat16* dst_row = nullptr;
+            int owner = 0;
+            if (p.rs_world > 0) {
+                owner = min(((tm * 2 + static_cast<int>(rank)) * BM + q * 32) / p.rs_shard_rows, p.rs_world - 1);   // same for the whole warp
+                const long long slot_row = static_cast<long long>(p.rs_rank) * p.rs_shard_rows + (row - owner * p.rs_shard_rows);
+                dst_row = static_cast<__nv_bfloat16*>(p.rs_landing[owner]) + slot_row * p.N;
+            }
+            epilogue_rows(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, row, tn * BN, BN, alpha, tmax, dst_row);
             tc_fence_before_sync();
             mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));            // 2 x 128 arrivals at the leader
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            if (p.rs_world > 0 && (tm * 2 + static_cast<int>(rank)) * BM + q * 32 < p.M) {
+                __syncwarp();                                               // the rows of all lanes are stored
+                if (lane == 0) {
+                    __threadfence_system();
+                    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.rs_counter[owner]), "r"(1u) : "memory");
+                }
+            }
+        }
+        if (p.rs_world > 0) {
+            // ---- tail: sum the slots of this rank's rows once every source delivered
+            volatile uint32_t* s_ok = abort_flag + 1;
+            float* s_red = reinterpret_cast<float*>(const_cast<uint32_t*>(abort_flag + 2));
+            if (warp == 2 && lane == 0) {
+                bool got = ok && peer::wait_flag(p.rs_counter[p.rs_rank], p.rs_target, p.rs_limit_ns);
+                if (!got) atomicOr(p.status, kErrPeerFlag);
+                *s_ok = got ? 1u : 0u;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*s_ok) {
+                const int tid = threadIdx.x - 64;                           // 0..127
+                const long long n_shard = static_cast<long long>(p.rs_shard_rows) * p.N;
+                const long long nvec = n_shard / 8;
+                const __nv_bfloat16* mine = static_cast<const __nv_bfloat16*>(p.rs_landing[p.rs_rank]);
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.rs_dst);
+                float ss = 0.f;
+                for (long long i = blockIdx.x * 128LL + tid; i < nvec; i += static_cast<long long>(gridDim.x) * 128) {
+                    float a8[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) a8[k] = 0.f;
+                    for (int s = 0; s < p.rs_world; ++s) {
+                        const int src = (p.rs_rank + s) % p.rs_world;
+                        Vec16<bf16> v = Vec16<bf16>::load_stream(mine + src * n_shard + i * 8);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) a8[k] += __bfloat162float(v.v[k]);
+                    }
+                    Vec16<bf16> o;
+                    if (p.rs_accumulate) {
+                        Vec16<bf16> old = Vec16<bf16>::load(dst + i * 8);
+#pragma unroll
+                        for (int k = 0; k < 8; k += 2) {
+                            const uint32_t r = rng_u32(static_cast<uint64_t>(i) * 4 + k / 2, p.rs_seed);
+                            o.v[k] = sr_bf16(a8[k] * p.rs_scale + __bfloat162float(old.v[k]), r);
+                            o.v[k + 1] = sr_bf16(a8[k + 1] * p.rs_scale + __bfloat162float(old.v[k + 1]), r >> 16);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(a8[k] * p.rs_scale);
+                    }
+                    if (p.rs_norm_partials) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) { float f = __bfloat162float(o.v[k]); ss += f * f; }
+                    }
+                    o.store(dst + i * 8);
+                }
+                if (p.rs_norm_partials) {
+                    ss = warp_reduce_sum(ss);
+                    if (lane == 0) s_red[q] = ss;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (tid == 0) p.rs_norm_partials[blockIdx.x % p.rs_num_partials] += s_red[0] + s_red[1] + s_red[2] + s_red[3];
+                }
+            }
         }
         if (p.absmax_out) {
             tmax = warp_reduce_max(tmax);

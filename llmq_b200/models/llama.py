@@ -192,13 +192,17 @@ class LlamaModel:
             K.quantize(act_q, sc, act, am)
         K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale, ready=ready)
 
-    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None):
+    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None, dw_rs=None):
         """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
-        W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second."""
+        W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second.
+        ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside."""
         if not self.quant:
             if dinp is not None:
                 K.gemm(dinp, dout, W, b_mn=True, ready=ready)
-            K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate)
+            if dw_rs is not None:
+                dw_rs(dout, inp)
+            else:
+                K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate)
             if dbias is not None:
                 K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
             return
@@ -206,7 +210,10 @@ class LlamaModel:
         K.quantize(dout_q, sc, dout, am)
         if dinp is not None:
             K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
-        K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
+        if dw_rs is not None:
+            dw_rs(dout_q, inp_q, sc, inp_scale)
+        else:
+            K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
         if dbias is not None:
             K.bias_backward(dbias, dout_q, self.tmp.bias_scratch, scale_a=sc, accumulate=True)
 
@@ -397,20 +404,22 @@ class LlamaModel:
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         BT, q = self.B * self.T, self.quant
         sc_of = lambda s: self._slot(l, s)[1]
+        fused_dw = getattr(self.grads, "fused_dw", None)
+        rs = (lambda name: fused_dw(l, name)) if fused_dw is not None else (lambda name: None)
         # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
-                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"])
+                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"))
         # ---- SwiGLU backward, in place over the saved up-projection
         K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
         # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
-                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"])
+                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"))
         # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
         K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],
                            absmax=self._slot(l, S_DRESATT)[0], accumulate_dweight=True)
         # ---- attention out projection
         self._bwd_mm(t.d_ln, dw["o_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESATT),
-                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc, ready=p.ready["o_w"])
+                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc, ready=p.ready["o_w"], dw_rs=rs("o_w"))
         # ---- attention core
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
         K.attention_backward(t.d_qkv, t.att_scratch, t.d_ln.view(self.B, self.T, Hq, cfg.head_size), att4, a.lse[l], a.qkv[l], Hq, Hkv)
@@ -418,7 +427,7 @@ class LlamaModel:
         # ---- QKV projection
         dqkv2d = t.d_qkv.view(BT, cfg.qkv_channels)
         self._bwd_mm(t.d_ln, dw["qkv_w"], dw.get("qkv_b"), dqkv2d, t.d_qkv_q if q else None, self._slot(l, S_DQKV),
-                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc, ready=p.ready["qkv_w"])
+                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc, ready=p.ready["qkv_w"], dw_rs=rs("qkv_w"))
 
     # ================================================================================== optimizer
     def update(self, lr: float, beta1: float = 0.9, beta2: float = 0.95, step: int = 1, eps: float = 1e-8,

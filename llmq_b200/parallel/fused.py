@@ -147,6 +147,46 @@ class FusedCollectives:
                                                     0 if norm_partials is None else norm_partials.numel(), ctypes.c_uint(seed & 0xFFFFFFFF),
                                                     self.sms, L.stream_ptr()), "p2p_reduce_scatter")
 
+    # ---- GEMM with the reduce-scatter inside (csrc/gemm_tcgen05_2cta.cu)
+    RS_COUNTER_BASE = MAX_CHANNELS * 8 * 4 + 2 * SMALL_SLOTS_FLOATS * 4       # counters live behind the small all-reduce slots
+
+    def gemm_rs_supported(self, M: int, N: int) -> bool:
+        return M % self.world == 0 and (M // self.world) % 32 == 0 and M >= 256 and N % 8 == 0
+
+    def gemm_rs(self, landing: torch.Tensor, counter_id: int, dst: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False,
+                scale_a=None, scale_b=None, alpha: float = 1.0, prev: Optional[torch.Tensor] = None, shard_accumulate: bool = False,
+                shard_scale: float = 1.0, norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
+        """dst (+)= shard_scale * (rows of this rank of the sum over ranks of (prev +) alpha * A @ B^T).
+
+        One kernel: tcgen05 GEMM whose epilogue stores each output row into the owner rank's ``landing`` buffer
+        ([world, M/world, N] bf16 in the heap, same allocation on every rank) and whose tail sums the slots.
+        ``counter_id`` names the arrival counter of this landing buffer (one per buffer).  Callers make sure that every
+        rank finished reading the previous content of its landing buffer (signal / wait) before the next call."""
+        seg, off = self.heap.locate(landing)
+        w = self.world
+        M = landing.shape[0] * landing.shape[1]
+        N = landing.shape[2]
+        Kd = a.shape[0] if a_mn else a.shape[1]
+        if not self.gemm_rs_supported(M, N) or landing.dtype != torch.bfloat16 or dst.dtype != torch.bfloat16:
+            raise ValueError("fused GEMM + reduce-scatter: unsupported shape or dtype")
+        key = ("rs", counter_id)
+        arrivals = int(L.kernels().llmq_gemm_rs_arrivals(M, N, w))
+        target = (self.gen.get(key, 0) + arrivals) & 0xFFFFFFFF
+        self.gen[key] = target
+        ptrs = list(seg.hdl.buffer_ptrs)
+        landing_arr = (ctypes.c_void_p * 8)(*([p + off for p in ptrs] + [0] * (8 - len(ptrs))))
+        cptrs = list(self.ctrl.hdl.buffer_ptrs)
+        coff = self.RS_COUNTER_BASE + 4 * counter_id
+        counter_arr = (ctypes.c_void_p * 8)(*([p + coff for p in cptrs] + [0] * (8 - len(cptrs))))
+        c_local = prev if prev is not None else landing
+        rc = L.kernels().llmq_gemm_rs(
+            L.ptr(a), L.ptr(b), L.ptr(c_local), M, N, Kd, L.dtype_code(a.dtype), L.dtype_code(b.dtype), int(a_mn), int(b_mn),
+            ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), int(prev is not None), L.ptr(scale_a), L.ptr(scale_b),
+            ctypes.c_float(alpha), L.ptr(self.status), self.sms, landing_arr, counter_arr, self.rank, w, ctypes.c_uint(target), L.ptr(dst),
+            int(shard_accumulate), ctypes.c_float(shard_scale), L.ptr(norm_partials), 0 if norm_partials is None else norm_partials.numel(),
+            ctypes.c_uint(seed & 0xFFFFFFFF), ctypes.c_double(self.wait_limit_s), L.stream_ptr())
+        L.check(rc, "gemm_rs")
+
     def all_reduce_small(self, t: torch.Tensor, op: str = "sum") -> None:
         """In-place sum / max / avg of a few fp32 values across ranks, one kernel, no library call."""
         n = t.numel()

@@ -376,7 +376,14 @@ class GradientManager:
         # in-kernel reduce-scatter: bf16 gradients in the symmetric heap, shards on the device
         self.fused = weights.fused if (weights.fused is not None and self.dtype == torch.bfloat16 and not host and w > 1) else None
         self.norm_fused = self.fused is not None
-        self.norm_partials = torch.zeros(K.NORM_PARTIALS, dtype=torch.float32, device=device) if self.fused is not None else None
+        # squared-norm partials: first half written by the side-stream reductions, second half by GEMMs with the
+        # reduce-scatter inside (main stream), so the two streams never touch the same word
+        self.norm_partials = torch.zeros(2 * K.NORM_PARTIALS, dtype=torch.float32, device=device) if self.fused is not None else None
+        # Weight-gradient GEMMs with the reduce-scatter inside the kernel.  Off unless LLMQ_GEMM_RS=1: the kernel's tail
+        # has to wait for the peers on the main stream, which measured 563 ms against 536 ms per step (Qwen2.5-7B, 2 GPUs)
+        # for the plain GEMM followed by the pull reduce-scatter kernel on the side stream.
+        self.gemm_rs = self.fused is not None and os.environ.get("LLMQ_GEMM_RS", "0") == "1"
+        self._rs_names: set = set()
         self._fdone: Dict[int, tuple] = {}           # channel -> (generation, event) of the last reduction reading a buffer
         self._fevents: List = []
         _heap = self.fused.heap if self.fused is not None else None
@@ -444,22 +451,55 @@ class GradientManager:
             f.wait(ch_ready, gen)
             for k, (full, dst) in enumerate(pairs):
                 f.reduce_scatter(full, dst, accumulate=accumulate, scale=1.0 / self.comm.world,
-                                 norm_partials=self.norm_partials if self.last else None, seed=seed + 17 * k)
+                                 norm_partials=self.norm_partials[:K.NORM_PARTIALS] if self.last else None, seed=seed + 17 * k)
             done = f.signal(ch_ready + 1)
             ev = torch.cuda.Event()
             ev.record(f.stream)
         self._fdone[ch_ready] = (done, ev)
         self._fevents.append(ev)
 
+    def _block_seed(self, l: int) -> int:
+        return (self.seed * 7919 + self.step * 104729 + l * 131 + self._acc_count[l] * 7) & 0x7FFFFFFF
+
+    def fused_dw(self, l: int, name: str):
+        """A callable ``run(a, b, scale_a, scale_b)`` that computes this rank's weight gradient ``a^T-stored @ b`` and
+        reduce-scatters it inside the same kernel (the result lands in the shard), or ``None`` when the plain GEMM
+        followed by ``notify_block`` has to be used: no peer-memory path, the reduction does not follow this
+        micro-step, or the shape does not split into row shards of a multiple of 32 rows."""
+        if not self.gemm_rs or not (self.sharded or (self.last and self.micro_step == 0)):
+            return None
+        k = next(i for i, s in enumerate(self.block_specs) if s.name == name)
+        spec = self.block_specs[k]
+        if not spec.matrix or not self.fused.gemm_rs_supported(spec.shape[0], spec.shape[1]):
+            return None
+        w = self.comm.world
+        M, N = spec.shape
+        if self.sharded:
+            i = l % 2
+            landing, dst, acc, counter = self.bufs[i][name].view(w, M // w, N), self.shards[l][name], self._acc_count[l] > 0, i * 16 + k
+        else:
+            full = self.full[l][name]                       # the own slot of the landing buffer is the shard itself
+            landing, dst, acc, counter = full.view(w, M // w, N), self.comm.local_shard(full), False, 64 + l * 16 + k
+        seed = self._block_seed(l) + 17 * k
+        parts = self.norm_partials[K.NORM_PARTIALS:] if self.last else None
+        self._rs_names.add(name)
+
+        def run(a, b, scale_a=None, scale_b=None):
+            self.fused.gemm_rs(landing, counter, dst, a, b, a_mn=True, b_mn=True, scale_a=scale_a, scale_b=scale_b, shard_accumulate=acc,
+                               shard_scale=1.0 / w, norm_partials=parts, seed=seed)
+        return run
+
     def notify_block(self, l: int) -> None:
         if self.fused is not None:
-            seed = (self.seed * 7919 + self.step * 104729 + l * 131 + self._acc_count[l] * 7) & 0x7FFFFFFF
+            seed = self._block_seed(l)
+            done, self._rs_names = self._rs_names, set()     # matrices already reduced inside their GEMM
             if not self.sharded:
                 if self.last:
-                    self._reduce_fused(CH_GRADS + 2 * l, [(t, self.comm.local_shard(t)) for t in self.full[l].values()], False, seed)
+                    self._reduce_fused(CH_GRADS + 2 * l, [(t, self.comm.local_shard(t)) for n, t in self.full[l].items() if n not in done],
+                                       False, seed)
             else:
                 i = l % 2
-                pairs = [(self.bufs[i][s.name], self.shards[l][s.name]) for s in self.block_specs]
+                pairs = [(self.bufs[i][s.name], self.shards[l][s.name]) for s in self.block_specs if s.name not in done]
                 self._reduce_fused(CH_GRADS + 2 * i, pairs, self._acc_count[l] > 0, seed)
                 self._acc_count[l] += 1
             return

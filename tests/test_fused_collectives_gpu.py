@@ -82,6 +82,35 @@ def _worker(rank, world, port, multimem, q):
         torch.cuda.synchronize()
         err = (dst.float() - 2 * ref_shard).abs().max().item()
         assert err <= 3e-2 * ref_shard.abs().max().item() + 1e-2, err
+        # ---- GEMM with the reduce-scatter inside: dW = dout^T @ inp per rank, mean over ranks, own rows
+        M, N, Kd = 1024, 640, 512
+        landing = fc.heap.empty((world, M // world, N), torch.bfloat16)
+        shard_dst = torch.zeros(M // world, N, dtype=torch.bfloat16, device=dev)
+        partials.zero_()
+        assert fc.gemm_rs_supported(M, N)
+        for it in range(3):
+            a_t = torch.randn(Kd, M, generator=g).bfloat16().to(dev)          # stored [K, M]
+            b_t = torch.randn(Kd, N, generator=g).bfloat16().to(dev)          # stored [K, N]
+            prev = torch.randn(M, N, generator=g).bfloat16().to(dev) if it == 2 else None
+            local = a_t.float().t() @ b_t.float()
+            if prev is not None:
+                local = local + prev.float()
+            tot = local.bfloat16().float()                                    # each rank's contribution is rounded to bf16
+            dist.all_reduce(tot)
+            want = (tot / world)[rank * M // world:(rank + 1) * M // world]
+            before = shard_dst.float().clone()
+            fc.gemm_rs(landing, 0, shard_dst, a_t, b_t, a_mn=True, b_mn=True, prev=prev, shard_accumulate=it > 0, shard_scale=1.0 / world,
+                       norm_partials=partials if it == 0 else None, seed=11 + it)
+            gen = fc.signal(4)                                                # nobody overwrites a landing buffer that is still being summed
+            fc.wait(4, gen)
+            torch.cuda.synchronize()
+            K.check_status(dev)
+            expect = want + (before if it > 0 else 0)
+            err = (shard_dst.float() - expect).abs().max().item()
+            assert err <= 2e-2 * expect.abs().max().item() + 1e-2, (it, err)
+            if it == 0:
+                ssq = shard_dst.float().pow(2).sum().item()
+                assert abs(partials.sum().item() - ssq) < 1e-3 * ssq
         # ---- a wait on a flag nobody sets runs out and is reported, the context stays usable
         fc.wait_limit_s = 0.5
         fc.wait(9, 1)

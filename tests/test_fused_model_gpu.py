@@ -9,6 +9,8 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 B, T = 2, 256
+# (ZeRO level, gradient accumulation steps); with one micro-step ZeRO-1 also takes the GEMM + reduce-scatter kernel
+CASES = ((1, 2), (1, 1), (2, 2), (3, 2))
 
 
 def _port():
@@ -32,23 +34,25 @@ def _worker(rank, world, port, q):
         g = torch.Generator().manual_seed(5 + rank)
         tok = torch.randint(0, 1024, (2, B, T + 1), generator=g, dtype=torch.int32)
         results = {}
-        for zero in (1, 2, 3):
-            for mode in ("nccl", "fused"):
-                opts = LLamaOptions(matmul_type="e4m3", collectives=mode, momentum_type="bf16", variance_type="bf16")
+        for zero, ga in CASES:
+            for mode in ("nccl", "fused", "fused+gemm_rs"):
+                os.environ["LLMQ_GEMM_RS"] = "1" if mode.endswith("gemm_rs") else "0"
+                opts = LLamaOptions(matmul_type="e4m3", collectives=mode.split("+")[0], momentum_type="bf16", variance_type="bf16")
                 opts.set_zero_level(zero)
                 m = LlamaModel(cfg, opts, comm, dev, B, T)
-                assert (m.fused is not None) == (mode == "fused")
+                assert (m.fused is not None) == mode.startswith("fused")
+                assert m.grads.gemm_rs == mode.endswith("gemm_rs")
                 m.init_weights(3)
                 out = []
                 for step in range(1, 4):
-                    for j in range(2):
+                    for j in range(ga):
                         m.forward(tok[j, :, :-1].contiguous(), j)
-                        m.backward(None, tok[j, :, 1:].contiguous(), 0.0, 2, j)
-                    r = m.update(lr=1e-3, step=step, grad_accum=2)
+                        m.backward(None, tok[j, :, 1:].contiguous(), 0.0, ga, j)
+                    r = m.update(lr=1e-3, step=step, grad_accum=ga)
                     out.append((r["loss"], r["norm"]))
                 torch.cuda.synchronize()
                 K.check_status(dev)
-                results[(zero, mode)] = out
+                results[(zero, ga, mode)] = out
                 del m
                 comm.barrier()
         q.put((rank, "ok", results))
@@ -74,9 +78,11 @@ def test_fused_training_matches_nccl():
             p.kill()
     assert all(r[1] == "ok" for r in res), res
     r0 = res[0][2]
-    for zero in (1, 2, 3):
-        a, b = r0[(zero, "nccl")], r0[(zero, "fused")]
-        for (l0, n0), (l1, n1) in zip(a, b):
-            assert abs(l0 - l1) < 5e-3, (zero, a, b)
-            assert abs(n0 - n1) < 2e-2 * max(1.0, n0), (zero, a, b)
+    for zero, ga in CASES:
+        a = r0[(zero, ga, "nccl")]
+        for mode in ("fused", "fused+gemm_rs"):
+            b = r0[(zero, ga, mode)]
+            for (l0, n0), (l1, n1) in zip(a, b):
+                assert abs(l0 - l1) < 5e-3, (zero, mode, a, b)
+                assert abs(n0 - n1) < 2e-2 * max(1.0, n0), (zero, mode, a, b)
         assert a[-1][0] < a[0][0]
