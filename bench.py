@@ -111,7 +111,7 @@ def main():
     trainer.init_weights()
     dev, comm, rank = trainer.device, trainer.comm, trainer.rank
     gen = torch.Generator().manual_seed(1234 + rank)
-    n_batches = 4
+    n_batches = min(256, GA * (args.warmup + 2 * args.steps))      # fresh tokens every micro-step (cycled only beyond 256)
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, T + 1), generator=gen, dtype=torch.int32) for _ in range(n_batches)]
     host_in = [t[:, :-1].contiguous().pin_memory() for t in host_tokens]
     host_tg = [t[:, 1:].contiguous().pin_memory() for t in host_tokens]
@@ -121,7 +121,7 @@ def main():
 
     def run_step(i, step_no, from_host):
         for j in range(GA):
-            k = (i * GA + j) % n_batches
+            k = ((step_no - 1) * GA + j) % n_batches
             if from_host:
                 trainer.step(host_in[k], host_tg[k])
             else:

@@ -5,13 +5,26 @@
 
 namespace {
 
+// i -> (i / per_row, i % per_row); multiply-high when the index space fits 31 bits, 64-bit division otherwise
+__device__ __forceinline__ void split_index(long long i, long long total, int per_row, const FastDiv& fd, long long& r, int& c) {
+    if (total < (1ll << 31)) {
+        uint32_t q, m;
+        fd.divmod(static_cast<uint32_t>(i), q, m);
+        r = q; c = static_cast<int>(m);
+    } else {
+        r = i / per_row;
+        c = static_cast<int>(i - r * per_row);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // SwiGLU.  Input rows are [up(D) | gate(D)];  out = up * gate * sigmoid(gate).
 // With q_out the kernel emits e4m3 directly using an abs-max that is already known (recompute path).
 template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(T* __restrict__ out, e4m3* __restrict__ q_out, const T* __restrict__ inp, long long rows, int D,
-                  float* __restrict__ absmax_out, const float* __restrict__ known_absmax, float* __restrict__ q_scale_out) {
+                  float* __restrict__ absmax_out, const float* __restrict__ known_absmax, float* __restrict__ q_scale_out,
+                  const FastDiv fd) {
     __shared__ float scratch[32];
     using V = Vec16<T>;
     const int vec_per_row = D / V::N;
@@ -25,23 +38,28 @@ swiglu_fwd_kernel(T* __restrict__ out, e4m3* __restrict__ q_out, const T* __rest
     float tmax = 0.f;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        long long r = i / vec_per_row;
-        int c = static_cast<int>(i - r * vec_per_row) * V::N;
+        long long r; int c;
+        split_index(i, total, vec_per_row, fd, r, c);
+        c *= V::N;
         const T* up = inp + r * 2 * D + c;
         V vu = V::load_stream(up), vg = V::load_stream(up + D), vo;
-        alignas(8) e4m3 q[V::N];
+        float f[V::N];
 #pragma unroll
         for (int k = 0; k < V::N; ++k) {
             float u = to_float(vu.v[k]), g = to_float(vg.v[k]);
             vo.v[k] = from_float<T>(u * g * fast_sigmoid(g));
-            float f = to_float(vo.v[k]);
-            tmax = fmaxf(tmax, fabsf(f));
-            if (q_out) q[k] = e4m3(f * qmul);
+            f[k] = to_float(vo.v[k]);
+            tmax = fmaxf(tmax, fabsf(f[k]));
         }
         if (out) vo.store(out + r * D + c);
         if (q_out) {
-            if constexpr (V::N == 8) *reinterpret_cast<uint2*>(q_out + r * D + c) = *reinterpret_cast<uint2*>(q);
-            else *reinterpret_cast<uint32_t*>(q_out + r * D + c) = *reinterpret_cast<uint32_t*>(q);
+            if constexpr (V::N == 8) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] *= qmul;
+                *reinterpret_cast<uint2*>(q_out + r * D + c) = pack_e4m3x8(f);
+            } else {
+                *reinterpret_cast<uint32_t*>(q_out + r * D + c) = pack_e4m3x2(f[0] * qmul, f[1] * qmul) | (pack_e4m3x2(f[2] * qmul, f[3] * qmul) << 16);
+            }
         }
     }
     block_absmax_commit(absmax_out, tmax, scratch);
@@ -50,7 +68,8 @@ swiglu_fwd_kernel(T* __restrict__ out, e4m3* __restrict__ q_out, const T* __rest
 // Backward: dinp = [d_up | d_gate]; dinp may alias inp (in-place over the saved up-projection).
 template <typename T>
 __global__ void __launch_bounds__(256)
-swiglu_bwd_kernel(T* dinp, const T* __restrict__ dout, const T* inp, long long rows, int D, float* __restrict__ absmax_out) {
+swiglu_bwd_kernel(T* dinp, const T* __restrict__ dout, const T* inp, long long rows, int D, float* __restrict__ absmax_out,
+                  const FastDiv fd) {
     __shared__ float scratch[32];
     using V = Vec16<T>;
     const int vec_per_row = D / V::N;
@@ -58,8 +77,9 @@ swiglu_bwd_kernel(T* dinp, const T* __restrict__ dout, const T* inp, long long r
     float tmax = 0.f;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        long long r = i / vec_per_row;
-        int c = static_cast<int>(i - r * vec_per_row) * V::N;
+        long long r; int c;
+        split_index(i, total, vec_per_row, fd, r, c);
+        c *= V::N;
         const T* up = inp + r * 2 * D + c;
         V vu = V::load(up), vg = V::load(up + D), vd = V::load_stream(dout + r * D + c), du, dg;
 #pragma unroll
@@ -83,7 +103,7 @@ swiglu_bwd_kernel(T* dinp, const T* __restrict__ dout, const T* inp, long long r
 template <typename T, bool Backward>
 __global__ void __launch_bounds__(256)
 rope_kernel(T* out, const T* inp, const float* __restrict__ freqs, int B, int Tlen, int Hq, int Hkv, int HS,
-            float* __restrict__ absmax_out) {
+            float* __restrict__ absmax_out, const FastDiv fd_vec, const FastDiv fd_h, const FastDiv fd_t) {
     __shared__ float scratch[32];
     using V = Vec16<T>;
     const int half = HS / 2;
@@ -93,11 +113,21 @@ rope_kernel(T* out, const T* inp, const float* __restrict__ freqs, int B, int Tl
     float tmax = 0.f;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        int v = static_cast<int>(i % vec_per_half);
-        long long rest = i / vec_per_half;
-        int h = static_cast<int>(rest % H);
-        long long bt = rest / H;
-        int t = static_cast<int>(bt % Tlen);
+        int v, h, t;
+        long long bt;
+        if (total < (1ll << 31)) {
+            uint32_t rest, vv, hh, btt, bb, tt;
+            fd_vec.divmod(static_cast<uint32_t>(i), rest, vv);
+            fd_h.divmod(rest, btt, hh);
+            fd_t.divmod(btt, bb, tt);
+            v = static_cast<int>(vv); h = static_cast<int>(hh); t = static_cast<int>(tt); bt = btt;
+        } else {
+            v = static_cast<int>(i % vec_per_half);
+            long long rest = i / vec_per_half;
+            h = static_cast<int>(rest % H);
+            bt = rest / H;
+            t = static_cast<int>(bt % Tlen);
+        }
         long long base = (bt * H + h) * HS + v * V::N;
         V x1 = V::load(inp + base), x2 = V::load(inp + base + half);
         if (h < Hq + Hkv) {
@@ -150,11 +180,11 @@ extern "C" int llmq_swiglu_forward(void* out, void* q_out, const void* inp, long
     if (dtype == 0) {
         if (D % 8) return -1;
         swiglu_fwd_kernel<bf16><<<grid_for(rows * (D / 8), 256, num_sms), 256, 0, s>>>(
-            static_cast<bf16*>(out), static_cast<e4m3*>(q_out), static_cast<const bf16*>(inp), rows, D, absmax, known_absmax, q_scale);
+            static_cast<bf16*>(out), static_cast<e4m3*>(q_out), static_cast<const bf16*>(inp), rows, D, absmax, known_absmax, q_scale, FastDiv(D / 8));
     } else if (dtype == 3) {
         if (D % 4) return -1;
         swiglu_fwd_kernel<float><<<grid_for(rows * (D / 4), 256, num_sms), 256, 0, s>>>(
-            static_cast<float*>(out), static_cast<e4m3*>(q_out), static_cast<const float*>(inp), rows, D, absmax, known_absmax, q_scale);
+            static_cast<float*>(out), static_cast<e4m3*>(q_out), static_cast<const float*>(inp), rows, D, absmax, known_absmax, q_scale, FastDiv(D / 4));
     } else return -10;
     return LLMQ_LAUNCH_CHECK();
 }
@@ -165,11 +195,11 @@ extern "C" int llmq_swiglu_backward(void* dinp, const void* dout, const void* in
     if (dtype == 0) {
         if (D % 8) return -1;
         swiglu_bwd_kernel<bf16><<<grid_for(rows * (D / 8), 256, num_sms), 256, 0, s>>>(
-            static_cast<bf16*>(dinp), static_cast<const bf16*>(dout), static_cast<const bf16*>(inp), rows, D, absmax);
+            static_cast<bf16*>(dinp), static_cast<const bf16*>(dout), static_cast<const bf16*>(inp), rows, D, absmax, FastDiv(D / 8));
     } else if (dtype == 3) {
         if (D % 4) return -1;
         swiglu_bwd_kernel<float><<<grid_for(rows * (D / 4), 256, num_sms), 256, 0, s>>>(
-            static_cast<float*>(dinp), static_cast<const float*>(dout), static_cast<const float*>(inp), rows, D, absmax);
+            static_cast<float*>(dinp), static_cast<const float*>(dout), static_cast<const float*>(inp), rows, D, absmax, FastDiv(D / 4));
     } else return -10;
     return LLMQ_LAUNCH_CHECK();
 }
@@ -180,16 +210,18 @@ extern "C" int llmq_rope(void* out, const void* inp, const float* freqs, int B, 
     const int H = Hq + 2 * Hkv;
     if (dtype == 0) {
         if ((HS / 2) % 8) return -1;
+        constexpr int VN = 8;
         long long work = static_cast<long long>(B) * T * H * (HS / 2 / 8);
         int g = grid_for(work, 256, num_sms);
-        if (backward) rope_kernel<bf16, true><<<g, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
-        else rope_kernel<bf16, false><<<g, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
+        if (backward) rope_kernel<bf16, true><<<g, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(inp), freqs, B, T, Hq, Hkv, HS, absmax, FastDiv(HS / 2 / VN), FastDiv(H), FastDiv(T));
+        else rope_kernel<bf16, false><<<g, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(inp), freqs, B, T, Hq, Hkv, HS, absmax, FastDiv(HS / 2 / VN), FastDiv(H), FastDiv(T));
     } else if (dtype == 3) {
         if ((HS / 2) % 4) return -1;
+        constexpr int VN = 4;
         long long work = static_cast<long long>(B) * T * H * (HS / 2 / 4);
         int g = grid_for(work, 256, num_sms);
-        if (backward) rope_kernel<float, true><<<g, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
-        else rope_kernel<float, false><<<g, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(inp), freqs, B, T, Hq, Hkv, HS, absmax);
+        if (backward) rope_kernel<float, true><<<g, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(inp), freqs, B, T, Hq, Hkv, HS, absmax, FastDiv(HS / 2 / VN), FastDiv(H), FastDiv(T));
+        else rope_kernel<float, false><<<g, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(inp), freqs, B, T, Hq, Hkv, HS, absmax, FastDiv(HS / 2 / VN), FastDiv(H), FastDiv(T));
     } else return -10;
     return LLMQ_LAUNCH_CHECK();
 }

@@ -75,6 +75,17 @@ template <> __device__ __forceinline__ __half from_float<__half>(float v) { retu
 template <> __device__ __forceinline__ e4m3 from_float<e4m3>(float v) { return e4m3(v); }   // saturating
 template <> __device__ __forceinline__ e5m2 from_float<e5m2>(float v) { return e5m2(v); }
 
+// Two floats -> two e4m3 bytes with one conversion instruction (saturating, round to nearest even).
+__device__ __forceinline__ uint32_t pack_e4m3x2(float lo, float hi) {
+    return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ uint2 pack_e4m3x8(const float (&f)[8]) {
+    uint2 r;
+    r.x = pack_e4m3x2(f[0], f[1]) | (pack_e4m3x2(f[2], f[3]) << 16);
+    r.y = pack_e4m3x2(f[4], f[5]) | (pack_e4m3x2(f[6], f[7]) << 16);
+    return r;
+}
+
 // 16-byte vector of T
 template <typename T>
 struct alignas(16) Vec16 {
@@ -92,6 +103,26 @@ struct alignas(16) Vec16 {
     }
     __device__ __forceinline__ void store(T* p) const { *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(v); }
     __device__ __forceinline__ void store_stream(T* p) const { __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(v)); }
+};
+
+// ------------------------------------------------------------------------------------------------
+// Division of a 31-bit index by a loop-invariant divisor with one multiply-high and a shift (the per-element
+// index arithmetic of the streaming kernels would otherwise cost more instructions than their math).
+struct FastDiv {
+    uint32_t d, mul, shr;
+    FastDiv() : d(1), mul(0), shr(0) {}
+    explicit FastDiv(uint32_t div) : d(div), mul(0), shr(0) {
+        if (div > 1) {
+            uint32_t lg = 0;
+            while ((1ull << lg) < div) ++lg;
+            const uint32_t p = 31 + lg;
+            mul = static_cast<uint32_t>(((1ull << p) + div - 1) / div);
+            shr = p - 32;
+        }
+    }
+    // n < 2^31
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : (__umulhi(n, mul) >> shr); }
+    __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const { q = div(n); r = n - q * d; }
 };
 
 // ------------------------------------------------------------------------------------------------

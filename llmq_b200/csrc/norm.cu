@@ -143,6 +143,78 @@ rmsnorm_bwd_kernel(T* __restrict__ dinp,               // in: upstream residual 
     block_absmax_commit(absmax_out, tmax, scratch);
 }
 
+// Same contract, for rows of up to 4 column vectors per thread: the row's dout, inp and residual gradient are
+// loaded once and stay in registers across the block-wide dot product (no second pass over L1 / L2), the norm
+// weights are loaded once per CTA, and three CTAs share an SM so that their reductions overlap.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 3 : 2)
+rmsnorm_bwd_reg_kernel(T* __restrict__ dinp, float* __restrict__ dw_partial, const T* __restrict__ dout, const T* __restrict__ inp,
+                       const T* __restrict__ weight, const float* __restrict__ rstd, int rows, int C, float* __restrict__ absmax_out) {
+    __shared__ float scratch[32];
+    using V = Vec16<T>;
+    float dw[VPT][V::N];
+    V vw[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = (k * NORM_THREADS + threadIdx.x) * V::N;
+        if (c < C) vw[k] = V::load(weight + c);
+#pragma unroll
+        for (int i = 0; i < V::N; ++i) dw[k][i] = 0.f;
+    }
+    float tmax = 0.f;
+    const float inv_c = 1.f / C;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* dy = dout + row * C;
+        const T* x = inp + row * C;
+        T* dx = dinp + row * C;
+        V vdy[VPT], vx[VPT], vd[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int c = (k * NORM_THREADS + threadIdx.x) * V::N;
+            if (c < C) { vdy[k] = V::load_stream(dy + c); vx[k] = V::load_stream(x + c); vd[k] = V::load(dx + c); }
+        }
+        const float rs = rstd[row];
+        float dot = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int c = (k * NORM_THREADS + threadIdx.x) * V::N;
+            if (c < C) {
+#pragma unroll
+                for (int i = 0; i < V::N; ++i) {
+                    const float xh = to_float(vx[k].v[i]) * rs;
+                    const float g = to_float(vdy[k].v[i]);
+                    dot += to_float(vw[k].v[i]) * g * xh;
+                    dw[k][i] += g * xh;
+                }
+            }
+        }
+        dot = block_reduce_sum(dot, scratch) * inv_c;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int c = (k * NORM_THREADS + threadIdx.x) * V::N;
+            if (c < C) {
+#pragma unroll
+                for (int i = 0; i < V::N; ++i) {
+                    const float xh = to_float(vx[k].v[i]) * rs;
+                    const float g = (to_float(vw[k].v[i]) * to_float(vdy[k].v[i]) - xh * dot) * rs;
+                    vd[k].v[i] = from_float<T>(to_float(vd[k].v[i]) + g);
+                    tmax = fmaxf(tmax, fabsf(to_float(vd[k].v[i])));
+                }
+                vd[k].store(dx + c);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = (k * NORM_THREADS + threadIdx.x) * V::N;
+        if (c < C) {
+#pragma unroll
+            for (int i = 0; i < V::N; ++i) dw_partial[static_cast<long long>(blockIdx.x) * C + c + i] = dw[k][i];
+        }
+    }
+    block_absmax_commit(absmax_out, tmax, scratch);
+}
+
 template <typename T>
 __global__ void rmsnorm_bwd_reduce_kernel(T* __restrict__ dweight, const float* __restrict__ dw_partial, int nparts, int C,
                                           int accumulate) {
@@ -176,12 +248,17 @@ int launch_bwd(void* dinp, void* dweight, float* scratch, const void* dout, cons
     rmsnorm_bwd_kernel<T, VPT><<<num_blocks, NORM_THREADS, 0, s>>>(static_cast<T*>(dinp), scratch,                    \
                                                                    static_cast<const T*>(dout), static_cast<const T*>(inp), \
                                                                    static_cast<const T*>(w), rstd, rows, C, absmax)
-    if (vecs <= 1) LAUNCH(1);
-    else if (vecs <= 2) LAUNCH(2);
-    else if (vecs <= 4) LAUNCH(4);
+#define LAUNCH_REG(VPT)                                                                                               \
+    rmsnorm_bwd_reg_kernel<T, VPT><<<num_blocks, NORM_THREADS, 0, s>>>(static_cast<T*>(dinp), scratch,                \
+                                                                       static_cast<const T*>(dout), static_cast<const T*>(inp), \
+                                                                       static_cast<const T*>(w), rstd, rows, C, absmax)
+    if (vecs <= 1) LAUNCH_REG(1);
+    else if (vecs <= 2) LAUNCH_REG(2);
+    else if (vecs <= 4) LAUNCH_REG(4);
     else if (vecs <= 8) LAUNCH(8);
     else return -2;
 #undef LAUNCH
+#undef LAUNCH_REG
     int rc = LLMQ_LAUNCH_CHECK();
     if (rc) return rc;
     rmsnorm_bwd_reduce_kernel<T><<<ceil_div_i(C, 256), 256, 0, s>>>(static_cast<T*>(dweight), scratch, num_blocks, C, accumulate_dw);

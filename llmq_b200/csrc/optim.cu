@@ -45,6 +45,39 @@ template <> __device__ __forceinline__ void store8_sr<float>(float* p, const flo
     *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
 }
 
+// Random words for one thread-iteration (8 elements x {param, m, v}): one full hash of the element counter,
+// then cheap multiply / xor-shift steps.  Depends only on (element index, seed), never on launch geometry.
+struct SrWords {
+    uint32_t h;
+    __device__ __forceinline__ SrWords(uint64_t ctr, uint32_t seed) : h(rng_u32(ctr, seed)) {}
+    __device__ __forceinline__ uint32_t get(uint32_t j) const {
+        uint32_t x = (h + j * 0x9e3779b9u) * 0x85ebca6bu;
+        x ^= x >> 15;
+        x *= 0xc2b2ae35u;
+        return x ^ (x >> 16);
+    }
+};
+__device__ __forceinline__ float sqrt_approx(float x) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+template <typename T> __device__ __forceinline__ void store8_srw(T* p, const float (&f)[8], const SrWords& w, uint32_t j0);
+template <> __device__ __forceinline__ void store8_srw<bf16>(bf16* p, const float (&f)[8], const SrWords& w, uint32_t j0) {
+    Vec16<bf16> v;
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        const uint32_t r = w.get(j0 + i / 2);
+        v.v[i] = sr_bf16(f[i], r);
+        v.v[i + 1] = sr_bf16(f[i + 1], r >> 16);
+    }
+    v.store(p);
+}
+template <> __device__ __forceinline__ void store8_srw<float>(float* p, const float (&f)[8], const SrWords&, uint32_t) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
 // One thread updates 8 consecutive parameters.  For e4m3 first moments 16 consecutive threads share one
 // fp32 scale (128 elements); the scale is recomputed from the new values every step.
 template <typename P, typename G, typename M, typename Vv>
@@ -83,9 +116,10 @@ adamw_kernel(P* __restrict__ param, const G* __restrict__ grad, M* __restrict__ 
             m[k] = beta1 * m[k] + (1.f - beta1) * gk;
             v[k] = beta2 * v[k] + (1.f - beta2) * gk * gk;
             float mh = m[k] * bc1, vh = v[k] * bc2;
-            p[k] -= lr * (mh / (sqrtf(vh) + eps) + wd * p[k]);
+            p[k] -= lr * (__fdividef(mh, sqrt_approx(vh) + eps) + wd * p[k]);
         }
         const uint64_t ctr = static_cast<uint64_t>(e + elem_offset);
+        const SrWords words(ctr, seed);
         if constexpr (sizeof(M) == 1) {
             float am = 0.f;
 #pragma unroll
@@ -98,30 +132,29 @@ adamw_kernel(P* __restrict__ param, const G* __restrict__ grad, M* __restrict__ 
                 float inv = 1.f / sc;
 #pragma unroll
                 for (int k = 0; k < 8; k += 2) {
-                    uint32_t r = rng_u32(ctr + k / 2, seed ^ 0x5bd1e995u);
-                    q[k] = sr_e4m3(m[k] * inv, r);
-                    q[k + 1] = sr_e4m3(m[k + 1] * inv, r * 0x9e3779b1u + 0x7f4a7c15u);
+                    q[k] = sr_e4m3(m[k] * inv, words.get(4 + k));
+                    q[k + 1] = sr_e4m3(m[k + 1] * inv, words.get(5 + k));
                 }
                 *reinterpret_cast<uint2*>(m_state + e) = *reinterpret_cast<uint2*>(q);
                 if ((i & 15) == 0) m_scales[e / 128] = sc;
             }
         } else {
-            if (active) store8_sr<M>(m_state + e, m, ctr, seed ^ 0x5bd1e995u);
+            if (active) store8_srw<M>(m_state + e, m, words, 4);
         }
         if (active) {
-            store8_sr<Vv>(v_state + e, v, ctr, seed ^ 0x1b873593u);
+            store8_srw<Vv>(v_state + e, v, words, 12);
             if constexpr (sizeof(P) == 2) {
                 Vec16<bf16> o;
 #pragma unroll
                 for (int k = 0; k < 8; k += 2) {
-                    uint32_t r = rng_u32(ctr + k / 2, seed);
+                    uint32_t r = words.get(k / 2);
                     o.v[k] = sr_bf16(p[k], r);
                     o.v[k + 1] = sr_bf16(p[k + 1], r >> 16);
                     tmax = fmaxf(tmax, fmaxf(fabsf(__bfloat162float(o.v[k])), fabsf(__bfloat162float(o.v[k + 1]))));
                 }
                 o.store(reinterpret_cast<bf16*>(param) + e);
             } else {
-                store8_sr<float>(reinterpret_cast<float*>(param) + e, p, ctr, seed);
+                store8_srw<float>(reinterpret_cast<float*>(param) + e, p, words, 0);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) tmax = fmaxf(tmax, fabsf(p[k]));
             }

@@ -3,7 +3,7 @@
     python -m llmq_b200.ops.bench gemm --m 16384 --n 37888 --k 3584 --dtype fp8 [--a-mn] [--b-mn] [--mode 0|1|2]
     python -m llmq_b200.ops.bench attention --b 8 --t 2048 --hq 28 --hkv 4 --hs 128
     python -m llmq_b200.ops.bench elementwise --rows 16384 --c 3584 --d 18944
-    python -m llmq_b200.ops.bench adamw --n 134217728
+    python -m llmq_b200.ops.bench adamw --numel 134217728
 
 Prints achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` is found at the repository root, the
 fraction of the measured cuBLAS bf16 / copy-bandwidth peak.  ``--iters 1 --no-flush`` gives a run that is
@@ -113,13 +113,27 @@ def bench_elementwise(a, tm):
     res["swiglu_forward"] = (ms, rows * D * 6)
     ms = tm.time(lambda: K.swiglu_backward(up, sw, up, absmax=am))
     res["swiglu_backward"] = (ms, rows * D * 10)
+    swq = torch.empty(rows, D, dtype=torch.float8_e4m3fn, device=DEV)
+    up2 = _rand((rows, 2 * D), torch.bfloat16)
+    am.fill_(8.0)
+    ms = tm.time(lambda: K.swiglu_forward(None, up2, q_out=swq, known_absmax=am, q_scale=sc))
+    res["swiglu_forward_quant"] = (ms, rows * D * 5)
+    ms = tm.time(lambda: K.quantize(swq, sc, sw, am))
+    res["quantize_e4m3_large"] = (ms, rows * D * 3)
+    ms = tm.time(lambda: K.abs_max(am, x))
+    res["abs_max"] = (ms, rows * C * 2)
+    hq, hkv, hs = 28, 4, 128
+    qkv = _rand((rows // 2048, 2048, hq + 2 * hkv, hs), torch.bfloat16)
+    freqs = K.rope_table(2048, hs, 1e6, DEV)
+    ms = tm.time(lambda: K.rope(qkv, qkv, freqs, hq, hkv, absmax=am))
+    res["rope"] = (ms, qkv.numel() * 4)
     out = {k: {"ms": round(v[0], 4), "gbs": round(v[1] / v[0] / 1e6, 1), f"frac_of_{src}_hbm": round(v[1] / v[0] / 1e6 / bw, 3)} for k, v in res.items()}
     print(json.dumps({"op": "elementwise", "rows": rows, "c": C, "d": D, **out}))
 
 
 def bench_adamw(a, tm):
     _, bw, src = _peaks()
-    n = a.n
+    n = a.numel
     p, g = _rand((n,), torch.bfloat16), _rand((n,), torch.bfloat16)
     m, v = torch.zeros(n, dtype=torch.bfloat16, device=DEV), torch.zeros(n, dtype=torch.bfloat16, device=DEV)
     gs, am = torch.ones(1, device=DEV), torch.zeros(1, device=DEV)
@@ -150,6 +164,7 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--c", type=int, default=3584)
     ap.add_argument("--d", type=int, default=18944)
+    ap.add_argument("--numel", type=int, default=1 << 28)
     a = ap.parse_args()
     tm = Timer(a.iters, a.warmup, not a.no_flush)
     {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw}[a.op](a, tm)

@@ -158,8 +158,11 @@ def rmsnorm_forward(y: Optional[torch.Tensor], rstd: Optional[torch.Tensor], inp
             q_scale.copy_((am / 448.0).reshape_as(q_scale))
 
 
+NORM_BWD_BLOCKS_PER_SM = 3         # persistent CTAs of the RMSNorm backward that share an SM
+
+
 def rmsnorm_backward_scratch_elems(C: int, device) -> int:
-    blocks = 2 * num_sms(device) if torch.device(device).type == "cuda" else 1
+    blocks = NORM_BWD_BLOCKS_PER_SM * num_sms(device) if torch.device(device).type == "cuda" else 1
     return blocks * C
 
 
@@ -170,7 +173,7 @@ def rmsnorm_backward(dinp: torch.Tensor, dweight: torch.Tensor, scratch: Optiona
     C = inp.shape[-1]
     rows = inp.numel() // C
     if inp.is_cuda:
-        blocks = 2 * num_sms(inp.device)
+        blocks = NORM_BWD_BLOCKS_PER_SM * num_sms(inp.device)
         assert scratch is not None and scratch.numel() >= blocks * C and scratch.dtype == torch.float32
         rc = L.kernels().llmq_rmsnorm_backward(
             L.ptr(dinp), L.ptr(dweight), L.ptr(scratch), L.ptr(dout), L.ptr(inp), L.ptr(weight), L.ptr(rstd), rows, C,
