@@ -25,6 +25,27 @@ using namespace sm100;
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
+// Backward kernels: four warpgroups share the 128 rows of a tile, each thread owns 16 score columns of its row, so
+// every scheduler has four warps to hide the latency of the exp / TMEM / shared-memory chain.
+constexpr int kBwdWarpgroups = 4;
+constexpr int kBwdComputeThreads = 128 * kBwdWarpgroups;
+constexpr int kBwdComputeWarps = kBwdComputeThreads / 32;
+constexpr int kBwdThreads = kBwdComputeThreads + 32;          // + one warp that only loads tiles and issues MMAs
+// barrier 1: the compute threads among themselves (barrier 0 is __syncthreads of the whole CTA)
+// One arrival per warp (512 single arrivals on one shared-memory word would serialise): the lanes' earlier
+// writes and fences are ordered before lane 0's releasing arrive by the warp barrier.
+__device__ __forceinline__ void warp_arrive(uint32_t bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+__device__ __forceinline__ void compute_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kBwdComputeThreads) : "memory"); }
+
+// 2^x with the hardware approximation (-inf -> 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
 
 // low descriptor half of (base + byte offset); the base part is loop invariant, the offset a constant after unrolling
 #define DLO(base, lbo, off) (desc_lo((base), (lbo)) + static_cast<uint32_t>((off) >> 4))
@@ -315,32 +336,67 @@ attn_delta_kernel(float* __restrict__ delta, const bf16* __restrict__ o, const b
 }
 
 // ------------------------------------------------------------------------------------------------
-// dK / dV
+// dK / dV.  Software pipeline over the (query head, query block) walk: while the threads turn S(it) / dP(it) into
+// P^T and dS^T, the tensor core already computes S(it+1) / dP(it+1) (score tiles are double buffered in TMEM) and
+// finishes dV / dK of tile it-1.  Q / dO tiles sit in a ring of four shared-memory buffers, loaded three tiles
+// ahead; P^T / dS^T are kept in registers until the MMAs that read the previous pair have completed.
+// 16 consecutive bf16 values (8 packed words): columns c0 .. c0+15 of row `row`
+__device__ __forceinline__ void store_row_chunk16_swz_packed(uint8_t* tile, int row, int c0, const uint32_t (&v)[8]) {
+    uint8_t* rowp = tile + row * 128;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const uint4 o = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+        const int u = (c0 >> 3) + g;
+        *reinterpret_cast<uint4*>(rowp + ((u ^ (row & 7)) << 4)) = o;
+    }
+}
+// 16 fp32 accumulator values of one row -> 16 bf16 in global memory (32 bytes)
+__device__ __forceinline__ void store16_bf16(bf16* dst, const uint32_t (&r)[16]) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        uint4 o;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) ob[jj] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * jj]), __uint_as_float(r[g * 8 + 2 * jj + 1]));
+        *reinterpret_cast<uint4*>(dst + g * 8) = o;
+    }
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 template <int HS>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, box 128 rows (K and V tiles)
                      const __grid_constant__ CUtensorMap tmap_q64,     // qkv, box 64 rows (Q tiles)
                      const __grid_constant__ CUtensorMap tmap_do64,    // dO, box 64 rows
                      const AttnParams p) {
-    constexpr int BKV = 128, BQ = 64, NCH = HS / 64;
+    constexpr int BKV = 128, BQ = 64, NCH = HS / 64, NBUF = 4;
     constexpr int KV_BYTES = BKV * HS * 2, Q_BYTES = BQ * HS * 2, PT_BYTES = BKV * BQ * 2;
-    constexpr uint32_t TMEM_COLS = (2 * BQ + 2 * HS) <= 256 ? 256 : 512;
+    constexpr uint32_t TMEM_COLS = 512;                       // S0 S1 | dP0 dP1 | dV | dK
+    constexpr int CW = BQ / kBwdWarpgroups;                   // score columns per compute thread
+    static_assert(CW == 16, "the column split below is written for 16 columns per thread");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = sK + KV_BYTES;
-    uint8_t* sQ = sV + KV_BYTES;            // 2 buffers
-    uint8_t* sdO = sQ + 2 * Q_BYTES;        // 2 buffers
-    uint8_t* sPT = sdO + 2 * Q_BYTES;
+    uint8_t* sQ = sV + KV_BYTES;              // NBUF buffers
+    uint8_t* sdO = sQ + NBUF * Q_BYTES;       // NBUF buffers
+    uint8_t* sPT = sdO + NBUF * Q_BYTES;
     uint8_t* sdST = sPT + PT_BYTES;
-    float* sLse = reinterpret_cast<float*>(sdST + PT_BYTES);      // [64] pre-multiplied by log2(e)
-    float* sDelta = sLse + BQ;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + BQ);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    float* sLse = reinterpret_cast<float*>(sdST + PT_BYTES);      // [2][64] pre-multiplied by log2(e)
+    float* sDelta = sLse + 2 * BQ;                                // [2][64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * BQ);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    const bool issuer = warp == kBwdComputeWarps;             // the extra warp: TMA producer + MMA issuer (lane 0)
+    const int wg = tid >> 7, r = tid & 127;                   // compute threads: column slice, row of the tile (TMEM lane)
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
-    const int kb = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // 1-D grid, key block slowest: the blocks with the longest walks (small kb) start first on every SM
+    const int kb = blockIdx.x / (p.Hkv * p.B);
+    const int kvh = (blockIdx.x % (p.Hkv * p.B)) % p.Hkv, b = (blockIdx.x % (p.Hkv * p.B)) / p.Hkv;
     const int G = p.Hq / p.Hkv;
     const int kv0 = kb * BKV;
     const int nqb = (p.T + BQ - 1) / BQ;
@@ -349,150 +405,194 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     const int n_it = per_head * G;
     const int kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
+    // barriers: 0 kv | 1-4 q/dO ring | 5 sp (scores ready) | 6 acc (dV/dK MMAs of a tile done) | 7 p_ready (P^T/dS^T stored)
+    //           8-9 s_free (score buffer read by all compute threads)
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t kv_bar = bar0, qdo_bar0 = bar0 + 8 /* +16 */, sp_bar = bar0 + 24, acc_bar = bar0 + 32;
+    // Two score barriers, used alternately: the commit of tile it+2 needs every compute warp to have read tile it, so a
+    // waiter can never miss a phase (with one barrier, tiles 0 and 1 can both complete before a slow warp looks).
+    const uint32_t kv_bar = bar0, acc_bar = bar0 + 48, p_ready = bar0 + 56;
+    auto sp_bar = [&](int it) { return (it & 1) ? bar0 + 80 : bar0 + 40; };
+    auto qdo_bar = [&](int buf) { return bar0 + 8 + 8 * buf; };
+    auto s_free = [&](int buf) { return bar0 + 64 + 8 * buf; };
     if (tid == 0) {
-        for (int i = 0; i < 5; ++i) mbar_init(bar0 + 8 * i, 1);
+        for (int i = 0; i < 7; ++i) mbar_init(bar0 + 8 * i, 1);
+        mbar_init(bar0 + 80, 1);
+        mbar_init(p_ready, kBwdComputeWarps);
+        mbar_init(s_free(0), kBwdComputeWarps);
+        mbar_init(s_free(1), kBwdComputeWarps);
         *abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    if (issuer) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tS = tmem, tdP = tmem + BQ, tdV = tmem + 2 * BQ, tdK = tmem + 2 * BQ + HS;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-
-    auto issue_qdo = [&](int it) {
-        const int hq = kvh * G + it / per_head;
-        const int qb = qb_first + it % per_head;
-        const int buf = it & 1;
-        const uint32_t bar = qdo_bar0 + 8 * buf;
-        mbar_expect_tx(bar, 2 * Q_BYTES);
-        for (int c = 0; c < NCH; ++c) {
-            tma_load_3d(smem_u32(sQ) + buf * Q_BYTES + c * (BQ * 128), &tmap_q64, bar, hq * HS + c * 64, qb * BQ, b);
-            tma_load_3d(smem_u32(sdO) + buf * Q_BYTES + c * (BQ * 128), &tmap_do64, bar, hq * HS + c * 64, qb * BQ, b);
-        }
-    };
-    if (tid == 0 && n_it > 0) {
-        tma_prefetch_desc(&tmap_kv128); tma_prefetch_desc(&tmap_q64); tma_prefetch_desc(&tmap_do64);
-        mbar_expect_tx(kv_bar, 2 * KV_BYTES);
-        for (int c = 0; c < NCH; ++c) {
-            tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv128, kv_bar, kcol + c * 64, kv0, b);
-            tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv128, kv_bar, vcol + c * 64, kv0, b);
-        }
-        issue_qdo(0);
-    }
-
-    const uint32_t idesc_st = make_instr_desc(1, 1, false, false, BKV, BQ);     // S^T = K Q^T, dP^T = V dO^T
-    const uint32_t idesc_acc = make_instr_desc(1, 1, false, true, BKV, HS);      // dV += P^T dO, dK += dS^T Q
-    const float sl2 = p.scale * kLog2e;
-    const int kv_row = kv0 + tid;
+    const uint32_t tdV = tmem + 4 * BQ, tdK = tmem + 4 * BQ + HS;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    auto tile_of = [&](int it, int& hq, int& qb) { hq = kvh * G + it / per_head; qb = qb_first + it % per_head; };
     bool ok = true;
 
-    for (int it = 0; it < n_it && ok; ++it) {
-        const int hq = kvh * G + it / per_head;
-        const int qb = qb_first + it % per_head;
-        const int buf = it & 1;
-        const uint32_t par = it & 1;
-        if (tid == 0 && it + 1 < n_it) issue_qdo(it + 1);        // other buffer was released by acc_bar of it-1
-        {
-            const int q = qb * BQ + (tid & 63);
-            const long long si = (static_cast<long long>(b) * p.Hq + hq) * p.T + q;
-            if (tid < 64) sLse[tid] = q < p.T ? p.lse[si] * kLog2e : INFINITY;
-            else sDelta[tid - 64] = q < p.T ? p.delta[si] : 0.f;
-        }
-        if (tid == 0) {
-            if (it == 0) ok = mbar_wait(kv_bar, 0, abort_flag);
-            ok = ok && mbar_wait(qdo_bar0 + 8 * buf, (it >> 1) & 1, abort_flag);
-            tc_fence_after_sync();
-            if (ok) {
+    if (issuer) {
+        // ============================================================ producer / issuer warp
+        if ((tid & 31) == 0 && n_it > 0) {
+            auto issue_qdo = [&](int it) {
+                int hq, qb; tile_of(it, hq, qb);
+                const int buf = it % NBUF;
+                mbar_expect_tx(qdo_bar(buf), 2 * Q_BYTES);
+                for (int c = 0; c < NCH; ++c) {
+                    tma_load_3d(smem_u32(sQ) + buf * Q_BYTES + c * (BQ * 128), &tmap_q64, qdo_bar(buf), hq * HS + c * 64, qb * BQ, b);
+                    tma_load_3d(smem_u32(sdO) + buf * Q_BYTES + c * (BQ * 128), &tmap_do64, qdo_bar(buf), hq * HS + c * 64, qb * BQ, b);
+                }
+            };
+            const uint32_t idesc_st = make_instr_desc(1, 1, false, false, BKV, BQ);     // S^T = K Q^T, dP^T = V dO^T
+            const uint32_t idesc_acc = make_instr_desc(1, 1, false, true, BKV, HS);      // dV += P^T dO, dK += dS^T Q
+            auto issue_sp = [&](int it) {
+                const int buf = it % NBUF;
+                const uint32_t tS = tmem + (it & 1) * BQ, tdP = tmem + 2 * BQ + (it & 1) * BQ;
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
                     mma_issue<false, false>(tS, DLO(smem_u32(sK), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi,
-                                            DLO(smem_u32(sQ), 16, buf * Q_BYTES + (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
+                                            DLO(smem_u32(sQ) + buf * Q_BYTES, 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
                 }
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
                     mma_issue<false, false>(tdP, DLO(smem_u32(sV), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi,
-                                            DLO(smem_u32(sdO), 16, buf * Q_BYTES + (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
+                                            DLO(smem_u32(sdO) + buf * Q_BYTES, 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
                 }
-                mma_commit(sp_bar);
+                mma_commit(sp_bar(it));
+            };
+            tma_prefetch_desc(&tmap_kv128); tma_prefetch_desc(&tmap_q64); tma_prefetch_desc(&tmap_do64);
+            mbar_expect_tx(kv_bar, 2 * KV_BYTES);
+            for (int c = 0; c < NCH; ++c) {
+                tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv128, kv_bar, kcol + c * 64, kv0, b);
+                tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv128, kv_bar, vcol + c * 64, kv0, b);
             }
-        }
-        __syncthreads();                                            // sLse / sDelta visible
-        if (!mbar_wait(sp_bar, par, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-        const bool diag = qb * BQ < kv0 + BKV;                      // some (kv, q) pairs have q < kv
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < BQ / 32; ++c) {
-            uint32_t rs[32], rp[32];
-            tmem_ld_32x32b_x32(tS + lane_off + c * 32, rs);
-            tmem_ld_32x32b_x32(tdP + lane_off + c * 32, rp);
-            tmem_ld_wait();
-            float pt[32], ds[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int qi = c * 32 + i;
-                float pv = exp2f(__uint_as_float(rs[i]) * sl2 - sLse[qi]);
-                if (diag && (qb * BQ + qi < kv_row)) pv = 0.f;
-                pt[i] = pv;
-                ds[i] = pv * (__uint_as_float(rp[i]) - sDelta[qi]) * p.scale;
-            }
-            store_row_chunk_swz(sPT, tid, c * 32, pt);
-            store_row_chunk_swz(sdST, tid, c * 32, ds);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
-        if (tid == 0) {
+            for (int i = 0; i < NBUF - 1 && i < n_it; ++i) issue_qdo(i);
+            ok = mbar_wait(kv_bar, 0, abort_flag) && mbar_wait(qdo_bar(0), 0, abort_flag);
             tc_fence_after_sync();
+            if (ok) issue_sp(0);
+            for (int it = 0; it < n_it && ok; ++it) {
+                if (it + 1 < n_it) {
+                    // scores of tile it+1 overwrite the buffer of tile it-1: every compute thread must have read it
+                    ok = mbar_wait(qdo_bar((it + 1) % NBUF), ((it + 1) / NBUF) & 1, abort_flag);
+                    if (ok && it >= 1) ok = mbar_wait(s_free((it + 1) & 1), ((it - 1) >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_sp(it + 1);
+                }
+                // dV / dK of tile it-1 done: its Q / dO buffer, (it - 1) % NBUF, takes tile it + NBUF - 1
+                if (it >= 1 && !mbar_wait(acc_bar, (it - 1) & 1, abort_flag)) { ok = false; break; }
+                if (it + NBUF - 1 < n_it) issue_qdo(it + NBUF - 1);
+                if (!mbar_wait(p_ready, it & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const int buf = it % NBUF;
 #pragma unroll
-            for (int k = 0; k < BQ / 16; ++k) {
-                mma_issue<false, false>(tdV, DLO(smem_u32(sPT), 16, k * 32), kDescHi,
-                                        DLO(smem_u32(sdO), BQ * 128, buf * Q_BYTES + k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
-            }
+                for (int k = 0; k < BQ / 16; ++k) {
+                    mma_issue<false, false>(tdV, DLO(smem_u32(sPT), 16, k * 32), kDescHi,
+                                            DLO(smem_u32(sdO) + buf * Q_BYTES, BQ * 128, k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
+                }
 #pragma unroll
-            for (int k = 0; k < BQ / 16; ++k) {
-                mma_issue<false, false>(tdK, DLO(smem_u32(sdST), 16, k * 32), kDescHi,
-                                        DLO(smem_u32(sQ), BQ * 128, buf * Q_BYTES + k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
+                for (int k = 0; k < BQ / 16; ++k) {
+                    mma_issue<false, false>(tdK, DLO(smem_u32(sdST), 16, k * 32), kDescHi,
+                                            DLO(smem_u32(sQ) + buf * Q_BYTES, BQ * 128, k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
+                }
+                mma_commit(acc_bar);
             }
-            mma_commit(acc_bar);
+            if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
         }
-        if (!mbar_wait(acc_bar, par, abort_flag)) { ok = false; break; }
+    } else {
+        // ============================================================ compute warps
+        auto load_stats = [&](int it) {                         // lse (threads 0-63) and delta (64-127) of tile it
+            if (tid >= 128) return;
+            int hq, qb; tile_of(it, hq, qb);
+            const int q = qb * BQ + (tid & 63);
+            const long long si = (static_cast<long long>(b) * p.Hq + hq) * p.T + q;
+            float* dst = (tid < 64 ? sLse : sDelta) + (it & 1) * BQ + (tid & 63);
+            if (tid < 64) *dst = q < p.T ? p.lse[si] * kLog2e : INFINITY;
+            else *dst = q < p.T ? p.delta[si] * p.scale : 0.f;       // delta pre-multiplied by the softmax scale
+        };
+        const float sl2 = p.scale * kLog2e;
+        const int kv_row = kv0 + r;
+        const int c0 = wg * CW;
+        if (n_it > 0) load_stats(0);
+        compute_barrier();
+        // One tile; false when a wait ran out.  The caller still runs the barrier of every remaining tile, so that a
+        // failure can never leave part of the CTA behind at a barrier.
+        auto tile_body = [&](int it) -> bool {
+            int hq, qb; tile_of(it, hq, qb);
+            if (it + 1 < n_it) load_stats(it + 1);             // read after the barrier at the end of this tile
+            if (!mbar_wait(sp_bar(it), (it >> 1) & 1, abort_flag)) return false;
+            tc_fence_after_sync();
+            const bool diag = qb * BQ < kv0 + BKV;              // some (kv, q) pairs have q < kv
+            const float* lse_t = sLse + (it & 1) * BQ;
+            const float* delta_t = sDelta + (it & 1) * BQ;
+            const uint32_t tS = tmem + (it & 1) * BQ, tdP = tmem + 2 * BQ + (it & 1) * BQ;
+            uint32_t ptp[CW / 2], dsp[CW / 2];
+            {
+                uint32_t rs[CW], rp[CW];
+                tmem_ld_32x32b_x16(tS + lane_off + c0, rs);
+                tmem_ld_32x32b_x16(tdP + lane_off + c0, rp);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                warp_arrive(s_free(it & 1));                    // this score buffer may be overwritten
+                float lse_c[CW], del_c[CW];
+#pragma unroll
+                for (int i = 0; i < CW; i += 4) {
+                    *reinterpret_cast<float4*>(lse_c + i) = *reinterpret_cast<const float4*>(lse_t + c0 + i);
+                    *reinterpret_cast<float4*>(del_c + i) = *reinterpret_cast<const float4*>(delta_t + c0 + i);
+                }
+                float pv[CW], ds[CW];
+#pragma unroll
+                for (int i = 0; i < CW; ++i) {
+                    pv[i] = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse_c[i]));
+                    ds[i] = fmaf(__uint_as_float(rp[i]), p.scale, -del_c[i]);
+                }
+                if (diag) {                                     // only tiles that touch the diagonal pay for the mask
+                    const int lim = kv_row - qb * BQ - c0;      // columns below lim are above the diagonal (q < kv)
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) if (i < lim) pv[i] = 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < CW; i += 2) {
+                    ptp[i / 2] = pack_bf16x2(pv[i], pv[i + 1]);
+                    dsp[i / 2] = pack_bf16x2(pv[i] * ds[i], pv[i + 1] * ds[i + 1]);
+                }
+            }
+            // P^T / dS^T of tile it-1 are read by its dV / dK MMAs until acc_bar completes
+            if (it > 0 && !mbar_wait(acc_bar, (it - 1) & 1, abort_flag)) return false;
+            store_row_chunk16_swz_packed(sPT, r, c0, ptp);
+            store_row_chunk16_swz_packed(sdST, r, c0, dsp);
+            fence_proxy_async_smem();
+            warp_arrive(p_ready);
+            return true;
+        };
+        for (int it = 0; it < n_it; ++it) {
+            if (ok) ok = tile_body(it);
+            compute_barrier();                                  // statistics of tile it+1 visible to all compute threads
+        }
+        if (ok && n_it > 0) ok = mbar_wait(acc_bar, (n_it - 1) & 1, abort_flag);
         tc_fence_after_sync();
-    }
-    if (!ok && tid == 0) atomicOr(p.status, kErrOther);
-
-    if (ok && n_it > 0) {
-        // The TMEM loads are warp-collective: every lane executes them, only the stores are predicated.
-        const bool row_ok = kv_row < p.T;
-        const int H = p.Hq + 2 * p.Hkv;
-        const long long rbase = (static_cast<long long>(b) * p.T + (row_ok ? kv_row : 0)) * H;
-        bf16* dk = p.dqkv + (rbase + p.Hq + kvh) * HS;
-        bf16* dv = p.dqkv + (rbase + p.Hq + p.Hkv + kvh) * HS;
-        __syncwarp();
+        if (!ok && r == 0) atomicOr(p.status, kErrOther);
+        if (ok && n_it > 0) {
+            // The TMEM loads are warp-collective: every lane executes them, only the stores are predicated.
+            const bool row_ok = kv_row < p.T;
+            const int H = p.Hq + 2 * p.Hkv;
+            const long long rbase = (static_cast<long long>(b) * p.T + (row_ok ? kv_row : 0)) * H;
+            bf16* dk = p.dqkv + (rbase + p.Hq + kvh) * HS;
+            bf16* dv = p.dqkv + (rbase + p.Hq + p.Hkv + kvh) * HS;
+            __syncwarp();
+            constexpr int ECW = HS / kBwdWarpgroups;           // output columns per thread
 #pragma unroll
-        for (int c = 0; c < HS / 32; ++c) {
-            uint32_t rk[32], rv[32];
-            tmem_ld_32x32b_x32(tdK + lane_off + c * 32, rk);
-            tmem_ld_32x32b_x32(tdV + lane_off + c * 32, rv);
-            tmem_ld_wait();
-            if (row_ok) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 ok4, ov4;
-                    __nv_bfloat162* kb2 = reinterpret_cast<__nv_bfloat162*>(&ok4);
-                    __nv_bfloat162* vb2 = reinterpret_cast<__nv_bfloat162*>(&ov4);
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        kb2[jj] = __floats2bfloat162_rn(__uint_as_float(rk[g * 8 + 2 * jj]), __uint_as_float(rk[g * 8 + 2 * jj + 1]));
-                        vb2[jj] = __floats2bfloat162_rn(__uint_as_float(rv[g * 8 + 2 * jj]), __uint_as_float(rv[g * 8 + 2 * jj + 1]));
-                    }
-                    *reinterpret_cast<uint4*>(dk + c * 32 + g * 8) = ok4;
-                    *reinterpret_cast<uint4*>(dv + c * 32 + g * 8) = ov4;
+            for (int c = 0; c < ECW; c += 16) {
+                const int col = wg * ECW + c;
+                uint32_t rk[16], rv[16];
+                tmem_ld_32x32b_x16(tdK + lane_off + col, rk);
+                tmem_ld_32x32b_x16(tdV + lane_off + col, rv);
+                tmem_ld_wait();
+                if (row_ok) {
+                    store16_bf16(dk + col, rk);
+                    store16_bf16(dv + col, rv);
                 }
             }
         }
@@ -500,166 +600,192 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+    if (issuer) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------------------------------
-// dQ
+// dQ.  Same software pipeline as dK / dV: S(j+1) / dP(j+1) run on the tensor core while the threads compute dS(j);
+// K / V tiles sit in a ring of four buffers loaded three tiles ahead; dQ accumulates in TMEM over the key walk.
 template <int HS>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box 128 rows
                    const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64 rows
                    const __grid_constant__ CUtensorMap tmap_do128,   // dO, box 128 rows
                    const AttnParams p) {
-    constexpr int BQ = 128, BKV = 64, NCH = HS / 64;
+    constexpr int BQ = 128, BKV = 64, NCH = HS / 64, NBUF = 4;
     constexpr int Q_BYTES = BQ * HS * 2, KV_BYTES = BKV * HS * 2, DS_BYTES = BQ * BKV * 2;
-    constexpr uint32_t TMEM_COLS = (2 * BKV + HS) <= 256 ? 256 : 512;
+    constexpr uint32_t TMEM_COLS = 512;                       // S0 S1 | dP0 dP1 | dQ
+    constexpr int CW = BKV / kBwdWarpgroups;
+    static_assert(CW == 16, "the column split below is written for 16 columns per thread");
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sdO = sQ + Q_BYTES;
-    uint8_t* sK = sdO + Q_BYTES;
-    uint8_t* sV = sK + KV_BYTES;
-    uint8_t* sdS = sV + KV_BYTES;
+    uint8_t* sK = sdO + Q_BYTES;              // NBUF buffers
+    uint8_t* sV = sK + NBUF * KV_BYTES;       // NBUF buffers
+    uint8_t* sdS = sV + NBUF * KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + DS_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    const bool issuer = warp == kBwdComputeWarps;
+    const int wg = tid >> 7, r = tid & 127;
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
-    const int qb = gridDim.x - 1 - blockIdx.x;
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int nqb = (p.T + BQ - 1) / BQ;
+    const int qb = nqb - 1 - blockIdx.x / (p.Hq * p.B);         // 1-D grid, longest key walks first
+    const int h = (blockIdx.x % (p.Hq * p.B)) % p.Hq, b = (blockIdx.x % (p.Hq * p.B)) / p.Hq;
     const int kvh = h / (p.Hq / p.Hkv);
     const int q0 = qb * BQ;
     const int n_kv = min((p.T + BKV - 1) / BKV, (q0 + BQ) / BKV);
     const int kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
+    // barriers: 0 q/dO | 1-4 k/v ring | 5 sp | 6 dq (dQ MMA of a tile done) | 7 p_ready (dS stored) | 8-9 s_free
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_bar = bar0, k_bar = bar0 + 8, v_bar = bar0 + 16, sp_bar = bar0 + 24, dq_bar = bar0 + 32;
+    const uint32_t q_bar = bar0, dq_bar = bar0 + 48, p_ready = bar0 + 56;
+    auto sp_bar = [&](int j) { return (j & 1) ? bar0 + 80 : bar0 + 40; };        // alternating, see the dK / dV kernel
+    auto kv_bar = [&](int buf) { return bar0 + 8 + 8 * buf; };
+    auto s_free = [&](int buf) { return bar0 + 64 + 8 * buf; };
     if (tid == 0) {
-        for (int i = 0; i < 5; ++i) mbar_init(bar0 + 8 * i, 1);
+        for (int i = 0; i < 7; ++i) mbar_init(bar0 + 8 * i, 1);
+        mbar_init(bar0 + 80, 1);
+        mbar_init(p_ready, kBwdComputeWarps);
+        mbar_init(s_free(0), kBwdComputeWarps);
+        mbar_init(s_free(1), kBwdComputeWarps);
         *abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    if (issuer) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tS = tmem, tdP = tmem + BKV, tdQ = tmem + 2 * BKV;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-
-    if (tid == 0) {
-        tma_prefetch_desc(&tmap_q128); tma_prefetch_desc(&tmap_kv64); tma_prefetch_desc(&tmap_do128);
-        mbar_expect_tx(q_bar, 2 * Q_BYTES);
-        for (int c = 0; c < NCH; ++c) {
-            tma_load_3d(smem_u32(sQ) + c * (BQ * 128), &tmap_q128, q_bar, h * HS + c * 64, q0, b);
-            tma_load_3d(smem_u32(sdO) + c * (BQ * 128), &tmap_do128, q_bar, h * HS + c * 64, q0, b);
-        }
-        mbar_expect_tx(k_bar, KV_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv64, k_bar, kcol + c * 64, 0, b);
-        mbar_expect_tx(v_bar, KV_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv64, v_bar, vcol + c * 64, 0, b);
-    }
-
-    const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
-    const uint32_t idesc_dq = make_instr_desc(1, 1, false, true, BQ, HS);
-    const float sl2 = p.scale * kLog2e;
-    const int row = q0 + tid;
-    const long long si = (static_cast<long long>(b) * p.Hq + h) * p.T + row;
-    const float lse2 = row < p.T ? p.lse[si] * kLog2e : INFINITY;
-    const float delta = row < p.T ? p.delta[si] : 0.f;
+    const uint32_t tdQ = tmem + 4 * BKV;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
 
-    for (int j = 0; j < n_kv && ok; ++j) {
-        const uint32_t par = j & 1;
-        if (tid == 0) {
-            if (j == 0) ok = mbar_wait(q_bar, 0, abort_flag);
-            ok = ok && mbar_wait(k_bar, par, abort_flag) && mbar_wait(v_bar, par, abort_flag);
-            tc_fence_after_sync();
-            if (ok) {
+    if (issuer) {
+        // ============================================================ producer / issuer warp
+        if ((tid & 31) == 0 && n_kv > 0) {
+            auto issue_kv = [&](int j) {
+                const int buf = j % NBUF;
+                mbar_expect_tx(kv_bar(buf), 2 * KV_BYTES);
+                for (int c = 0; c < NCH; ++c) {
+                    tma_load_3d(smem_u32(sK) + buf * KV_BYTES + c * (BKV * 128), &tmap_kv64, kv_bar(buf), kcol + c * 64, j * BKV, b);
+                    tma_load_3d(smem_u32(sV) + buf * KV_BYTES + c * (BKV * 128), &tmap_kv64, kv_bar(buf), vcol + c * 64, j * BKV, b);
+                }
+            };
+            const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
+            const uint32_t idesc_dq = make_instr_desc(1, 1, false, true, BQ, HS);
+            auto issue_sp = [&](int j) {
+                const int buf = j % NBUF;
+                const uint32_t tS = tmem + (j & 1) * BKV, tdP = tmem + 2 * BKV + (j & 1) * BKV;
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
                     mma_issue<false, false>(tS, DLO(smem_u32(sQ), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
-                                            DLO(smem_u32(sK), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
+                                            DLO(smem_u32(sK) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
                 }
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
                     mma_issue<false, false>(tdP, DLO(smem_u32(sdO), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
-                                            DLO(smem_u32(sV), 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
+                                            DLO(smem_u32(sV) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
                 }
-                mma_commit(sp_bar);
+                mma_commit(sp_bar(j));
+            };
+            tma_prefetch_desc(&tmap_q128); tma_prefetch_desc(&tmap_kv64); tma_prefetch_desc(&tmap_do128);
+            mbar_expect_tx(q_bar, 2 * Q_BYTES);
+            for (int c = 0; c < NCH; ++c) {
+                tma_load_3d(smem_u32(sQ) + c * (BQ * 128), &tmap_q128, q_bar, h * HS + c * 64, q0, b);
+                tma_load_3d(smem_u32(sdO) + c * (BQ * 128), &tmap_do128, q_bar, h * HS + c * 64, q0, b);
             }
-        }
-        if (!mbar_wait(sp_bar, par, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (tid == 0 && j + 1 < n_kv) {                       // V tile is free again
-            mbar_expect_tx(v_bar, KV_BYTES);
-            for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv64, v_bar, vcol + c * 64, (j + 1) * BKV, b);
-        }
-        const bool diag = (j + 1) * BKV > q0;
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < BKV / 32; ++c) {
-            uint32_t rs[32], rp[32];
-            tmem_ld_32x32b_x32(tS + lane_off + c * 32, rs);
-            tmem_ld_32x32b_x32(tdP + lane_off + c * 32, rp);
-            tmem_ld_wait();
-            float ds[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float pv = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-                if (diag && (j * BKV + c * 32 + i > row)) pv = 0.f;
-                ds[i] = pv * (__uint_as_float(rp[i]) - delta) * p.scale;
-            }
-            store_row_chunk_swz(sdS, tid, c * 32, ds);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
-        if (tid == 0) {
+            for (int j = 0; j < NBUF - 1 && j < n_kv; ++j) issue_kv(j);
+            ok = mbar_wait(q_bar, 0, abort_flag) && mbar_wait(kv_bar(0), 0, abort_flag);
             tc_fence_after_sync();
-#pragma unroll
-            for (int k = 0; k < BKV / 16; ++k) {
-                mma_issue<false, false>(tdQ, DLO(smem_u32(sdS), 16, k * 32), kDescHi,
-                                        DLO(smem_u32(sK), BKV * 128, k * (16 * 128)), kDescHi, idesc_dq, (j > 0 || k > 0));
-            }
-            mma_commit(dq_bar);
-        }
-        if (!mbar_wait(dq_bar, par, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (tid == 0 && j + 1 < n_kv) {                       // K tile is free again
-            mbar_expect_tx(k_bar, KV_BYTES);
-            for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv64, k_bar, kcol + c * 64, (j + 1) * BKV, b);
-        }
-    }
-    if (!ok && tid == 0) atomicOr(p.status, kErrOther);
-
-    if (ok) {
-        const int H = p.Hq + 2 * p.Hkv;
-        bf16* dq = p.dqkv + ((static_cast<long long>(b) * p.T + row) * H + h) * HS;
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < HS / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tdQ + lane_off + c * 32, r);
-            tmem_ld_wait();
-            if (row < p.T) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 o4;
-                    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o4);
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj)
-                        ob[jj] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * jj]), __uint_as_float(r[g * 8 + 2 * jj + 1]));
-                    *reinterpret_cast<uint4*>(dq + c * 32 + g * 8) = o4;
+            if (ok) issue_sp(0);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (j + 1 < n_kv) {
+                    ok = mbar_wait(kv_bar((j + 1) % NBUF), ((j + 1) / NBUF) & 1, abort_flag);
+                    if (ok && j >= 1) ok = mbar_wait(s_free((j + 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_sp(j + 1);
                 }
+                // dQ MMA of tile j-1 done: its K / V buffer, (j - 1) % NBUF, takes tile j + NBUF - 1
+                if (j >= 1 && !mbar_wait(dq_bar, (j - 1) & 1, abort_flag)) { ok = false; break; }
+                if (j + NBUF - 1 < n_kv) issue_kv(j + NBUF - 1);
+                if (!mbar_wait(p_ready, j & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const int buf = j % NBUF;
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k) {
+                    mma_issue<false, false>(tdQ, DLO(smem_u32(sdS), 16, k * 32), kDescHi,
+                                            DLO(smem_u32(sK) + buf * KV_BYTES, BKV * 128, k * (16 * 128)), kDescHi, idesc_dq, (j > 0 || k > 0));
+                }
+                mma_commit(dq_bar);
+            }
+            if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
+        }
+    } else {
+        // ============================================================ compute warps
+        const float sl2 = p.scale * kLog2e;
+        const int row = q0 + r;
+        const long long si = (static_cast<long long>(b) * p.Hq + h) * p.T + row;
+        const float lse2 = row < p.T ? p.lse[si] * kLog2e : INFINITY;
+        const float delta_s = row < p.T ? p.delta[si] * p.scale : 0.f;
+        const int c0 = wg * CW;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            if (!mbar_wait(sp_bar(j), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const bool diag = (j + 1) * BKV > q0;
+            const uint32_t tS = tmem + (j & 1) * BKV, tdP = tmem + 2 * BKV + (j & 1) * BKV;
+            uint32_t dsp[CW / 2];
+            {
+                uint32_t rs[CW], rp[CW];
+                tmem_ld_32x32b_x16(tS + lane_off + c0, rs);
+                tmem_ld_32x32b_x16(tdP + lane_off + c0, rp);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                warp_arrive(s_free(j & 1));
+                float pv[CW];
+#pragma unroll
+                for (int i = 0; i < CW; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
+                if (diag) {
+                    const int lim = row - j * BKV - c0;         // columns above lim are beyond the diagonal (kv > q)
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) if (i > lim) pv[i] = 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < CW; i += 2)
+                    dsp[i / 2] = pack_bf16x2(pv[i] * fmaf(__uint_as_float(rp[i]), p.scale, -delta_s),
+                                             pv[i + 1] * fmaf(__uint_as_float(rp[i + 1]), p.scale, -delta_s));
+            }
+            // dS of tile j-1 is read by its dQ MMA until dq_bar completes
+            if (j > 0 && !mbar_wait(dq_bar, (j - 1) & 1, abort_flag)) { ok = false; break; }
+            store_row_chunk16_swz_packed(sdS, r, c0, dsp);
+            fence_proxy_async_smem();
+            warp_arrive(p_ready);
+        }
+        if (ok && n_kv > 0) ok = mbar_wait(dq_bar, (n_kv - 1) & 1, abort_flag);
+        tc_fence_after_sync();
+        if (!ok && r == 0) atomicOr(p.status, kErrOther);
+        if (ok) {
+            const int H = p.Hq + 2 * p.Hkv;
+            bf16* dq = p.dqkv + ((static_cast<long long>(b) * p.T + (row < p.T ? row : 0)) * H + h) * HS;
+            __syncwarp();
+            constexpr int ECW = HS / kBwdWarpgroups;
+#pragma unroll
+            for (int c = 0; c < ECW; c += 16) {
+                const int col = wg * ECW + c;
+                uint32_t acc[16];
+                tmem_ld_32x32b_x16(tdQ + lane_off + col, acc);
+                tmem_ld_wait();
+                if (row < p.T) store16_bf16(dq + col, acc);
             }
         }
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+    if (issuer) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // Tag makes the static flag unique per kernel instantiation (several kernels share one signature).
@@ -716,20 +842,20 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.scale = 1.f / sqrtf(static_cast<float>(HS));
     p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = static_cast<bf16*>(dqkv); p.status = status;
     {
-        constexpr int smem = 2 * 128 * HS * 2 + 4 * 64 * HS * 2 + 2 * 128 * 64 * 2 + 2 * 64 * 4 + 128;
+        constexpr int smem = 2 * 128 * HS * 2 + 8 * 64 * HS * 2 + 2 * 128 * 64 * 2 + 4 * 64 * 4 + 128;
         rc = set_smem<1000 + HS>(attn_bwd_dkdv_kernel<HS>, smem);
         if (rc) return rc;
-        dim3 grid((T + 127) / 128, Hkv, B);
-        attn_bwd_dkdv_kernel<HS><<<grid, 128, smem, s>>>(t128, t64, tdo64, p);
+        dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
+        attn_bwd_dkdv_kernel<HS><<<grid, kBwdThreads, smem, s>>>(t128, t64, tdo64, p);
         rc = LLMQ_LAUNCH_CHECK();
         if (rc) return rc;
     }
     {
-        constexpr int smem = 2 * 128 * HS * 2 + 2 * 64 * HS * 2 + 128 * 64 * 2 + 128;
+        constexpr int smem = 2 * 128 * HS * 2 + 8 * 64 * HS * 2 + 128 * 64 * 2 + 128;
         rc = set_smem<2000 + HS>(attn_bwd_dq_kernel<HS>, smem);
         if (rc) return rc;
-        dim3 grid((T + 127) / 128, Hq, B);
-        attn_bwd_dq_kernel<HS><<<grid, 128, smem, s>>>(t128, t64, tdo128, p);
+        dim3 grid(((T + 127) / 128) * Hq * B, 1, 1);
+        attn_bwd_dq_kernel<HS><<<grid, kBwdThreads, smem, s>>>(t128, t64, tdo128, p);
         rc = LLMQ_LAUNCH_CHECK();
     }
     return rc;
