@@ -30,7 +30,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kBwdWarpgroups = 4;
 constexpr int kBwdComputeThreads = 128 * kBwdWarpgroups;
 constexpr int kBwdComputeWarps = kBwdComputeThreads / 32;
-constexpr int kBwdThreads = kBwdComputeThreads + 32;          // + one warp that only loads tiles and issues MMAs
+constexpr int kBwdThreads = kBwdComputeThreads + 64;          // + one warp that issues the MMAs + one that issues the TMA loads
 // barrier 1: the compute threads among themselves (barrier 0 is __syncthreads of the whole CTA)
 // One arrival per warp (512 single arrivals on one shared-memory word would serialise): the lanes' earlier
 // writes and fences are ordered before lane 0's releasing arrive by the warp barrier.
@@ -102,6 +102,8 @@ struct AttnParams {
     float* lse;                  // (B,Hq,T), natural log
     const float* delta;          // (B,Hq,T)
     bf16* dqkv;                  // backward: packed gradient
+    const bf16* qkv;             // backward: packed inputs and the output gradient as plain pointers
+    const bf16* d_out;
     unsigned int* status;
 };
 
@@ -387,11 +389,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     float* sLse = reinterpret_cast<float*>(sdST + PT_BYTES);      // [2][64] pre-multiplied by log2(e)
     float* sDelta = sLse + 2 * BQ;                                // [2][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sDelta + 2 * BQ);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const bool issuer = warp == kBwdComputeWarps;             // the extra warp: TMA producer + MMA issuer (lane 0)
+    const bool issuer = warp == kBwdComputeWarps;             // MMA issuer (lane 0); its only other work is waiting
+    const bool producer = warp == kBwdComputeWarps + 1;       // TMA producer (lane 0)
     const int wg = tid >> 7, r = tid & 127;                   // compute threads: column slice, row of the tile (TMEM lane)
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
     // 1-D grid, key block slowest: the blocks with the longest walks (small kb) start first on every SM
@@ -406,7 +409,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     const int kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
     // barriers: 0 kv | 1-4 q/dO ring | 5 sp (scores ready) | 6 acc (dV/dK MMAs of a tile done) | 7 p_ready (P^T/dS^T stored)
-    //           8-9 s_free (score buffer read by all compute threads)
+    //           8-9 s_free (score buffer read by all compute threads) | 10 second sp | 11-14 q/dO buffer free
     const uint32_t bar0 = smem_u32(bars);
     // Two score barriers, used alternately: the commit of tile it+2 needs every compute warp to have read tile it, so a
     // waiter can never miss a phase (with one barrier, tiles 0 and 1 can both complete before a slow warp looks).
@@ -414,9 +417,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     auto sp_bar = [&](int it) { return (it & 1) ? bar0 + 80 : bar0 + 40; };
     auto qdo_bar = [&](int buf) { return bar0 + 8 + 8 * buf; };
     auto s_free = [&](int buf) { return bar0 + 64 + 8 * buf; };
+    auto qdo_free = [&](int buf) { return bar0 + 88 + 8 * buf; };
     if (tid == 0) {
         for (int i = 0; i < 7; ++i) mbar_init(bar0 + 8 * i, 1);
-        mbar_init(bar0 + 80, 1);
+        for (int i = 10; i < 15; ++i) mbar_init(bar0 + 8 * i, 1);
         mbar_init(p_ready, kBwdComputeWarps);
         mbar_init(s_free(0), kBwdComputeWarps);
         mbar_init(s_free(1), kBwdComputeWarps);
@@ -433,22 +437,39 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     auto tile_of = [&](int it, int& hq, int& qb) { hq = kvh * G + it / per_head; qb = qb_first + it % per_head; };
     bool ok = true;
 
-    if (issuer) {
-        // ============================================================ producer / issuer warp
+    if (producer) {
+        // ============================================================ TMA producer warp
         if ((tid & 31) == 0 && n_it > 0) {
-            auto issue_qdo = [&](int it) {
-                int hq, qb; tile_of(it, hq, qb);
+            tma_prefetch_desc(&tmap_kv128); tma_prefetch_desc(&tmap_q64); tma_prefetch_desc(&tmap_do64);
+            mbar_expect_tx(kv_bar, 2 * KV_BYTES);
+            for (int c = 0; c < NCH; ++c) {
+                tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv128, kv_bar, kcol + c * 64, kv0, b);
+                tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv128, kv_bar, vcol + c * 64, kv0, b);
+            }
+            int hq = kvh * G, qb = qb_first;
+            for (int it = 0; it < n_it; ++it) {
                 const int buf = it % NBUF;
+                // the buffer's previous tile, it - NBUF, has been consumed by its dV / dK MMAs
+                if (it >= NBUF && !mbar_wait(qdo_free(buf), ((it / NBUF) - 1) & 1, abort_flag)) { atomicOr(p.status, kErrOther); break; }
                 mbar_expect_tx(qdo_bar(buf), 2 * Q_BYTES);
                 for (int c = 0; c < NCH; ++c) {
                     tma_load_3d(smem_u32(sQ) + buf * Q_BYTES + c * (BQ * 128), &tmap_q64, qdo_bar(buf), hq * HS + c * 64, qb * BQ, b);
                     tma_load_3d(smem_u32(sdO) + buf * Q_BYTES + c * (BQ * 128), &tmap_do64, qdo_bar(buf), hq * HS + c * 64, qb * BQ, b);
                 }
-            };
+                if (++qb == nqb) { qb = qb_first; ++hq; }
+            }
+        }
+    } else if (issuer) {
+        // ============================================================ MMA issuer warp
+        if ((tid & 31) == 0 && n_it > 0) {
             const uint32_t idesc_st = make_instr_desc(1, 1, false, false, BKV, BQ);     // S^T = K Q^T, dP^T = V dO^T
             const uint32_t idesc_acc = make_instr_desc(1, 1, false, true, BKV, HS);      // dV += P^T dO, dK += dS^T Q
-            auto issue_sp = [&](int it) {
+            // scores of tile it: needs its Q / dO and, from tile 2 on, the score buffer read by every compute warp
+            auto issue_sp = [&](int it) -> bool {
                 const int buf = it % NBUF;
+                if (!mbar_wait(qdo_bar(buf), (it / NBUF) & 1, abort_flag)) return false;
+                if (it >= 2 && !mbar_wait(s_free(it & 1), ((it - 2) >> 1) & 1, abort_flag)) return false;
+                tc_fence_after_sync();
                 const uint32_t tS = tmem + (it & 1) * BQ, tdP = tmem + 2 * BQ + (it & 1) * BQ;
 #pragma unroll
                 for (int k = 0; k < HS / 16; ++k) {
@@ -461,29 +482,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
                                             DLO(smem_u32(sdO) + buf * Q_BYTES, 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi, idesc_st, k > 0);
                 }
                 mma_commit(sp_bar(it));
+                return true;
             };
-            tma_prefetch_desc(&tmap_kv128); tma_prefetch_desc(&tmap_q64); tma_prefetch_desc(&tmap_do64);
-            mbar_expect_tx(kv_bar, 2 * KV_BYTES);
-            for (int c = 0; c < NCH; ++c) {
-                tma_load_3d(smem_u32(sK) + c * (BKV * 128), &tmap_kv128, kv_bar, kcol + c * 64, kv0, b);
-                tma_load_3d(smem_u32(sV) + c * (BKV * 128), &tmap_kv128, kv_bar, vcol + c * 64, kv0, b);
-            }
-            for (int i = 0; i < NBUF - 1 && i < n_it; ++i) issue_qdo(i);
-            ok = mbar_wait(kv_bar, 0, abort_flag) && mbar_wait(qdo_bar(0), 0, abort_flag);
-            tc_fence_after_sync();
-            if (ok) issue_sp(0);
+            ok = mbar_wait(kv_bar, 0, abort_flag) && issue_sp(0);
             for (int it = 0; it < n_it && ok; ++it) {
-                if (it + 1 < n_it) {
-                    // scores of tile it+1 overwrite the buffer of tile it-1: every compute thread must have read it
-                    ok = mbar_wait(qdo_bar((it + 1) % NBUF), ((it + 1) / NBUF) & 1, abort_flag);
-                    if (ok && it >= 1) ok = mbar_wait(s_free((it + 1) & 1), ((it - 1) >> 1) & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_sp(it + 1);
-                }
-                // dV / dK of tile it-1 done: its Q / dO buffer, (it - 1) % NBUF, takes tile it + NBUF - 1
-                if (it >= 1 && !mbar_wait(acc_bar, (it - 1) & 1, abort_flag)) { ok = false; break; }
-                if (it + NBUF - 1 < n_it) issue_qdo(it + NBUF - 1);
+                if (it + 1 < n_it && !issue_sp(it + 1)) { ok = false; break; }
                 if (!mbar_wait(p_ready, it & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const int buf = it % NBUF;
@@ -498,6 +501,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
                                             DLO(smem_u32(sQ) + buf * Q_BYTES, BQ * 128, k * (16 * 128)), kDescHi, idesc_acc, (it > 0 || k > 0));
                 }
                 mma_commit(acc_bar);
+                mma_commit(qdo_free(buf));
             }
             if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
         }
@@ -604,50 +608,53 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
 }
 
 // ------------------------------------------------------------------------------------------------
-// dQ.  Same software pipeline as dK / dV: S(j+1) / dP(j+1) run on the tensor core while the threads compute dS(j);
-// K / V tiles sit in a ring of four buffers loaded three tiles ahead; dQ accumulates in TMEM over the key walk.
+// dQ.  One CTA owns 128 query rows of one kv head and walks over the query heads of that group, and for every head
+// over the key tiles up to the diagonal, so the start-up and drain costs of a CTA are paid once per group instead
+// of once per head.  Q and dO of the current head live in tensor memory as the A operands of the score MMAs (they
+// are constant during a key walk), K / V tiles stream through a ring of four shared-memory buffers three tiles
+// ahead of the MMAs, S / dP are double buffered in TMEM, dQ accumulates in TMEM and is drained once per head.
 template <int HS>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box 128 rows
-                   const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64 rows
-                   const __grid_constant__ CUtensorMap tmap_do128,   // dO, box 128 rows
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64 rows
                    const AttnParams p) {
     constexpr int BQ = 128, BKV = 64, NCH = HS / 64, NBUF = 4;
-    constexpr int Q_BYTES = BQ * HS * 2, KV_BYTES = BKV * HS * 2, DS_BYTES = BQ * BKV * 2;
-    constexpr uint32_t TMEM_COLS = 512;                       // S0 S1 | dP0 dP1 | dQ
+    constexpr int KV_BYTES = BKV * HS * 2, DS_BYTES = BQ * BKV * 2;
+    constexpr uint32_t TMEM_COLS = 512;                       // Q | dO (bf16 pairs, A operands) | S0 S1 | dP0 dP1 | dQ
     constexpr int CW = BKV / kBwdWarpgroups;
     static_assert(CW == 16, "the column split below is written for 16 columns per thread");
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;
-    uint8_t* sdO = sQ + Q_BYTES;
-    uint8_t* sK = sdO + Q_BYTES;              // NBUF buffers
+    uint8_t* sK = smem;                       // NBUF buffers
     uint8_t* sV = sK + NBUF * KV_BYTES;       // NBUF buffers
     uint8_t* sdS = sV + NBUF * KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + DS_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const bool issuer = warp == kBwdComputeWarps;
+    const bool issuer = warp == kBwdComputeWarps, producer = warp == kBwdComputeWarps + 1;
     const int wg = tid >> 7, r = tid & 127;
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
     const int nqb = (p.T + BQ - 1) / BQ;
-    const int qb = nqb - 1 - blockIdx.x / (p.Hq * p.B);         // 1-D grid, longest key walks first
-    const int h = (blockIdx.x % (p.Hq * p.B)) % p.Hq, b = (blockIdx.x % (p.Hq * p.B)) / p.Hq;
-    const int kvh = h / (p.Hq / p.Hkv);
+    const int qb = nqb - 1 - blockIdx.x / (p.Hkv * p.B);        // 1-D grid, longest key walks first
+    const int kvh = (blockIdx.x % (p.Hkv * p.B)) % p.Hkv, b = (blockIdx.x % (p.Hkv * p.B)) / p.Hkv;
+    const int G = p.Hq / p.Hkv;
     const int q0 = qb * BQ;
     const int n_kv = min((p.T + BKV - 1) / BKV, (q0 + BQ) / BKV);
+    const int total = n_kv * G;                                 // tiles of the whole walk, t = g * n_kv + j
     const int kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
-    // barriers: 0 q/dO | 1-4 k/v ring | 5 sp | 6 dq (dQ MMA of a tile done) | 7 p_ready (dS stored) | 8-9 s_free
+    // barriers: 0 head_ready | 1-4 k/v ring | 5, 10 sp (alternating) | 6 dq (dQ MMA of a tile done) | 7 p_ready | 8-9 s_free
+    //           11-14 k/v buffer free
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_bar = bar0, dq_bar = bar0 + 48, p_ready = bar0 + 56;
-    auto sp_bar = [&](int j) { return (j & 1) ? bar0 + 80 : bar0 + 40; };        // alternating, see the dK / dV kernel
+    const uint32_t head_ready = bar0, dq_bar = bar0 + 48, p_ready = bar0 + 56;
+    auto sp_bar = [&](int t) { return (t & 1) ? bar0 + 80 : bar0 + 40; };        // alternating, see the dK / dV kernel
     auto kv_bar = [&](int buf) { return bar0 + 8 + 8 * buf; };
     auto s_free = [&](int buf) { return bar0 + 64 + 8 * buf; };
+    auto kv_free = [&](int buf) { return bar0 + 88 + 8 * buf; };
     if (tid == 0) {
-        for (int i = 0; i < 7; ++i) mbar_init(bar0 + 8 * i, 1);
-        mbar_init(bar0 + 80, 1);
+        for (int i = 1; i < 7; ++i) mbar_init(bar0 + 8 * i, 1);
+        for (int i = 10; i < 15; ++i) mbar_init(bar0 + 8 * i, 1);
+        mbar_init(head_ready, kBwdComputeWarps);
         mbar_init(p_ready, kBwdComputeWarps);
         mbar_init(s_free(0), kBwdComputeWarps);
         mbar_init(s_free(1), kBwdComputeWarps);
@@ -659,68 +666,74 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tdQ = tmem + 4 * BKV;
+    const uint32_t tQ = tmem, tdO = tmem + HS / 2, tS0 = tmem + HS, tdP0 = tmem + HS + 2 * BKV, tdQ = tmem + HS + 4 * BKV;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
 
-    if (issuer) {
-        // ============================================================ producer / issuer warp
-        if ((tid & 31) == 0 && n_kv > 0) {
-            auto issue_kv = [&](int j) {
-                const int buf = j % NBUF;
+    if (producer) {
+        // ============================================================ TMA producer warp
+        if ((tid & 31) == 0 && total > 0) {
+            tma_prefetch_desc(&tmap_kv64);
+            int j = 0;
+            for (int t = 0; t < total; ++t) {
+                const int buf = t % NBUF;
+                // the buffer's previous tile, t - NBUF, has been consumed by its dQ MMA
+                if (t >= NBUF && !mbar_wait(kv_free(buf), ((t / NBUF) - 1) & 1, abort_flag)) { atomicOr(p.status, kErrOther); break; }
                 mbar_expect_tx(kv_bar(buf), 2 * KV_BYTES);
                 for (int c = 0; c < NCH; ++c) {
                     tma_load_3d(smem_u32(sK) + buf * KV_BYTES + c * (BKV * 128), &tmap_kv64, kv_bar(buf), kcol + c * 64, j * BKV, b);
                     tma_load_3d(smem_u32(sV) + buf * KV_BYTES + c * (BKV * 128), &tmap_kv64, kv_bar(buf), vcol + c * 64, j * BKV, b);
                 }
-            };
+                if (++j == n_kv) j = 0;
+            }
+        }
+    } else if (issuer) {
+        // ============================================================ MMA issuer warp
+        if ((tid & 31) == 0 && total > 0) {
             const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
             const uint32_t idesc_dq = make_instr_desc(1, 1, false, true, BQ, HS);
-            auto issue_sp = [&](int j) {
-                const int buf = j % NBUF;
-                const uint32_t tS = tmem + (j & 1) * BKV, tdP = tmem + 2 * BKV + (j & 1) * BKV;
-#pragma unroll
-                for (int k = 0; k < HS / 16; ++k) {
-                    mma_issue<false, false>(tS, DLO(smem_u32(sQ), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
-                                            DLO(smem_u32(sK) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
-                }
-#pragma unroll
-                for (int k = 0; k < HS / 16; ++k) {
-                    mma_issue<false, false>(tdP, DLO(smem_u32(sdO), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
-                                            DLO(smem_u32(sV) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
-                }
-                mma_commit(sp_bar(j));
-            };
-            tma_prefetch_desc(&tmap_q128); tma_prefetch_desc(&tmap_kv64); tma_prefetch_desc(&tmap_do128);
-            mbar_expect_tx(q_bar, 2 * Q_BYTES);
-            for (int c = 0; c < NCH; ++c) {
-                tma_load_3d(smem_u32(sQ) + c * (BQ * 128), &tmap_q128, q_bar, h * HS + c * 64, q0, b);
-                tma_load_3d(smem_u32(sdO) + c * (BQ * 128), &tmap_do128, q_bar, h * HS + c * 64, q0, b);
-            }
-            for (int j = 0; j < NBUF - 1 && j < n_kv; ++j) issue_kv(j);
-            ok = mbar_wait(q_bar, 0, abort_flag) && mbar_wait(kv_bar(0), 0, abort_flag);
-            tc_fence_after_sync();
-            if (ok) issue_sp(0);
-            for (int j = 0; j < n_kv && ok; ++j) {
-                if (j + 1 < n_kv) {
-                    ok = mbar_wait(kv_bar((j + 1) % NBUF), ((j + 1) / NBUF) & 1, abort_flag);
-                    if (ok && j >= 1) ok = mbar_wait(s_free((j + 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_sp(j + 1);
-                }
-                // dQ MMA of tile j-1 done: its K / V buffer, (j - 1) % NBUF, takes tile j + NBUF - 1
-                if (j >= 1 && !mbar_wait(dq_bar, (j - 1) & 1, abort_flag)) { ok = false; break; }
-                if (j + NBUF - 1 < n_kv) issue_kv(j + NBUF - 1);
-                if (!mbar_wait(p_ready, j & 1, abort_flag)) { ok = false; break; }
+            // scores of tile t; needs its K / V tile and, from t = 2 on, the score buffer read by every compute warp
+            auto issue_sp = [&](int t) -> bool {
+                const int buf = t % NBUF;
+                if (!mbar_wait(kv_bar(buf), (t / NBUF) & 1, abort_flag)) return false;
+                if (t >= 2 && !mbar_wait(s_free(t & 1), ((t - 2) >> 1) & 1, abort_flag)) return false;
                 tc_fence_after_sync();
-                const int buf = j % NBUF;
+                const uint32_t tS = tS0 + (t & 1) * BKV, tdP = tdP0 + (t & 1) * BKV;
+#pragma unroll
+                for (int k = 0; k < HS / 16; ++k) {
+                    mma_issue_f16_tmem_a(tS, tQ + k * 8, DLO(smem_u32(sK) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi,
+                                         idesc_s, k > 0);
+                }
+#pragma unroll
+                for (int k = 0; k < HS / 16; ++k) {
+                    mma_issue_f16_tmem_a(tdP, tdO + k * 8, DLO(smem_u32(sV) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi,
+                                         idesc_s, k > 0);
+                }
+                mma_commit(sp_bar(t));
+                return true;
+            };
+            ok = mbar_wait(head_ready, 0, abort_flag);          // Q / dO of the first head are in tensor memory
+            if (ok) ok = issue_sp(0);
+            int g = 0, j = 0;
+            for (int t = 0; t < total && ok; ++t) {
+                const bool last_of_head = j == n_kv - 1;
+                // within a head the next scores are issued one tile ahead; across heads they have to wait for the new Q / dO
+                if (!last_of_head && !issue_sp(t + 1)) { ok = false; break; }
+                if (!mbar_wait(p_ready, t & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const int buf = t % NBUF;
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
                     mma_issue<false, false>(tdQ, DLO(smem_u32(sdS), 16, k * 32), kDescHi,
                                             DLO(smem_u32(sK) + buf * KV_BYTES, BKV * 128, k * (16 * 128)), kDescHi, idesc_dq, (j > 0 || k > 0));
                 }
                 mma_commit(dq_bar);
+                mma_commit(kv_free(buf));
+                if (last_of_head && t + 1 < total) {
+                    if (!mbar_wait(head_ready, (g + 1) & 1, abort_flag)) { ok = false; break; }
+                    if (!issue_sp(t + 1)) { ok = false; break; }
+                }
+                if (++j == n_kv) { j = 0; ++g; }
             }
             if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
         }
@@ -728,59 +741,95 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q128,    // qkv, box
         // ============================================================ compute warps
         const float sl2 = p.scale * kLog2e;
         const int row = q0 + r;
-        const long long si = (static_cast<long long>(b) * p.Hq + h) * p.T + row;
-        const float lse2 = row < p.T ? p.lse[si] * kLog2e : INFINITY;
-        const float delta_s = row < p.T ? p.delta[si] * p.scale : 0.f;
+        const bool row_ok = row < p.T;
         const int c0 = wg * CW;
-        for (int j = 0; j < n_kv && ok; ++j) {
-            if (!mbar_wait(sp_bar(j), (j >> 1) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after_sync();
-            const bool diag = (j + 1) * BKV > q0;
-            const uint32_t tS = tmem + (j & 1) * BKV, tdP = tmem + 2 * BKV + (j & 1) * BKV;
-            uint32_t dsp[CW / 2];
-            {
-                uint32_t rs[CW], rp[CW];
-                tmem_ld_32x32b_x16(tS + lane_off + c0, rs);
-                tmem_ld_32x32b_x16(tdP + lane_off + c0, rp);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                warp_arrive(s_free(j & 1));
-                float pv[CW];
+        const int H = p.Hq + 2 * p.Hkv;
+        const bool stores_qdo = wg < HS / 32;                   // uniform per warp: the TMEM stores are warp-collective
+        constexpr int ECW = HS / kBwdWarpgroups;                // dQ columns per thread
+        // this thread's 32-element slices of the Q and dO rows of head hq (16 packed words each)
+        auto load_qdo = [&](int hq, uint32_t (&wq)[16], uint32_t (&wo)[16]) {
+            if (stores_qdo && row_ok) {
+                const uint4* gq = reinterpret_cast<const uint4*>(p.qkv + ((static_cast<long long>(b) * p.T + row) * H + hq) * HS + wg * 32);
+                const uint4* go = reinterpret_cast<const uint4*>(p.d_out + ((static_cast<long long>(b) * p.T + row) * p.Hq + hq) * HS + wg * 32);
 #pragma unroll
-                for (int i = 0; i < CW; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
-                if (diag) {
-                    const int lim = row - j * BKV - c0;         // columns above lim are beyond the diagonal (kv > q)
-#pragma unroll
-                    for (int i = 0; i < CW; ++i) if (i > lim) pv[i] = 0.f;
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint4 x = __ldg(gq + q4), y = __ldg(go + q4);
+                    wq[4 * q4] = x.x; wq[4 * q4 + 1] = x.y; wq[4 * q4 + 2] = x.z; wq[4 * q4 + 3] = x.w;
+                    wo[4 * q4] = y.x; wo[4 * q4 + 1] = y.y; wo[4 * q4 + 2] = y.z; wo[4 * q4 + 3] = y.w;
                 }
+            } else {
 #pragma unroll
-                for (int i = 0; i < CW; i += 2)
-                    dsp[i / 2] = pack_bf16x2(pv[i] * fmaf(__uint_as_float(rp[i]), p.scale, -delta_s),
-                                             pv[i + 1] * fmaf(__uint_as_float(rp[i + 1]), p.scale, -delta_s));
+                for (int q4 = 0; q4 < 16; ++q4) { wq[q4] = 0u; wo[q4] = 0u; }
             }
-            // dS of tile j-1 is read by its dQ MMA until dq_bar completes
-            if (j > 0 && !mbar_wait(dq_bar, (j - 1) & 1, abort_flag)) { ok = false; break; }
-            store_row_chunk16_swz_packed(sdS, r, c0, dsp);
-            fence_proxy_async_smem();
-            warp_arrive(p_ready);
-        }
-        if (ok && n_kv > 0) ok = mbar_wait(dq_bar, (n_kv - 1) & 1, abort_flag);
-        tc_fence_after_sync();
-        if (!ok && r == 0) atomicOr(p.status, kErrOther);
-        if (ok) {
-            const int H = p.Hq + 2 * p.Hkv;
-            bf16* dq = p.dqkv + ((static_cast<long long>(b) * p.T + (row < p.T ? row : 0)) * H + h) * HS;
+        };
+        auto store_qdo = [&](const uint32_t (&wq)[16], const uint32_t (&wo)[16]) {
+            if (stores_qdo) {
+                tmem_st_32x32b_x16(tQ + lane_off + wg * 16, wq);
+                tmem_st_32x32b_x16(tdO + lane_off + wg * 16, wo);
+                tmem_st_wait();
+            }
+            tc_fence_before_sync();
+            warp_arrive(head_ready);
+        };
+        uint32_t wq[16], wo[16];
+        load_qdo(kvh * G, wq, wo);
+        store_qdo(wq, wo);
+        for (int g = 0; g < G && ok; ++g) {
+            const int h = kvh * G + g;
+            if (g + 1 < G) load_qdo(h + 1, wq, wo);             // prefetch: consumed when this head's walk is over
+            const long long si = (static_cast<long long>(b) * p.Hq + h) * p.T + row;
+            const float lse2 = row_ok ? p.lse[si] * kLog2e : INFINITY;
+            const float delta_s = row_ok ? p.delta[si] * p.scale : 0.f;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int t = g * n_kv + j;
+                if (!mbar_wait(sp_bar(t), (t >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const bool diag = (j + 1) * BKV > q0;
+                const uint32_t tS = tS0 + (t & 1) * BKV, tdP = tdP0 + (t & 1) * BKV;
+                uint32_t dsp[CW / 2];
+                {
+                    uint32_t rs[CW], rp[CW];
+                    tmem_ld_32x32b_x16(tS + lane_off + c0, rs);
+                    tmem_ld_32x32b_x16(tdP + lane_off + c0, rp);
+                    tmem_ld_wait();
+                    tc_fence_before_sync();
+                    warp_arrive(s_free(t & 1));
+                    float pv[CW];
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
+                    if (diag) {
+                        const int lim = row - j * BKV - c0;     // columns above lim are beyond the diagonal (kv > q)
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) if (i > lim) pv[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < CW; i += 2)
+                        dsp[i / 2] = pack_bf16x2(pv[i] * fmaf(__uint_as_float(rp[i]), p.scale, -delta_s),
+                                                 pv[i + 1] * fmaf(__uint_as_float(rp[i + 1]), p.scale, -delta_s));
+                }
+                // dS of tile t-1 is read by its dQ MMA until dq_bar completes
+                if (t > 0 && !mbar_wait(dq_bar, (t - 1) & 1, abort_flag)) { ok = false; break; }
+                store_row_chunk16_swz_packed(sdS, r, c0, dsp);
+                fence_proxy_async_smem();
+                warp_arrive(p_ready);
+            }
+            if (!ok) break;
+            // ---- the head's walk is over: drain dQ, hand the next head's Q / dO to the tensor core, then store
+            if (!mbar_wait(dq_bar, (g * n_kv + n_kv - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            uint32_t acc[ECW];
             __syncwarp();
-            constexpr int ECW = HS / kBwdWarpgroups;
 #pragma unroll
-            for (int c = 0; c < ECW; c += 16) {
-                const int col = wg * ECW + c;
-                uint32_t acc[16];
-                tmem_ld_32x32b_x16(tdQ + lane_off + col, acc);
-                tmem_ld_wait();
-                if (row < p.T) store16_bf16(dq + col, acc);
+            for (int c = 0; c < ECW; c += 16) tmem_ld_32x32b_x16(tdQ + lane_off + wg * ECW + c, *reinterpret_cast<uint32_t(*)[16]>(acc + c));
+            tmem_ld_wait();
+            if (g + 1 < G) store_qdo(wq, wo);
+            if (row_ok) {
+                bf16* dq = p.dqkv + ((static_cast<long long>(b) * p.T + row) * H + h) * HS + wg * ECW;
+#pragma unroll
+                for (int c = 0; c < ECW; c += 16) store16_bf16(dq + c, *reinterpret_cast<const uint32_t(*)[16]>(acc + c));
             }
         }
+        if (!ok && r == 0) atomicOr(p.status, kErrOther);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -841,8 +890,9 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
     AttnParams p{};
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.scale = 1.f / sqrtf(static_cast<float>(HS));
     p.lse = const_cast<float*>(lse); p.delta = delta; p.dqkv = static_cast<bf16*>(dqkv); p.status = status;
+    p.qkv = static_cast<const bf16*>(qkv); p.d_out = static_cast<const bf16*>(d_out);
     {
-        constexpr int smem = 2 * 128 * HS * 2 + 8 * 64 * HS * 2 + 2 * 128 * 64 * 2 + 4 * 64 * 4 + 128;
+        constexpr int smem = 2 * 128 * HS * 2 + 8 * 64 * HS * 2 + 2 * 128 * 64 * 2 + 4 * 64 * 4 + 256;
         rc = set_smem<1000 + HS>(attn_bwd_dkdv_kernel<HS>, smem);
         if (rc) return rc;
         dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
@@ -851,11 +901,11 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
         if (rc) return rc;
     }
     {
-        constexpr int smem = 2 * 128 * HS * 2 + 8 * 64 * HS * 2 + 128 * 64 * 2 + 128;
+        constexpr int smem = 8 * 64 * HS * 2 + 128 * 64 * 2 + 256;
         rc = set_smem<2000 + HS>(attn_bwd_dq_kernel<HS>, smem);
         if (rc) return rc;
-        dim3 grid(((T + 127) / 128) * Hq * B, 1, 1);
-        attn_bwd_dq_kernel<HS><<<grid, kBwdThreads, smem, s>>>(t128, t64, tdo128, p);
+        dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
+        attn_bwd_dq_kernel<HS><<<grid, kBwdThreads, smem, s>>>(t64, p);
         rc = LLMQ_LAUNCH_CHECK();
     }
     return rc;
