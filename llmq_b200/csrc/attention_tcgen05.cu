@@ -30,7 +30,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kBwdWarpgroups = 4;
 constexpr int kBwdComputeThreads = 128 * kBwdWarpgroups;
 constexpr int kBwdComputeWarps = kBwdComputeThreads / 32;
-constexpr int kBwdThreads = kBwdComputeThreads + 64;          // + one warp that issues the MMAs + one that issues the TMA loads
+// + three single-lane helper warps: score-MMA issuer, TMA producer, accumulation-MMA issuer.  MMA issue is synchronous
+// with execution (the queue is shallow), so two issuing threads keep the tensor pipe fed while the other one waits.
+constexpr int kBwdThreads = kBwdComputeThreads + 96;
 // barrier 1: the compute threads among themselves (barrier 0 is __syncthreads of the whole CTA)
 // One arrival per warp (512 single arrivals on one shared-memory word would serialise): the lanes' earlier
 // writes and fences are ordered before lane 0's releasing arrive by the warp barrier.
@@ -395,6 +397,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
     const int tid = threadIdx.x, warp = tid >> 5;
     const bool issuer = warp == kBwdComputeWarps;             // MMA issuer (lane 0); its only other work is waiting
     const bool producer = warp == kBwdComputeWarps + 1;       // TMA producer (lane 0)
+    const bool issuer2 = warp == kBwdComputeWarps + 2;        // issuer of the dV / dK MMAs (lane 0)
     const int wg = tid >> 7, r = tid & 127;                   // compute threads: column slice, row of the tile (TMEM lane)
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
     // 1-D grid, key block slowest: the blocks with the longest walks (small kb) start first on every SM
@@ -463,7 +466,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
         // ============================================================ MMA issuer warp
         if ((tid & 31) == 0 && n_it > 0) {
             const uint32_t idesc_st = make_instr_desc(1, 1, false, false, BKV, BQ);     // S^T = K Q^T, dP^T = V dO^T
-            const uint32_t idesc_acc = make_instr_desc(1, 1, false, true, BKV, HS);      // dV += P^T dO, dK += dS^T Q
             // scores of tile it: needs its Q / dO and, from tile 2 on, the score buffer read by every compute warp
             auto issue_sp = [&](int it) -> bool {
                 const int buf = it % NBUF;
@@ -484,9 +486,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_kv128,   // qkv, b
                 mma_commit(sp_bar(it));
                 return true;
             };
-            ok = mbar_wait(kv_bar, 0, abort_flag) && issue_sp(0);
+            ok = mbar_wait(kv_bar, 0, abort_flag);
+            for (int it = 0; it < n_it && ok; ++it) ok = issue_sp(it);
+            if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
+        }
+    } else if (issuer2) {
+        // ============================================================ dV / dK MMA issuer warp
+        if ((tid & 31) == 0 && n_it > 0) {
+            const uint32_t idesc_acc = make_instr_desc(1, 1, false, true, BKV, HS);      // dV += P^T dO, dK += dS^T Q
             for (int it = 0; it < n_it && ok; ++it) {
-                if (it + 1 < n_it && !issue_sp(it + 1)) { ok = false; break; }
                 if (!mbar_wait(p_ready, it & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const int buf = it % NBUF;
@@ -631,7 +639,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const bool issuer = warp == kBwdComputeWarps, producer = warp == kBwdComputeWarps + 1;
+    const bool issuer = warp == kBwdComputeWarps, producer = warp == kBwdComputeWarps + 1, issuer2 = warp == kBwdComputeWarps + 2;
     const int wg = tid >> 7, r = tid & 127;
     if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
     const int nqb = (p.T + BQ - 1) / BQ;
@@ -691,7 +699,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box
         // ============================================================ MMA issuer warp
         if ((tid & 31) == 0 && total > 0) {
             const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
-            const uint32_t idesc_dq = make_instr_desc(1, 1, false, true, BQ, HS);
             // scores of tile t; needs its K / V tile and, from t = 2 on, the score buffer read by every compute warp
             auto issue_sp = [&](int t) -> bool {
                 const int buf = t % NBUF;
@@ -712,13 +719,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box
                 mma_commit(sp_bar(t));
                 return true;
             };
-            ok = mbar_wait(head_ready, 0, abort_flag);          // Q / dO of the first head are in tensor memory
-            if (ok) ok = issue_sp(0);
             int g = 0, j = 0;
             for (int t = 0; t < total && ok; ++t) {
-                const bool last_of_head = j == n_kv - 1;
-                // within a head the next scores are issued one tile ahead; across heads they have to wait for the new Q / dO
-                if (!last_of_head && !issue_sp(t + 1)) { ok = false; break; }
+                // the first tile of a head needs that head's Q / dO in tensor memory
+                if (j == 0 && !mbar_wait(head_ready, g & 1, abort_flag)) { ok = false; break; }
+                ok = issue_sp(t);
+                if (++j == n_kv) { j = 0; ++g; }
+            }
+            if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
+        }
+    } else if (issuer2) {
+        // ============================================================ dQ MMA issuer warp
+        if ((tid & 31) == 0 && total > 0) {
+            const uint32_t idesc_dq = make_instr_desc(1, 1, false, true, BQ, HS);
+            int j = 0;
+            for (int t = 0; t < total && ok; ++t) {
                 if (!mbar_wait(p_ready, t & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const int buf = t % NBUF;
@@ -729,11 +744,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box
                 }
                 mma_commit(dq_bar);
                 mma_commit(kv_free(buf));
-                if (last_of_head && t + 1 < total) {
-                    if (!mbar_wait(head_ready, (g + 1) & 1, abort_flag)) { ok = false; break; }
-                    if (!issue_sp(t + 1)) { ok = false; break; }
-                }
-                if (++j == n_kv) { j = 0; ++g; }
+                if (++j == n_kv) j = 0;
             }
             if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
         }
