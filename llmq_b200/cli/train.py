@@ -165,6 +165,10 @@ def run_training(cfg: TrainingConfig, argv=None) -> dict:
     else:
         trainer.import_weights(model_dir)
     logger.log_allocator(trainer.get_allocator_info(0), rank)
+    if cfg.debug_log_allocations > 0 and getattr(trainer, "model", None) is not None:
+        from ..utils.memory import large_tensors
+        for name, shape, mib, where in large_tensors(trainer.model, cfg.debug_log_allocations):
+            logger.log_message(start_step, f"allocation {name} {tuple(shape)} {mib:.0f} MiB ({where})")
 
     schedule = make_schedule(cfg.lr_schedule, cfg.learning_rate, steps, cfg.warmup_steps, cfg.final_lr_fraction, cfg.cooldown_steps)
     pin = trainer.device.type == "cuda"
@@ -213,6 +217,10 @@ def run_training(cfg: TrainingConfig, argv=None) -> dict:
         if abs(zl) > 10 or abs(zn) > 10:
             logger.log_message(step, f"outlier detected: loss z-score {zl:.1f}, norm z-score {zn:.1f}")
         logger.log_step(step, step_tokens, ms, res["norm"], res["loss"], res["loss_1k"], res["z_max"], res["z_mean"], lr)
+        if cfg.debug_time_breakdown and res.get("time_breakdown"):
+            logger.log_time_breakdown(step, res["time_breakdown"])
+        if cfg.debug_log_abs_max > 0 and step % cfg.debug_log_abs_max == 0 and getattr(trainer, "model", None) is not None:
+            logger.log_abs_maxes(step, trainer.model.abs_maxes())
     evaluate(steps)
     if cfg.save_training_state:
         save(steps)

@@ -14,6 +14,8 @@ gate into ``up_w`` [2D, C] (up first), embeddings may be tied to the LM head.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from types import SimpleNamespace
 from typing import Dict, List, Optional
@@ -30,6 +32,40 @@ from ..parallel.zero import F8_TYPES, MATRICES, GradientManager, OptimizerStateM
 # abs-max slots per layer: index -> (absmax, scale)
 S_LN1, S_ATT, S_LN2, S_SWIGLU, S_DRESFFN, S_DMLPUP, S_DRESATT, S_DQKV = range(8)
 N_SLOTS = 16
+
+
+class _BlockGraphs:
+    """CUDA graphs of the per-layer forward and recompute + backward bodies (``--use-cuda-graphs``).
+
+    Every layer works on its own fixed buffers, so each (phase, layer, accumulate) body is captured once - on its
+    second execution, after an eager warm-up run - and replayed afterwards; one replay stands for the ~20-45 kernel
+    launches of a block.  Role of the per-block capture / update in the reference (llama_model.cpp:120-176,403-459).
+    """
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.stream = torch.cuda.Stream(device)
+        self.graphs: Dict[tuple, tuple] = {}
+        self.warm: set = set()
+
+    def run(self, key: tuple, fn) -> None:
+        from ..ops import lib as _L
+        entry = self.graphs.get(key)
+        if entry is None:
+            if key not in self.warm:                       # first time: plain launches (lazy one-time set-up happens here)
+                self.warm.add(key)
+                fn()
+                return
+            graph = torch.cuda.CUDAGraph()
+            before = _L.launch_count
+            self.stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.graph(graph, stream=self.stream):
+                fn()
+            entry = (graph, _L.launch_count - before)
+            _L.launch_count = before                       # capturing launched nothing
+            self.graphs[key] = entry
+        entry[0].replay()
+        _L.launch_count += entry[1]
 
 
 class LlamaModel:
@@ -49,6 +85,12 @@ class LlamaModel:
         if seq_len > cfg.max_position_embeddings:
             raise ValueError("sequence length exceeds max_position_embeddings")
         self.fused = self._make_fused()
+        self._marks: List = []
+        # per-block CUDA graphs: only where a block body contains nothing but kernels on fixed buffers
+        self.graphs = None
+        if (opts.use_cuda_graphs and self.device.type == "cuda" and not opts.offload_residual
+                and os.environ.get("LLMQ_GEMM_RS", "0") != "1" and os.environ.get("LLMQ_GEMM_POLL", "0") != "1"):
+            self.graphs = _BlockGraphs(self.device)
         self.weights = WeightsManager(cfg, opts, self.comm, self.device, self.fused)
         self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
         self.opt_state = OptimizerStateManager(cfg, opts, self.comm, self.device, self.weights)
@@ -153,6 +195,30 @@ class LlamaModel:
         self.tmp = t
         self.host_scalars = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
 
+    # ---- optional phase timing (--debug-time-breakdown): CUDA events on the main stream, read after the step
+    def _mark(self, name: str) -> None:
+        if self.opts.trigger_timing_events and self.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.device))
+            self._marks.append((name, ev))
+
+    def time_breakdown(self) -> Dict[str, float]:
+        """Milliseconds per phase since the last call (phases of all micro-steps are summed); synchronises."""
+        marks, self._marks = self._marks, []
+        out: Dict[str, float] = {}
+        if len(marks) < 2:
+            return out
+        marks[-1][1].synchronize()
+        for (n0, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
+            if n1 != "start":
+                out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
+        return out
+
+    def abs_maxes(self) -> Dict[str, List[float]]:
+        """Abs-max of every quantised activation / gradient slot, per layer (--debug-log-abs-max)."""
+        vals = self.stats[:, :, 0].float().cpu()
+        return {f"layer{l}": [round(float(v), 6) for v in vals[l]] for l in range(vals.shape[0])}
+
     def _slot(self, l: int, s: int):
         st = self.stats[l, s]
         return st[0:1], st[1:2]
@@ -222,6 +288,7 @@ class LlamaModel:
         """inputs: int32 (B, T) on any device.  Activations stay in the run state for ``backward``."""
         cfg, a, w = self.cfg, self.acts, self.weights
         L = cfg.num_hidden_layers
+        self._mark("start")
         if inputs is not None:                    # None: the caller already placed the tokens in self.inputs
             self.inputs.copy_(inputs.reshape(self.B, self.T), non_blocking=True)
         K.encoder_forward(a.x.write_target(0), self.inputs, w.get_embeddings())
@@ -239,7 +306,10 @@ class LlamaModel:
                 K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.res_att[l - 1], p.ln1_w, cfg.rms_norm_eps, residual_out=a.x.write_target(l),
                                   inp2=self.tmp.proj, absmax=am)
                 a.x.written(l)
-            self._forward_block(l, p)
+            if self.graphs is not None:
+                self.graphs.run(("fwd", l), lambda: self._forward_block(l, p))
+            else:
+                self._forward_block(l, p)
             w.release_block(l)
         K.rmsnorm_forward(self.lnf, self.rstd_f, a.res_att[L - 1], w.get_lnf(), cfg.rms_norm_eps, residual_out=a.x.write_target(L),
                           inp2=self.tmp.proj)
@@ -326,7 +396,9 @@ class LlamaModel:
             self.losses.zero_()
         g.start_micro_step(micro_step, grad_accum)
         dloss = 1.0 / (self.B * self.T * grad_accum)
+        self._mark("forward")
         self._lmhead(write_grads=True, dloss=dloss, z_loss=z_loss, accumulate_dw=micro_step > 0)
+        self._mark("lm-head")
         # final norm: t.d_ln holds d(lnf); produce d(residual stream) in t.d_res
         t.d_res.zero_()
         K.rmsnorm_backward(t.d_res, g.nb_full["lnf_w"], t.norm_scratch, t.d_ln, a.x.get(L), w.get_lnf(), self.rstd_f,
@@ -339,8 +411,14 @@ class LlamaModel:
             if l > 0:
                 w.gather_block(l - 1)
             p = w.get_block(l)
-            self._recompute_block(l, p)
-            self._backward_block(l, p, dw, acc)
+            if self.graphs is not None:
+                def body(l=l, p=p, dw=dw, acc=acc):
+                    self._recompute_block(l, p)
+                    self._backward_block(l, p, dw, acc)
+                self.graphs.run(("bwd", l, bool(acc)), body)
+            else:
+                self._recompute_block(l, p)
+                self._backward_block(l, p, dw, acc)
             # LN1 backward adds into the residual gradient, which then belongs to layer l-1 (or the embedding)
             slot = self._slot(l - 1, S_DRESFFN)[0] if l > 0 else None
             K.rmsnorm_backward(t.d_res, dw["ln1_w"], t.norm_scratch, t.d_ln, a.x.get(l), p.ln1_w, a.rstd1[l], absmax=slot,
@@ -352,6 +430,7 @@ class LlamaModel:
         K.encoder_backward(g.nb_full["embed"], t.d_res, self.inputs)
         g.notify_non_block("embed")
         g.end_micro_step()
+        self._mark("backward")
 
     def _recompute_block(self, l: int, p) -> None:
         cfg, a, t, re = self.cfg, self.acts, self.tmp, self.re
@@ -498,9 +577,13 @@ class LlamaModel:
         hs = self.host_scalars
         hs[0:2].copy_(self.norm_io, non_blocking=True)
         hs[2:4].copy_(self.lse_stats, non_blocking=True)
+        self._mark("optimizer")
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
-        return {"loss": loss, "loss_1k": loss1k, "norm": float(hs[0]), "z_max": float(hs[2]), "z_mean": float(hs[3]) / ntok}
+        res = {"loss": loss, "loss_1k": loss1k, "norm": float(hs[0]), "z_max": float(hs[2]), "z_mean": float(hs[3]) / ntok}
+        if self.opts.trigger_timing_events:
+            res["time_breakdown"] = self.time_breakdown()
+        return res
 
     # ================================================================================== introspection
     def get_gradients(self) -> Dict[str, torch.Tensor]:

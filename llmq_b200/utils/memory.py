@@ -155,3 +155,49 @@ def allocator_report(model) -> Dict[str, Dict[str, int]]:
         free, total = torch.cuda.mem_get_info(model.device)
         rep["_device"] = {"free": free, "total": total, "reserved": torch.cuda.memory_reserved(model.device)}
     return rep
+
+
+def large_tensors(model, min_mib: float):
+    """[(name, shape, MiB, device | pinned | host)] of the model's weight / optimizer / gradient / activation tensors
+    of at least ``min_mib`` MiB (``--debug-log-allocations``), largest first."""
+    seen, out = set(), []
+
+    def add(name, t):
+        if not isinstance(t, torch.Tensor) or t.numel() == 0:
+            return
+        key = t.untyped_storage().data_ptr()
+        mib = t.untyped_storage().nbytes() / 2**20
+        if key in seen or mib < min_mib:
+            return
+        seen.add(key)
+        where = "device" if t.device.type == "cuda" else ("pinned" if t.is_pinned() else "host")
+        out.append((name, tuple(t.shape), mib, where))
+
+    w = model.weights
+    for i, b in enumerate(w.bufs):
+        for n, t in b.t.items():
+            add(f"work[{i}].{n}", t)
+    for l, d in enumerate(w.master_blocks):
+        for n, t in d.items():
+            add(f"master[{l}].{n}", t)
+    for n, t in w.master_nb.items():
+        add(f"master.{n}", t)
+    for n, t in model.opt_state.m.items():
+        add(f"adam_m.{n}", t)
+    for n, t in model.opt_state.v.items():
+        add(f"adam_v.{n}", t)
+    g = model.grads
+    for coll_name in ("full", "bufs", "shards"):
+        for l, d in enumerate(getattr(g, coll_name, [])):
+            for n, t in d.items():
+                add(f"grad_{coll_name}[{l}].{n}", t)
+    for n, t in g.nb_full.items():
+        add(f"grad.{n}", t)
+    for n, v in vars(model.acts).items():
+        if hasattr(v, "dev"):
+            v = list(v.dev) + list(getattr(v, "host", []))
+        for i, t in enumerate(v if isinstance(v, list) else [v]):
+            add(f"act.{n}[{i}]", t)
+    for n, t in vars(model.tmp).items():
+        add(f"tmp.{n}", t)
+    return sorted(out, key=lambda e: -e[2])

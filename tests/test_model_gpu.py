@@ -90,3 +90,33 @@ def test_variants_bit_identical_on_gpu(kw, mm):
 def test_loss_goes_down_fp8():
     _, _, out, _ = run(LLamaOptions(matmul_type="e4m3", momentum_type="bf16", variance_type="bf16"), steps=8, ga=1, lr=3e-3)
     assert out[-1][0] < out[0][0] - 0.3, out
+
+
+@pytest.mark.parametrize("mm", [None, "e4m3"])
+def test_cuda_graphs_reproduce_eager_steps(mm):
+    """Per-block CUDA graphs (captured on the second step, replayed afterwards) give the same steps as plain launches."""
+    from llmq_b200.ops import lib as L
+    base = run(LLamaOptions(matmul_type=mm), steps=4, ga=2)[2]
+    n0 = L.launch_count
+    cfg, m, out, _ = run(LLamaOptions(matmul_type=mm, use_cuda_graphs=True), steps=4, ga=2)
+    assert m.graphs is not None and len(m.graphs.graphs) >= 2 * cfg.num_hidden_layers     # fwd + bwd of every layer
+    assert out == base, (out, base)
+    # replays are still counted as kernel launches
+    n1 = L.launch_count
+    run(LLamaOptions(matmul_type=mm), steps=4, ga=2)
+    assert n1 - n0 == L.launch_count - n1
+
+
+def test_time_breakdown_reports_phases():
+    opts = LLamaOptions(matmul_type="e4m3", trigger_timing_events=True)
+    m = LlamaModel(cfg_small(), opts, device="cuda:0", batch_size=B, seq_len=T)
+    m.init_weights(0)
+    x, y = data(2, 1)
+    for j in range(2):
+        m.forward(x[j], j)
+        m.backward(x[j], y[j], 0.0, 2, j)
+    r = m.update(lr=1e-3, step=1, grad_accum=2)
+    tb = r["time_breakdown"]
+    assert set(tb) == {"forward", "lm-head", "backward", "optimizer"} and all(v > 0 for v in tb.values()), tb
+    am = m.abs_maxes()
+    assert len(am) == 2 and max(am["layer0"]) > 0
