@@ -5,17 +5,23 @@
 // packed gradient dqkv with the same layout.  It takes the place of the cuDNN SDPA graphs and the
 // scalar fallback kernel of the reference (src/kernels/cudnn_att.cpp:46-263, src/kernels/attention.cu).
 //
-// Every CTA has 128 threads; thread i owns row i of the 128-row MMA tile (TMEM lane i), so softmax
-// statistics never leave the thread.  Score tiles are produced in TMEM by tcgen05.mma, read back with
-// tcgen05.ld, turned into bf16 probabilities in shared memory (128-byte swizzled, K-major) and fed to
-// the second MMA.  The shared-memory tile of V (rows = key positions) doubles as an MN-major B operand,
-// so no transposed copy of V, K, Q or dO is ever made.
+// All three main kernels share one organisation.  A CTA owns a 128-row tile (queries for forward and dQ, keys for
+// dK / dV) and has 19 warps: 16 compute warps (four warpgroups; thread (wg, r) owns row r = TMEM lane r and a quarter
+// of the columns of every score tile), one warp whose lane 0 issues the score MMAs, one whose lane 0 issues the TMA
+// loads and one whose lane 0 issues the accumulation MMAs.  MMA issue is synchronous with execution, so two issuing
+// threads are needed to keep the tensor pipe busy while the other one waits for the compute warps.  Everything is
+// handed over through mbarriers (one arrival per warp); score tiles are double buffered in tensor memory, the
+// streamed operand (K / V, or Q / dO for dK / dV) sits in a ring of four shared-memory buffers.  Operands that are
+// constant during a walk live in tensor memory as A operands where the 512 columns allow it (Q in forward, Q and dO
+// in dQ; the bf16 probabilities of the forward pass too), so they are not re-read from shared memory by every MMA.
+// The shared-memory tile of V / K / Q / dO doubles as an MN-major B operand, so no transposed copy is ever made.
 //
 // Backward is split into two deterministic kernels (no atomics):
 //   * dK/dV: one CTA per (batch, kv head, 128 keys) walks over all query heads of the group and all
 //     query blocks at or below the diagonal; dK and dV accumulate in TMEM across the whole walk.
-//   * dQ   : one CTA per (batch, q head, 128 queries) walks over the key blocks; dQ accumulates in TMEM.
-// A small pre-pass computes delta = rowsum(dO * O).
+//   * dQ   : one CTA per (batch, kv head, 128 queries) walks over the query heads of the group and their key
+//     blocks; dQ accumulates in TMEM and is drained once per head.
+// A small pre-pass computes delta = rowsum(dO * O).  Blocks with the longest walks are scheduled first.
 #include "ptx_sm100.cuh"
 #include "api.h"
 #include "common.cuh"
@@ -82,21 +88,6 @@ int encode_btw(CUtensorMap* out, const void* base, int B, int T, long long W, in
     return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 
-// Writes 32 consecutive bf16 values (columns c0 .. c0+31 of row `row`) into a [rows][64] K-major tile with
-// the 128-byte swizzle: 16-byte unit u of a row lands at unit (u ^ (row & 7)).
-__device__ __forceinline__ void store_row_chunk_swz(uint8_t* tile, int row, int c0, const float (&v)[32]) {
-    uint8_t* rowp = tile + row * 128;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-        uint4 o;
-        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
-        int u = (c0 >> 3) + g;
-        *reinterpret_cast<uint4*>(rowp + ((u ^ (row & 7)) << 4)) = o;
-    }
-}
-
 struct AttnParams {
     int B, T, Hq, Hkv;
     float scale;                 // 1/sqrt(HS)
@@ -108,213 +99,6 @@ struct AttnParams {
     const bf16* d_out;
     unsigned int* status;
 };
-
-// ------------------------------------------------------------------------------------------------
-// Forward.  O accumulates in TMEM across all key tiles (tcgen05.mma with accumulate); it is rescaled only when a
-// row maximum moved by more than 2^8 since the last rescale (the stale maximum keeps P <= 256, exact in the
-// final normalisation).  Score tiles are double buffered in TMEM and K / V in shared memory, so the tensor core
-// computes S(j+1) while the threads run the softmax of tile j.
-template <int HS>
-__global__ void __launch_bounds__(128, 2)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv, const AttnParams p) {
-    constexpr int BQ = 128, BKV = 64, NCH = HS / 64;
-    constexpr int Q_BYTES = BQ * HS * 2, KV_BYTES = BKV * HS * 2, P_BYTES = BQ * BKV * 2;
-    constexpr uint32_t TMEM_COLS = 256;                       // S0 | S1 | O
-    constexpr float kRescaleThreshold = 8.f;                  // in log2 units
-    extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;
-    uint8_t* sK = sQ + Q_BYTES;            // 2 buffers
-    uint8_t* sV = sK + 2 * KV_BYTES;       // 2 buffers
-    uint8_t* sP = sV + 2 * KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-
-    const int tid = threadIdx.x, warp = tid >> 5;
-    if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }   // swizzled tiles need 1 KiB alignment
-    const int qb = gridDim.x - 1 - blockIdx.x;                // longest rows first
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int kvh = h / (p.Hq / p.Hkv);
-    const int q0 = qb * BQ;
-    const int n_kv = min((p.T + BKV - 1) / BKV, (q0 + BQ) / BKV);
-    const int qcol = h * HS, kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
-
-    const uint32_t bar0 = smem_u32(bars);
-    const uint32_t q_bar = bar0, o_bar = bar0 + 8;
-    auto k_bar = [&](int i) { return bar0 + 16 + 8 * i; };
-    auto v_bar = [&](int i) { return bar0 + 32 + 8 * i; };
-    auto s_bar = [&](int i) { return bar0 + 48 + 8 * i; };
-    if (tid == 0) {
-        for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8 * i, 1);
-        *abort_flag = 0;
-        mbar_init_fence();
-    }
-    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = *tmem_slot;
-    const uint32_t tO = tmem + 128;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-
-    auto load_k = [&](int j) {
-        const int bi = j & 1;
-        mbar_expect_tx(k_bar(bi), KV_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sK) + bi * KV_BYTES + c * (BKV * 128), &tmap_kv, k_bar(bi), kcol + c * 64, j * BKV, b);
-    };
-    auto load_v = [&](int j) {
-        const int bi = j & 1;
-        mbar_expect_tx(v_bar(bi), KV_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sV) + bi * KV_BYTES + c * (BKV * 128), &tmap_kv, v_bar(bi), vcol + c * 64, j * BKV, b);
-    };
-    const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
-    const uint32_t idesc_o = make_instr_desc(1, 1, false, true, BQ, HS);
-    auto issue_s = [&](int j) {                               // S[j&1] = Q K(j)^T
-        const int bi = j & 1;
-#pragma unroll
-        for (int k = 0; k < HS / 16; ++k) {
-            mma_issue<false, false>(tmem + bi * 64, DLO(smem_u32(sQ), 16, (k / 4) * (BQ * 128) + (k % 4) * 32), kDescHi,
-                                    DLO(smem_u32(sK), 16, bi * KV_BYTES + (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
-        }
-        mma_commit(s_bar(bi));
-    };
-
-    bool ok = true;
-    if (tid == 0) {
-        tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_kv);
-        mbar_expect_tx(q_bar, Q_BYTES);
-        for (int c = 0; c < NCH; ++c) tma_load_3d(smem_u32(sQ) + c * (BQ * 128), &tmap_q, q_bar, qcol + c * 64, q0, b);
-        load_k(0); load_v(0);
-        if (n_kv > 1) { load_k(1); load_v(1); }
-        ok = mbar_wait(q_bar, 0, abort_flag) && mbar_wait(k_bar(0), 0, abort_flag);
-        tc_fence_after_sync();
-        if (ok) issue_s(0);
-    }
-
-    const float sl2 = p.scale * kLog2e;
-    const int row = q0 + tid;
-    float m_ref = -INFINITY, l = 0.f;
-
-    for (int j = 0; j < n_kv && ok; ++j) {
-        const int bi = j & 1;
-        const uint32_t par = (j >> 1) & 1;
-        if (!mbar_wait(s_bar(bi), par, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (tid == 0) {
-            if (j + 1 < n_kv) {                               // next score tile runs on the tensor core during this softmax
-                ok = mbar_wait(k_bar(bi ^ 1), ((j + 1) >> 1) & 1, abort_flag);
-                tc_fence_after_sync();
-                if (ok) issue_s(j + 1);
-            }
-            if (ok && j + 2 < n_kv) load_k(j + 2);            // K[bi] was released by S(j)
-        }
-        float s[64];
-        __syncwarp();
-        {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem + bi * 64 + lane_off, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
-            tmem_ld_32x32b_x32(tmem + bi * 64 + lane_off + 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(r[i]);
-        }
-        if ((j + 1) * BKV > q0) {                             // tile touches the diagonal
-#pragma unroll
-            for (int i = 0; i < 64; ++i) if (j * BKV + i > row) s[i] = -INFINITY;
-        }
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, s[i]);
-        // everything below needs PV(j-1) finished: it read P, and it wrote the O we may rescale
-        if (j > 0) {
-            if (!mbar_wait(o_bar, (j - 1) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after_sync();
-            if (tid == 0 && j + 1 < n_kv && j + 1 >= 2) load_v(j + 1);     // V[(j+1)&1] was released by PV(j-1)
-        }
-        const bool need = j == 0 ? true : (mx - m_ref) * sl2 > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-            const float m_new = fmaxf(m_ref, mx);
-            if (j > 0) {
-                const float alpha = exp2f((m_ref - m_new) * sl2);
-                l *= alpha;
-#pragma unroll
-                for (int c = 0; c < HS / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(tO + lane_off + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st_32x32b_x32(tO + lane_off + c * 32, r);
-                }
-                tmem_st_wait();
-            }
-            m_ref = m_new;
-        }
-        const float moff = m_ref * sl2;
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 64; ++i) { s[i] = exp2f(s[i] * sl2 - moff); sum += s[i]; }
-        l += sum;
-        {
-            float t[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) t[i] = s[i];
-            store_row_chunk_swz(sP, tid, 0, t);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) t[i] = s[32 + i];
-            store_row_chunk_swz(sP, tid, 32, t);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
-        if (tid == 0) {
-            ok = mbar_wait(v_bar(bi), par, abort_flag);
-            tc_fence_after_sync();
-            if (ok) {
-#pragma unroll
-                for (int k = 0; k < BKV / 16; ++k) {
-                    mma_issue<false, false>(tO, DLO(smem_u32(sP), 16, k * 32), kDescHi,
-                                            DLO(smem_u32(sV), BKV * 128, bi * KV_BYTES + k * (16 * 128)), kDescHi, idesc_o, (j > 0 || k > 0));
-                }
-                mma_commit(o_bar);
-            }
-        }
-    }
-    if (ok && n_kv > 0) ok = mbar_wait(o_bar, (n_kv - 1) & 1, abort_flag);
-    tc_fence_after_sync();
-    if (!ok && tid == 0) atomicOr(p.status, kErrOther);
-
-    if (ok) {
-        const float inv = 1.f / l;
-        bf16* o = p.out + ((static_cast<long long>(b) * p.T + (row < p.T ? row : 0)) * p.Hq + h) * HS;
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < HS / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tO + lane_off + c * 32, r);
-            tmem_ld_wait();
-            if (row < p.T) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 v;
-                    __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj)
-                        vb[jj] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * jj]) * inv, __uint_as_float(r[g * 8 + 2 * jj + 1]) * inv);
-                    *reinterpret_cast<uint4*>(o + c * 32 + g * 8) = v;
-                }
-            }
-        }
-        if (row < p.T) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + row] = m_ref * p.scale + logf(l);
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
-}
 
 // ------------------------------------------------------------------------------------------------
 // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per row
@@ -848,6 +632,286 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box
     if (issuer) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Forward.  Same organisation as the dQ kernel: one CTA owns 128 query rows of one kv head and walks over the query
+// heads of the group and, per head, over the 64-key tiles up to the diagonal.  Q lives in tensor memory as the A
+// operand of S = Q K^T; the bf16 probabilities go back into tensor memory (two buffers) and are the A operand of
+// O += P V, so neither Q nor P is ever re-read from shared memory; K / V stream through a ring of four buffers.
+// Four threads share a row (16 score columns each): the row maximum is exchanged through shared memory once per
+// tile, the row sum only at the end of a head.  O is rescaled only when a row maximum moved by more than 2^8 since
+// the last rescale (the stale maximum keeps P <= 256, exact after the final normalisation).
+template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&r)[N]) {
+    if constexpr (N == 32) tmem_ld_32x32b_x32(addr, r); else tmem_ld_32x32b_x16(addr, r);
+}
+template <int N> __device__ __forceinline__ void tmem_st_cols(uint32_t addr, const uint32_t (&r)[N]) {
+    if constexpr (N == 32) tmem_st_32x32b_x32(addr, r); else tmem_st_32x32b_x16(addr, r);
+}
+
+template <int HS>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64 rows
+                const AttnParams p) {
+    constexpr int BQ = 128, BKV = 64, NCH = HS / 64, NBUF = 4;
+    constexpr int KV_BYTES = BKV * HS * 2;
+    constexpr uint32_t TMEM_COLS = 512;                       // Q | S0 S1 | P0 P1 (bf16 pairs) | O
+    constexpr int CW = BKV / kBwdWarpgroups;                  // score columns per thread
+    constexpr int ECW = HS / kBwdWarpgroups;                  // output columns per thread
+    constexpr float kRescaleThreshold = 8.f;                  // in log2 units
+    static_assert(CW == 16, "the column split below is written for 16 columns per thread");
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sK = smem;                       // NBUF buffers
+    uint8_t* sV = sK + NBUF * KV_BYTES;       // NBUF buffers
+    float* sMax = reinterpret_cast<float*>(sV + NBUF * KV_BYTES);     // [2][4][128] slice maxima of a tile
+    float* sSum = sMax + 2 * kBwdWarpgroups * BQ;                      // [4][128] slice sums of a head
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSum + kBwdWarpgroups * BQ);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const bool issuer = warp == kBwdComputeWarps, producer = warp == kBwdComputeWarps + 1, issuer2 = warp == kBwdComputeWarps + 2;
+    const int wg = tid >> 7, r = tid & 127;
+    if (smem_u32(smem) & 1023u) { if (tid == 0) atomicOr(p.status, kErrOther); return; }
+    const int nqb = (p.T + BQ - 1) / BQ;
+    const int qb = nqb - 1 - blockIdx.x / (p.Hkv * p.B);        // 1-D grid, longest key walks first
+    const int kvh = (blockIdx.x % (p.Hkv * p.B)) % p.Hkv, b = (blockIdx.x % (p.Hkv * p.B)) / p.Hkv;
+    const int G = p.Hq / p.Hkv;
+    const int q0 = qb * BQ;
+    const int n_kv = min((p.T + BKV - 1) / BKV, (q0 + BQ) / BKV);
+    const int total = n_kv * G;                                 // tiles of the whole walk, t = g * n_kv + j
+    const int kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
+
+    // barriers: 0 head_ready | 1-4 k/v ring | 5-6 s (scores ready) | 7-8 s_free | 9-10 p_ready | 11-12 p_free (PV of the
+    //           tile done) | 13-16 k/v buffer free.  Two-entry sets alternate with the tile parity.
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t head_ready = bar0;
+    auto kv_bar = [&](int buf) { return bar0 + 8 + 8 * buf; };
+    auto s_bar = [&](int t) { return bar0 + 40 + 8 * (t & 1); };
+    auto s_free = [&](int t) { return bar0 + 56 + 8 * (t & 1); };
+    auto p_ready = [&](int t) { return bar0 + 72 + 8 * (t & 1); };
+    auto p_free = [&](int t) { return bar0 + 88 + 8 * (t & 1); };
+    auto kv_free = [&](int buf) { return bar0 + 104 + 8 * buf; };
+    if (tid == 0) {
+        mbar_init(head_ready, kBwdComputeWarps);
+        for (int i = 0; i < 4; ++i) { mbar_init(kv_bar(i), 1); mbar_init(kv_free(i), 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_bar(i), 1); mbar_init(p_free(i), 1);
+            mbar_init(s_free(i), kBwdComputeWarps); mbar_init(p_ready(i), kBwdComputeWarps);
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (issuer) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tQ = tmem, tS0 = tmem + HS / 2, tP0 = tS0 + 2 * BKV, tO = tP0 + BKV;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    bool ok = true;
+
+    if (producer) {
+        // ============================================================ TMA producer warp
+        if ((tid & 31) == 0 && total > 0) {
+            tma_prefetch_desc(&tmap_kv64);
+            int j = 0;
+            for (int t = 0; t < total; ++t) {
+                const int buf = t % NBUF;
+                if (t >= NBUF && !mbar_wait(kv_free(buf), ((t / NBUF) - 1) & 1, abort_flag)) { atomicOr(p.status, kErrOther); break; }
+                mbar_expect_tx(kv_bar(buf), 2 * KV_BYTES);
+                for (int c = 0; c < NCH; ++c) {
+                    tma_load_3d(smem_u32(sK) + buf * KV_BYTES + c * (BKV * 128), &tmap_kv64, kv_bar(buf), kcol + c * 64, j * BKV, b);
+                    tma_load_3d(smem_u32(sV) + buf * KV_BYTES + c * (BKV * 128), &tmap_kv64, kv_bar(buf), vcol + c * 64, j * BKV, b);
+                }
+                if (++j == n_kv) j = 0;
+            }
+        }
+    } else if (issuer) {
+        // ============================================================ S = Q K^T issuer warp
+        if ((tid & 31) == 0 && total > 0) {
+            const uint32_t idesc_s = make_instr_desc(1, 1, false, false, BQ, BKV);
+            int g = 0, j = 0;
+            for (int t = 0; t < total && ok; ++t) {
+                const int buf = t % NBUF;
+                if (j == 0 && !mbar_wait(head_ready, g & 1, abort_flag)) { ok = false; break; }       // this head's Q is in tensor memory
+                if (!mbar_wait(kv_bar(buf), (t / NBUF) & 1, abort_flag)) { ok = false; break; }
+                if (t >= 2 && !mbar_wait(s_free(t), ((t - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < HS / 16; ++k) {
+                    mma_issue_f16_tmem_a(tS0 + (t & 1) * BKV, tQ + k * 8,
+                                         DLO(smem_u32(sK) + buf * KV_BYTES, 16, (k / 4) * (BKV * 128) + (k % 4) * 32), kDescHi, idesc_s, k > 0);
+                }
+                mma_commit(s_bar(t));
+                if (++j == n_kv) { j = 0; ++g; }
+            }
+            if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
+        }
+    } else if (issuer2) {
+        // ============================================================ O += P V issuer warp
+        if ((tid & 31) == 0 && total > 0) {
+            const uint32_t idesc_o = make_instr_desc(1, 1, false, true, BQ, HS);
+            int j = 0;
+            for (int t = 0; t < total && ok; ++t) {
+                if (!mbar_wait(p_ready(t), (t >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const int buf = t % NBUF;
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k) {
+                    mma_issue_f16_tmem_a(tO, tP0 + (t & 1) * (BKV / 2) + k * 8,
+                                         DLO(smem_u32(sV) + buf * KV_BYTES, BKV * 128, k * (16 * 128)), kDescHi, idesc_o, (j > 0 || k > 0));
+                }
+                mma_commit(p_free(t));
+                mma_commit(kv_free(buf));
+                if (++j == n_kv) j = 0;
+            }
+            if (!ok) { *abort_flag = 1u; atomicOr(p.status, kErrOther); }
+        }
+    } else {
+        // ============================================================ compute warps
+        const float sl2 = p.scale * kLog2e;
+        const int row = q0 + r;
+        const bool row_ok = row < p.T;
+        const int c0 = wg * CW;
+        const int H = p.Hq + 2 * p.Hkv;
+        const bool stores_q = wg < HS / 32;                     // uniform per warp: the TMEM stores are warp-collective
+        auto load_q = [&](int hq, uint32_t (&wq)[16]) {
+            if (stores_q && row_ok) {
+                const uint4* gq = reinterpret_cast<const uint4*>(p.qkv + ((static_cast<long long>(b) * p.T + row) * H + hq) * HS + wg * 32);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint4 x = __ldg(gq + q4);
+                    wq[4 * q4] = x.x; wq[4 * q4 + 1] = x.y; wq[4 * q4 + 2] = x.z; wq[4 * q4 + 3] = x.w;
+                }
+            } else {
+#pragma unroll
+                for (int q4 = 0; q4 < 16; ++q4) wq[q4] = 0u;
+            }
+        };
+        auto store_q = [&](const uint32_t (&wq)[16]) {
+            if (stores_q) { tmem_st_32x32b_x16(tQ + lane_off + wg * 16, wq); tmem_st_wait(); }
+            tc_fence_before_sync();
+            warp_arrive(head_ready);
+        };
+        uint32_t wq[16];
+        load_q(kvh * G, wq);
+        store_q(wq);
+        float m_ref = -INFINITY, l_part = 0.f;
+        for (int g = 0; g < G; ++g) {
+            const int h = kvh * G + g;
+            if (g + 1 < G) load_q(h + 1, wq);                   // prefetch: consumed when this head's walk is over
+            m_ref = -INFINITY; l_part = 0.f;
+            for (int j = 0; j < n_kv; ++j) {
+                const int t = g * n_kv + j;
+                float sv[CW];
+                // ---- scores of this thread's 16 columns, masked; slice maximum to shared memory
+                if (ok) {
+                    ok = mbar_wait(s_bar(t), (t >> 1) & 1, abort_flag);
+                    if (ok) {
+                        tc_fence_after_sync();
+                        uint32_t rs[CW];
+                        tmem_ld_32x32b_x16(tS0 + (t & 1) * BKV + lane_off + c0, rs);
+                        tmem_ld_wait();
+                        tc_fence_before_sync();
+                        warp_arrive(s_free(t));
+#pragma unroll
+                        for (int i = 0; i < CW; ++i) sv[i] = __uint_as_float(rs[i]);
+                        if ((j + 1) * BKV > q0) {               // tile touches the diagonal
+                            const int lim = row - j * BKV - c0; // columns above lim are beyond the diagonal (kv > q)
+#pragma unroll
+                            for (int i = 0; i < CW; ++i) if (i > lim) sv[i] = -INFINITY;
+                        }
+                        float mx = sv[0];
+#pragma unroll
+                        for (int i = 1; i < CW; ++i) mx = fmaxf(mx, sv[i]);
+                        sMax[((t & 1) * kBwdWarpgroups + wg) * BQ + r] = mx;
+                    }
+                }
+                compute_barrier();                              // every thread takes part, also after a failed wait
+                if (!ok) continue;
+                float m_tile = -INFINITY;
+#pragma unroll
+                for (int w4 = 0; w4 < kBwdWarpgroups; ++w4) m_tile = fmaxf(m_tile, sMax[((t & 1) * kBwdWarpgroups + w4) * BQ + r]);
+                // ---- lazy rescale.  The TMEM loads / stores are warp-collective, so the decision is taken per warp; the
+                // four warps that share rows see the same numbers and therefore decide alike.
+                const bool need = j == 0 || (m_tile - m_ref) * sl2 > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float m_new = fmaxf(m_ref, m_tile);
+                    if (j > 0) {
+                        const float alpha = fast_exp2((m_ref - m_new) * sl2);
+                        l_part *= alpha;
+                        // O is being accumulated by the PV MMAs of tile t-1: wait for them, then scale this thread's columns
+                        if (!mbar_wait(p_free(t - 1), ((t - 1) >> 1) & 1, abort_flag)) { ok = false; continue; }
+                        tc_fence_after_sync();
+                        uint32_t ro[ECW];
+                        tmem_ld_cols<ECW>(tO + lane_off + wg * ECW, ro);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < ECW; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+                        tmem_st_cols<ECW>(tO + lane_off + wg * ECW, ro);
+                        tmem_st_wait();
+                    }
+                    m_ref = m_new;
+                }
+                // ---- probabilities -> bf16 -> tensor memory (A operand of the PV MMA)
+                const float moff = m_ref * sl2;
+                uint32_t pw[CW / 2];
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < CW; i += 2) {
+                    const float p0 = fast_exp2(fmaf(sv[i], sl2, -moff)), p1 = fast_exp2(fmaf(sv[i + 1], sl2, -moff));
+                    sum += p0 + p1;
+                    pw[i / 2] = pack_bf16x2(p0, p1);
+                }
+                l_part += sum;
+                // this P buffer was read by the PV MMAs of tile t-2
+                if (t >= 2 && !mbar_wait(p_free(t), ((t - 2) >> 1) & 1, abort_flag)) { ok = false; continue; }
+                tc_fence_after_sync();
+                __syncwarp();
+                tmem_st_32x32b_x8(tP0 + (t & 1) * (BKV / 2) + lane_off + wg * (CW / 2), pw);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                warp_arrive(p_ready(t));
+            }
+            // ---- the head's walk is over: row sums, normalise, store; hand the next head's Q to the tensor core
+            const int t_last = g * n_kv + n_kv - 1;
+            if (ok) ok = mbar_wait(p_free(t_last), (t_last >> 1) & 1, abort_flag);
+            tc_fence_after_sync();
+            sSum[wg * BQ + r] = l_part;
+            compute_barrier();
+            if (ok) {
+                float l = 0.f;
+#pragma unroll
+                for (int w4 = 0; w4 < kBwdWarpgroups; ++w4) l += sSum[w4 * BQ + r];
+                const float inv = 1.f / l;
+                uint32_t ro[ECW];
+                __syncwarp();
+                tmem_ld_cols<ECW>(tO + lane_off + wg * ECW, ro);
+                tmem_ld_wait();
+                if (g + 1 < G) store_q(wq);
+                if (row_ok) {
+                    bf16* o = p.out + ((static_cast<long long>(b) * p.T + row) * p.Hq + h) * HS + wg * ECW;
+#pragma unroll
+                    for (int c = 0; c < ECW; c += 8) {
+                        uint4 v;
+                        __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj)
+                            vb[jj] = __floats2bfloat162_rn(__uint_as_float(ro[c + 2 * jj]) * inv, __uint_as_float(ro[c + 2 * jj + 1]) * inv);
+                        *reinterpret_cast<uint4*>(o + c) = v;
+                    }
+                    if (wg == 0) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + row] = m_ref * p.scale + logf(l);
+                }
+            }
+            compute_barrier();                                  // sSum is reused by the next head
+        }
+        if (!ok && r == 0) atomicOr(p.status, kErrOther);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (issuer) tmem_dealloc(tmem, TMEM_COLS);
+}
+
 // Tag makes the static flag unique per kernel instantiation (several kernels share one signature).
 template <int Tag, typename K>
 int set_smem(K kernel, int bytes) {
@@ -865,19 +929,17 @@ int set_smem(K kernel, int bytes) {
 template <int HS>
 int fwd_impl(void* out, float* lse, const void* qkv, int B, int T, int Hq, int Hkv, unsigned int* status, cudaStream_t s) {
     const int H = Hq + 2 * Hkv;
-    CUtensorMap tq, tkv;
-    int rc = encode_btw(&tq, qkv, B, T, static_cast<long long>(H) * HS, 128);
+    CUtensorMap tkv;
+    int rc = encode_btw(&tkv, qkv, B, T, static_cast<long long>(H) * HS, 64);
     if (rc) return rc;
-    rc = encode_btw(&tkv, qkv, B, T, static_cast<long long>(H) * HS, 64);
-    if (rc) return rc;
-    constexpr int smem = 128 * HS * 2 + 4 * 64 * HS * 2 + 128 * 64 * 2 + 128;
+    constexpr int smem = 8 * 64 * HS * 2 + 3 * kBwdWarpgroups * 128 * 4 + 256;
     rc = set_smem<HS>(attn_fwd_kernel<HS>, smem);
     if (rc) return rc;
     AttnParams p{};
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.scale = 1.f / sqrtf(static_cast<float>(HS));
-    p.out = static_cast<bf16*>(out); p.lse = lse; p.status = status;
-    dim3 grid((T + 127) / 128, Hq, B);
-    attn_fwd_kernel<HS><<<grid, 128, smem, s>>>(tq, tkv, p);
+    p.out = static_cast<bf16*>(out); p.lse = lse; p.status = status; p.qkv = static_cast<const bf16*>(qkv);
+    dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
+    attn_fwd_kernel<HS><<<grid, kBwdThreads, smem, s>>>(tkv, p);
     return LLMQ_LAUNCH_CHECK();
 }
 
