@@ -84,7 +84,8 @@ def main():
     ap.add_argument("--lmhead-chunks", type=int, default=4)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (the result is then not the headline metric)")
     ap.add_argument("--collectives", default="auto")
-    ap.add_argument("--cuda-graphs", type=int, default=0, help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs)")
+    ap.add_argument("--cuda-graphs", type=int, default=-1,
+                    help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs), 0 = plain launches, -1 = on for one GPU")
     ap.add_argument("--zero-level", type=int, default=0, help="0 = pick from --gpus (1 GPU: unsharded, else 3)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -104,7 +105,7 @@ def main():
     if args.layers:
         cfg = cfg.replace(num_hidden_layers=args.layers)
     opts = LLamaOptions(recompute_swiglu=True, matmul_type=args.matmul_dtype, momentum_type="bf16", variance_type="bf16",
-                        lmhead_chunks=args.lmhead_chunks, collectives=args.collectives, use_cuda_graphs=bool(args.cuda_graphs))
+                        lmhead_chunks=args.lmhead_chunks, collectives=args.collectives, use_cuda_graphs=(args.cuda_graphs == 1 or (args.cuda_graphs < 0 and args.gpus == 1)))
     zl = args.zero_level or (1 if args.gpus == 1 else 3)
     opts.set_zero_level(zl)
     B, T, GA = args.batch, args.seq_len, args.grad_accum

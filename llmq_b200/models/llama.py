@@ -189,6 +189,7 @@ class LlamaModel:
         if BT % chunks:
             raise ValueError("lmhead_chunks must divide batch * seq_len")
         t.logits = z(BT // chunks, V)
+        t.lnf_T = z(C, BT // chunks) if dev.type == "cuda" else None      # lnf chunk transposed, B operand of the LM-head dW GEMM
         t.att_scratch = torch.zeros(B * Hq * T, dtype=torch.float32, device=dev)
         t.norm_scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32, device=dev)
         t.bias_scratch = torch.zeros(64 * QC, dtype=torch.float32, device=dev)
@@ -373,16 +374,39 @@ class LlamaModel:
         dW = self.grads.nb_full[head_name] if write_grads else None
         tg = self.targets.view(BT)
         losses, lse = self.losses.view(BT), self.lse_tok.view(BT)
+        # The backward GEMMs read W and lnf as B operands along the "wrong" axis; with MN-major TMA loads they run at
+        # 0.6-0.8 of the K-major rate, so on the GPU the two small transposes below (W^T once per optimizer step,
+        # lnf^T per chunk) are cheaper than letting the GEMM read them in place.
+        use_t = write_grads and W.is_cuda and self.opts.lmhead_transposed_operands
+        WT = self._head_transposed(W) if use_t else None
         for c in range(chunks):
             sl = slice(c * n, (c + 1) * n)
             K.gemm(t.logits, self.lnf[sl], W)
             K.fused_classifier(t.logits, losses[sl], lse[sl], tg[sl], dloss, z_reg=z_loss * dloss, write_dlogits=write_grads)
             if write_grads:
-                K.gemm(dW, t.logits, self.lnf[sl], a_mn=True, b_mn=True, accumulate=accumulate_dw or c > 0)
+                if use_t:
+                    K.transpose(t.lnf_T, self.lnf[sl])
+                    K.gemm(dW, t.logits, t.lnf_T, a_mn=True, accumulate=accumulate_dw or c > 0)
+                else:
+                    K.gemm(dW, t.logits, self.lnf[sl], a_mn=True, b_mn=True, accumulate=accumulate_dw or c > 0)
                 if c == chunks - 1 and not cfg.tie_word_embeddings:
                     self.grads.notify_non_block(head_name)
-                K.gemm(t.d_ln[sl], t.logits, W, b_mn=True)
+                if use_t:
+                    K.gemm(t.d_ln[sl], t.logits, WT)
+                else:
+                    K.gemm(t.d_ln[sl], t.logits, W, b_mn=True)
         K.lse_stats(self.lse_stats, self.lse_tok.view(-1), accumulate=False)
+
+    def _head_transposed(self, W: torch.Tensor) -> torch.Tensor:
+        """W^T (C, V) of the LM-head weight, refreshed when the weights changed (once per optimizer step)."""
+        ver = (self.weights.version, W.data_ptr())
+        if getattr(self, "_head_T", None) is None:
+            self._head_T = torch.empty(W.shape[1], W.shape[0], dtype=W.dtype, device=W.device)
+            self._head_T_ver = None
+        if self._head_T_ver != ver:
+            K.transpose(self._head_T, W)
+            self._head_T_ver = ver
+        return self._head_T
 
     # ================================================================================== backward
     def backward(self, inputs: torch.Tensor, targets: torch.Tensor, z_loss: float = 0.0, grad_accum: int = 1,

@@ -26,6 +26,7 @@ class LLamaOptions:
     lmhead_chunks: int = 1
     attn_bwd_chunks: int = 1
     use_cuda_graphs: bool = False
+    lmhead_transposed_operands: bool = True   # LM-head backward reads W^T / lnf^T copies (K-major GEMM operands)
     trigger_timing_events: bool = False
     # placement of state
     offload_master: bool = False
