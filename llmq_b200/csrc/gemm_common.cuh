@@ -41,6 +41,15 @@ struct GemmParams {
     int rs_num_partials;
     unsigned int rs_seed;
     unsigned long long rs_limit_ns;
+    // Optional SwiGLU fused into the epilogue (CTA-pair kernel only, bf16 output).  ep_D = features D.
+    //   ep_mode 1 (forward, N = 2D): the pair stages rows [f, f+128) (up) and [D+f, D+f+128) (gate) of B, so one
+    //     accumulator tile holds up and gate of the same 128 features; C[M, 2D] gets both, ep_ptr[M, D] gets
+    //     up * gate * sigmoid(gate), absmax_out tracks the latter.
+    //   ep_mode 2 (backward, N = D): the accumulator is d(swiglu out); ep_ptr[M, 2D] holds [up | gate] on entry and
+    //     [d_up | d_gate] on exit (in place), C is not written, absmax_out tracks the gradients.
+    int ep_mode;
+    void* ep_ptr;
+    int ep_D;
 };
 
 // Each lane of the calling warp owns one accumulator row (TMEM lane); `t_row` addresses column 0 of that row
@@ -145,6 +154,89 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
                 for (int j = 0; j < 32; ++j)
                     if (col0 + j < p.N) tmax = fmaxf(tmax, fabsf(v[j]));
             }
+        }
+    }
+}
+
+__device__ __forceinline__ float gemm_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+__device__ __forceinline__ void load32_bf16(const __nv_bfloat16* p, float (&v)[32]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p + g * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); v[g * 8 + 2 * j] = f.x; v[g * 8 + 2 * j + 1] = f.y; }
+    }
+}
+__device__ __forceinline__ void store32_bf16(__nv_bfloat16* p, const float (&v)[32]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+        *reinterpret_cast<uint4*>(p + g * 8) = o;
+    }
+}
+
+// SwiGLU forward epilogue: accumulator columns [0,128) = up, [128,256) = gate of features f0 .. f0+127 (all D and
+// row pitches are multiples of 8 elements, so every 32-column chunk is 16-byte aligned).
+__device__ __forceinline__ void epilogue_rows_swiglu_fwd(const GemmParams& p, uint32_t t_row, int row, int f0, float alpha, float& tmax) {
+    using namespace sm100;
+    const bool row_ok = row < p.M;
+    __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+    __nv_bfloat16* srow = static_cast<__nv_bfloat16*>(p.ep_ptr) + static_cast<long long>(row) * p.ep_D;
+#pragma unroll 1
+    for (int c = 0; c < 128; c += 32) {
+        if (f0 + c >= p.ep_D) break;                 // uniform across the warp
+        uint32_t ru[32], rg[32];
+        tmem_ld_32x32b_x32(t_row + c, ru);
+        tmem_ld_32x32b_x32(t_row + 128 + c, rg);
+        tmem_ld_wait();
+        if (row_ok) {
+            float u[32], g[32], o[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                // the saved projection is bf16: the activation is computed from the rounded values, like the separate kernel
+                u[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[j]) * alpha));
+                g[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[j]) * alpha));
+                o[j] = __bfloat162float(__float2bfloat16_rn(u[j] * g[j] * gemm_sigmoid(g[j])));
+                tmax = fmaxf(tmax, fabsf(o[j]));
+            }
+            store32_bf16(crow + f0 + c, u);
+            store32_bf16(crow + p.ep_D + f0 + c, g);
+            store32_bf16(srow + f0 + c, o);
+        }
+    }
+}
+
+// SwiGLU backward epilogue over accumulator columns [0, ncols) = d(out) of features f0 ..
+__device__ __forceinline__ void epilogue_rows_swiglu_bwd(const GemmParams& p, uint32_t t_row, int row, int f0, int ncols, float alpha, float& tmax) {
+    using namespace sm100;
+    const bool row_ok = row < p.M;
+    __nv_bfloat16* urow = static_cast<__nv_bfloat16*>(p.ep_ptr) + static_cast<long long>(row) * 2 * p.ep_D;
+#pragma unroll 1
+    for (int c = 0; c < ncols; c += 32) {
+        if (f0 + c >= p.ep_D) break;
+        uint32_t rd[32];
+        tmem_ld_32x32b_x32(t_row + c, rd);
+        tmem_ld_wait();
+        if (row_ok) {
+            float u[32], g[32];
+            load32_bf16(urow + f0 + c, u);
+            load32_bf16(urow + p.ep_D + f0 + c, g);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float d = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rd[j]) * alpha));   // d(out) as the bf16 the unfused path stores
+                const float sg = gemm_sigmoid(g[j]);
+                const float du = __bfloat162float(__float2bfloat16_rn(d * g[j] * sg));
+                const float dg = __bfloat162float(__float2bfloat16_rn(d * u[j] * sg * (1.f + g[j] * (1.f - sg))));
+                tmax = fmaxf(tmax, fmaxf(fabsf(du), fabsf(dg)));
+                u[j] = du; g[j] = dg;
+            }
+            store32_bf16(urow + f0 + c, u);
+            store32_bf16(urow + p.ep_D + f0 + c, g);
         }
     }
 }

@@ -290,6 +290,20 @@ extern "C" int llmq_gemm_rs(const void* A, const void* B, void* C, int M, int N,
                      nullptr, status, num_sms, nullptr, 0u, 0, 0.0, &rs, stream);
 }
 
+// GEMM with SwiGLU in the epilogue (see GemmParams::ep_mode).  mode 1: C[M, 2D] = A @ B^T with B = [up | gate] rows,
+// aux[M, D] = swiglu(C).  mode 2: aux[M, 2D] ([up | gate] -> [d_up | d_gate], in place) from d(out) = A @ B^T, N = D.
+// bf16 results; M >= 256, D a multiple of 128 (mode 1) / 8 (mode 2).  absmax_out follows the epilogue's output.
+extern "C" int llmq_gemm_swiglu(const void* A, const void* B, void* C, void* aux, int mode, int M, int D, int K, int ab_dtype, int b_dtype,
+                                int a_mn_major, int b_mn_major, long long lda, long long ldb, const float* scale_a, const float* scale_b,
+                                float alpha, float* absmax_out, unsigned int* status, int num_sms, cudaStream_t stream) {
+    if ((mode != 1 && mode != 2) || M < 256 || D % 8 || (mode == 1 && D % 128) || !aux || (mode == 1 && !C)) return -30;
+    GemmParams ep{};
+    ep.ep_mode = mode; ep.ep_ptr = aux; ep.ep_D = D;
+    const int N = mode == 1 ? 2 * D : D;
+    return gemm_impl(A, B, mode == 1 ? C : aux, nullptr, M, N, K, ab_dtype, b_dtype, a_mn_major, b_mn_major, lda, ldb, N, 0, 0, 0, scale_a, scale_b,
+                     alpha, absmax_out, status, num_sms, nullptr, 0u, 0, 0.0, &ep, stream);
+}
+
 extern "C" unsigned int llmq_gemm_rs_arrivals(int M, int N, int world) {
     return static_cast<unsigned int>(world) * static_cast<unsigned int>(M / world / 32) * static_cast<unsigned int>((N + BN - 1) / BN);
 }
@@ -331,6 +345,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
     p.ready_flags = ready_flags; p.ready_gen = ready_gen; p.ready_rows_per_src = ready_rows_per_src > 0 ? ready_rows_per_src : 1;
     p.ready_limit_ns = static_cast<unsigned long long>(ready_limit_s * 1e9);
     if (rs) {
+        p.ep_mode = rs->ep_mode; p.ep_ptr = rs->ep_ptr; p.ep_D = rs->ep_D;
         p.rs_world = rs->rs_world; p.rs_rank = rs->rs_rank; p.rs_shard_rows = rs->rs_shard_rows;
         for (int i = 0; i < 8; ++i) { p.rs_landing[i] = rs->rs_landing[i]; p.rs_counter[i] = rs->rs_counter[i]; }
         p.rs_target = rs->rs_target; p.rs_dst = rs->rs_dst; p.rs_accumulate = rs->rs_accumulate; p.rs_scale = rs->rs_scale;

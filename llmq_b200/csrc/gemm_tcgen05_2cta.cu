@@ -76,7 +76,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int bk = ROW_BYTES / p.elem_bytes;
     const int k_iters = (p.K + bk - 1) / bk;
     const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-    const int tiles_n = (p.N + BN - 1) / BN;
+    // SwiGLU forward mode: a column tile is 128 features, staged as 128 "up" rows + 128 "gate" rows of B
+    const int tiles_n = p.ep_mode == 1 ? (p.ep_D + BN_HALF - 1) / BN_HALF : (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     // fused reduce-scatter: start with the rows owned by the next rank, finish with our own
@@ -120,7 +121,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 int tm, tn; tile_coords(t, tiles_m, tiles_n, rot, tm, tn);
                 const int row0 = (tm * 2 + static_cast<int>(rank)) * BM;               // this CTA's rows of A / C
-                const int brow0 = tn * BN + static_cast<int>(rank) * BN_HALF;          // this CTA's rows of B
+                const int brow0 = p.ep_mode == 1 ? tn * BN_HALF + static_cast<int>(rank) * p.ep_D
+                                                 : tn * BN + static_cast<int>(rank) * BN_HALF;   // this CTA's rows of B
                 if (p.ready_flags && !p.b_mn_major && brow0 < p.N) {
                     const int last = min(brow0 + BN_HALF, p.N) - 1;
                     for (int src = brow0 / p.ready_rows_per_src; src <= last / p.ready_rows_per_src && ok; ++src) ensure_src(src);
@@ -215,7 +217,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const long long slot_row = static_cast<long long>(p.rs_rank) * p.rs_shard_rows + (row - owner * p.rs_shard_rows);
                 dst_row = static_cast<__nv_bfloat16*>(p.rs_landing[owner]) + slot_row * p.N;
             }
-            epilogue_rows(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, row, tn * BN, BN, alpha, tmax, dst_row);
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+            if (p.ep_mode == 1)      epilogue_rows_swiglu_fwd(p, t_row, row, tn * BN_HALF, alpha, tmax);
+            else if (p.ep_mode == 2) epilogue_rows_swiglu_bwd(p, t_row, row, tn * BN, BN, alpha, tmax);
+            else                     epilogue_rows(p, t_row, row, tn * BN, BN, alpha, tmax, dst_row);
             tc_fence_before_sync();
             mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));            // 2 x 128 arrivals at the leader
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -310,7 +315,7 @@ int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
         if (e != cudaSuccess) return static_cast<int>(e);
         attr_set[dev & 63] = true;
     }
-    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+    const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * (p.ep_mode == 1 ? (p.ep_D + BN_HALF - 1) / BN_HALF : (p.N + BN - 1) / BN);
     int pairs = num_sms / 2;
     if (tiles < pairs) pairs = tiles;
     if (p.elem_bytes == 1) gemm_tcgen05_2cta_kernel<true><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);

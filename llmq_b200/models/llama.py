@@ -86,6 +86,9 @@ class LlamaModel:
             raise ValueError("sequence length exceeds max_position_embeddings")
         self.fused = self._make_fused()
         self._marks: List = []
+        # SwiGLU inside the epilogues of the up-projection GEMM and of the down-projection's dX GEMM
+        self._fuse_swiglu = (opts.fuse_swiglu and self.device.type == "cuda" and self.dtype == torch.bfloat16
+                             and batch_size * seq_len >= 256 and cfg.intermediate_size % 128 == 0)
         # per-block CUDA graphs: only where a block body contains nothing but kernels on fixed buffers
         self.graphs = None
         if (opts.use_cuda_graphs and self.device.type == "cuda" and not opts.offload_residual
@@ -259,12 +262,17 @@ class LlamaModel:
             K.quantize(act_q, sc, act, am)
         K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale, ready=ready)
 
-    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None, dw_rs=None):
+    def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None, dw_rs=None,
+                swiglu_inout=None, swiglu_absmax=None):
         """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
         W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second.
-        ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside."""
+        ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside.
+        ``swiglu_inout`` ([up | gate] -> [d_up | d_gate], in place): the input-gradient GEMM applies the SwiGLU backward
+        in its epilogue instead of writing ``dinp``."""
         if not self.quant:
-            if dinp is not None:
+            if swiglu_inout is not None:
+                K.gemm_swiglu_backward(swiglu_inout, dout, W, absmax=swiglu_absmax)
+            elif dinp is not None:
                 K.gemm(dinp, dout, W, b_mn=True, ready=ready)
             if dw_rs is not None:
                 dw_rs(dout, inp)
@@ -275,7 +283,9 @@ class LlamaModel:
             return
         am, sc = slot
         K.quantize(dout_q, sc, dout, am)
-        if dinp is not None:
+        if swiglu_inout is not None:
+            K.gemm_swiglu_backward(swiglu_inout, dout_q, W, scale_a=sc, scale_b=w_scale, absmax=swiglu_absmax)
+        elif dinp is not None:
             K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
         if dw_rs is not None:
             dw_rs(dout_q, inp_q, sc, inp_scale)
@@ -330,8 +340,18 @@ class LlamaModel:
         self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
         K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x.current(l), p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
                           absmax=self._slot(l, S_LN2)[0])
-        self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
-        K.swiglu_forward(a.swiglu[l], a.up[l], absmax=self._slot(l, S_SWIGLU)[0])
+        if self._fuse_swiglu and (int(self.opts.fuse_swiglu) & 1) and p.ready["up_w"] is None:
+            # up projection and SwiGLU from one accumulator tile: the activation never re-reads the projection
+            am, sc = self._slot(l, S_LN2)
+            if self.quant:
+                K.quantize(a.ln2_q[l], sc, a.ln2[l], am)
+                K.gemm_swiglu_forward(a.up[l], a.swiglu[l], a.ln2_q[l], p.up_w, scale_a=sc, scale_b=p.scales["up_w"],
+                                      absmax=self._slot(l, S_SWIGLU)[0])
+            else:
+                K.gemm_swiglu_forward(a.up[l], a.swiglu[l], a.ln2[l], p.up_w, absmax=self._slot(l, S_SWIGLU)[0])
+        else:
+            self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
+            K.swiglu_forward(a.swiglu[l], a.up[l], absmax=self._slot(l, S_SWIGLU)[0])
         self._fwd_mm(t.proj, a.swiglu[l], a.swiglu_q[l] if self.quant else None, self._slot(l, S_SWIGLU), p.down_w, p.scales["down_w"], ready=p.ready["down_w"])
 
     # ================================================================================== validation
@@ -510,10 +530,13 @@ class LlamaModel:
         fused_dw = getattr(self.grads, "fused_dw", None)
         rs = (lambda name: fused_dw(l, name)) if fused_dw is not None else (lambda name: None)
         # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
+        fuse_sw = self._fuse_swiglu and bool(int(self.opts.fuse_swiglu) & 2) and p.ready["down_w"] is None
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
-                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"))
-        # ---- SwiGLU backward, in place over the saved up-projection
-        K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
+                     a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"),
+                     swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0])
+        # ---- SwiGLU backward, in place over the saved up-projection (unless the GEMM epilogue above already did it)
+        if not fuse_sw:
+            K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
         # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
                      a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"))

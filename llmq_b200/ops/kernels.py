@@ -118,6 +118,34 @@ def gemm(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = Fa
         absmax.copy_(torch.maximum(absmax, out.float().abs().max().reshape_as(absmax)))
 
 
+def gemm_swiglu_forward(up_out: torch.Tensor, act_out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, *,
+                        scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
+                        absmax: Optional[torch.Tensor] = None) -> None:
+    """up_out[M, 2D] = a @ w^T (w rows = [up | gate]) and act_out[M, D] = up * gate * sigmoid(gate) from the same
+    accumulator tile; ``absmax`` tracks act_out.  CUDA only (bf16 outputs, M >= 256, D a multiple of 128)."""
+    M, D = act_out.shape
+    st = _dev_state(a.device)
+    rc = L.kernels().llmq_gemm_swiglu(L.ptr(a), L.ptr(w), L.ptr(up_out), L.ptr(act_out), 1, M, D, a.shape[1], L.dtype_code(a.dtype),
+                                      L.dtype_code(w.dtype), 0, 0, _ll(a.stride(0)), _ll(w.stride(0)), L.ptr(scale_a), L.ptr(scale_b),
+                                      _f(1.0), L.ptr(absmax), L.ptr(st["status"]), st["sms"], L.stream_ptr())
+    L.check(rc, "gemm_swiglu_forward")
+
+
+def gemm_swiglu_backward(up_inout: torch.Tensor, dout: torch.Tensor, w: torch.Tensor, *, scale_a: Optional[torch.Tensor] = None,
+                         scale_b: Optional[torch.Tensor] = None, absmax: Optional[torch.Tensor] = None) -> None:
+    """d(act) = dout[M, C] @ w[C, D] stays in the accumulator; up_inout[M, 2D] goes from [up | gate] to [d_up | d_gate]."""
+    M, D2 = up_inout.shape
+    st = _dev_state(dout.device)
+    rc = L.kernels().llmq_gemm_swiglu(L.ptr(dout), L.ptr(w), None, L.ptr(up_inout), 2, M, D2 // 2, dout.shape[1], L.dtype_code(dout.dtype),
+                                      L.dtype_code(w.dtype), 0, 1, _ll(dout.stride(0)), _ll(w.stride(0)), L.ptr(scale_a), L.ptr(scale_b),
+                                      _f(1.0), L.ptr(absmax), L.ptr(st["status"]), st["sms"], L.stream_ptr())
+    L.check(rc, "gemm_swiglu_backward")
+
+
+def gemm_swiglu_supported(M: int, D: int, t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and M >= 256 and D % 128 == 0
+
+
 # =====================================================================================================
 # RMSNorm
 def rmsnorm_forward(y: Optional[torch.Tensor], rstd: Optional[torch.Tensor], inp: torch.Tensor, weight: torch.Tensor, eps: float,

@@ -26,6 +26,10 @@ class LLamaOptions:
     lmhead_chunks: int = 1
     attn_bwd_chunks: int = 1
     use_cuda_graphs: bool = False
+    # bit 0 / 1: SwiGLU forward / backward inside GEMM epilogues (GPU, bf16 activations).  Bit-identical to the separate
+    # kernels; off by default: with four epilogue warps per CTA the extra math takes as long as the memory pass it saves
+    # (Qwen2.5-7B step: 495.6 ms without, 494.3 forward only, 498.9 backward only, 497.8 both).
+    fuse_swiglu: int = 0
     lmhead_transposed_operands: bool = True   # LM-head backward reads W^T / lnf^T copies (K-major GEMM operands)
     trigger_timing_events: bool = False
     # placement of state

@@ -120,3 +120,21 @@ def test_time_breakdown_reports_phases():
     assert set(tb) == {"forward", "lm-head", "backward", "optimizer"} and all(v > 0 for v in tb.values()), tb
     am = m.abs_maxes()
     assert len(am) == 2 and max(am["layer0"]) > 0
+
+
+@pytest.mark.parametrize("mm", [None, "e4m3"])
+def test_swiglu_in_gemm_epilogues_is_bit_identical(mm):
+    """SwiGLU forward / backward inside the GEMM epilogues round exactly like the separate kernels."""
+    base = run(LLamaOptions(matmul_type=mm, fuse_swiglu=0), steps=3, ga=2)
+    fused = run(LLamaOptions(matmul_type=mm, fuse_swiglu=3), steps=3, ga=2)
+    assert fused[1]._fuse_swiglu and not base[1]._fuse_swiglu
+    assert fused[2] == base[2], (fused[2], base[2])
+    for n in base[3]:
+        assert torch.equal(base[3][n], fused[3][n]), n
+
+
+def test_lmhead_transposed_operands_match():
+    base = run(LLamaOptions(matmul_type="e4m3", lmhead_transposed_operands=False), steps=3, ga=2)
+    tr = run(LLamaOptions(matmul_type="e4m3", lmhead_transposed_operands=True), steps=3, ga=2)
+    for (l0, n0), (l1, n1) in zip(base[2], tr[2]):
+        assert abs(l0 - l1) < 2e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0)
