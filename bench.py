@@ -85,6 +85,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (the result is then not the headline metric)")
     ap.add_argument("--collectives", default="auto")
     ap.add_argument("--fuse-swiglu", type=int, default=None)
+    ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--cuda-graphs", type=int, default=-1,
                     help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs), 0 = plain launches, -1 = on for one GPU")
     ap.add_argument("--zero-level", type=int, default=0, help="0 = pick from --gpus (1 GPU: unsharded, else 3)")
@@ -109,6 +110,8 @@ def main():
                         lmhead_chunks=args.lmhead_chunks, collectives=args.collectives, use_cuda_graphs=(args.cuda_graphs == 1 or (args.cuda_graphs < 0 and args.gpus == 1)))
     if args.fuse_swiglu is not None:
         opts.fuse_swiglu = args.fuse_swiglu
+    if args.overlap_dw is not None:
+        opts.overlap_dw = bool(args.overlap_dw)
     zl = args.zero_level or (1 if args.gpus == 1 else 3)
     opts.set_zero_level(zl)
     B, T, GA = args.batch, args.seq_len, args.grad_accum

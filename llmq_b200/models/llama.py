@@ -86,6 +86,9 @@ class LlamaModel:
             raise ValueError("sequence length exceeds max_position_embeddings")
         self.fused = self._make_fused()
         self._marks: List = []
+        self._dw_stream = (torch.cuda.Stream(self.device, priority=-1)
+                           if (opts.overlap_dw and self.device.type == "cuda") else None)
+        self._dw_events: List = []
         # SwiGLU inside the epilogues of the up-projection GEMM and of the down-projection's dX GEMM
         self._fuse_swiglu = (opts.fuse_swiglu and self.device.type == "cuda" and self.dtype == torch.bfloat16
                              and batch_size * seq_len >= 256 and cfg.intermediate_size % 128 == 0)
@@ -277,7 +280,7 @@ class LlamaModel:
             if dw_rs is not None:
                 dw_rs(dout, inp)
             else:
-                K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate)
+                self._launch_dw(lambda: K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate))
             if dbias is not None:
                 K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
             return
@@ -290,9 +293,44 @@ class LlamaModel:
         if dw_rs is not None:
             dw_rs(dout_q, inp_q, sc, inp_scale)
         else:
-            K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
+            self._launch_dw(lambda: K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate))
         if dbias is not None:
             K.bias_backward(dbias, dout_q, self.tmp.bias_scratch, scale_a=sc, accumulate=True)
+
+    # ---- weight-gradient GEMMs off the critical path
+    # A dW GEMM only feeds the optimizer, while the chain dX GEMM -> element-wise kernels -> next dX GEMM decides the
+    # length of the backward pass.  On the GPU the dW GEMMs therefore go to a second, higher-priority stream: their
+    # CTAs (one per SM, tensor-core bound) share the SMs with the memory-bound element-wise kernels of the main
+    # stream.  Every block joins the side stream before it ends, so nothing outlives the buffers it reads.
+    def _launch_dw(self, fn):
+        side = self._dw_stream
+        if side is None:
+            fn()
+            return None
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            fn()
+            done = torch.cuda.Event()
+            done.record(side)
+        self._dw_events.append(done)
+        return done
+
+    def _wait_dw(self, ev) -> None:
+        """The main stream waits for one weight-gradient GEMM."""
+        if self._dw_stream is not None and ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+
+    def _join_dw(self) -> None:
+        """The main stream waits for every outstanding weight-gradient GEMM."""
+        if self._dw_stream is None:
+            return
+        main = torch.cuda.current_stream(self.device)
+        for e in self._dw_events:
+            main.wait_event(e)
+        self._dw_events = []
 
     # ================================================================================== forward
     def forward(self, inputs: torch.Tensor, micro_step: int = 0) -> None:
@@ -534,6 +572,7 @@ class LlamaModel:
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
                      a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"),
                      swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0])
+        ev_down = self._dw_events[-1] if self._dw_events else None      # dW(down) reads d_res / its fp8 copy
         # ---- SwiGLU backward, in place over the saved up-projection (unless the GEMM epilogue above already did it)
         if not fuse_sw:
             K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
@@ -541,6 +580,7 @@ class LlamaModel:
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
                      a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"))
         # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
+        self._wait_dw(ev_down)                                          # the next two kernels overwrite d_res and its fp8 copy
         K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],
                            absmax=self._slot(l, S_DRESATT)[0], accumulate_dweight=True)
         # ---- attention out projection
@@ -554,6 +594,7 @@ class LlamaModel:
         dqkv2d = t.d_qkv.view(BT, cfg.qkv_channels)
         self._bwd_mm(t.d_ln, dw["qkv_w"], dw.get("qkv_b"), dqkv2d, t.d_qkv_q if q else None, self._slot(l, S_DQKV),
                      a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc, ready=p.ready["qkv_w"], dw_rs=rs("qkv_w"))
+        self._join_dw()                                                 # the caller reuses d_res, d_ln and the gradient buffers
 
     # ================================================================================== optimizer
     def update(self, lr: float, beta1: float = 0.9, beta2: float = 0.95, step: int = 1, eps: float = 1e-8,

@@ -26,6 +26,7 @@ class LLamaOptions:
     lmhead_chunks: int = 1
     attn_bwd_chunks: int = 1
     use_cuda_graphs: bool = False
+    overlap_dw: bool = True                   # weight-gradient GEMMs on a second stream, overlapping the element-wise kernels
     # bit 0 / 1: SwiGLU forward / backward inside GEMM epilogues (GPU, bf16 activations).  Bit-identical to the separate
     # kernels; off by default: with four epilogue warps per CTA the extra math takes as long as the memory pass it saves
     # (Qwen2.5-7B step: 495.6 ms without, 494.3 forward only, 498.9 backward only, 497.8 both).

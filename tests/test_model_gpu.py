@@ -138,3 +138,15 @@ def test_lmhead_transposed_operands_match():
     tr = run(LLamaOptions(matmul_type="e4m3", lmhead_transposed_operands=True), steps=3, ga=2)
     for (l0, n0), (l1, n1) in zip(base[2], tr[2]):
         assert abs(l0 - l1) < 2e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0)
+
+
+@pytest.mark.parametrize("mm", [None, "e4m3"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_dw_side_stream_is_bit_identical(mm, graphs):
+    """Weight-gradient GEMMs on the second stream (with and without CUDA graphs) change nothing but the schedule."""
+    base = run(LLamaOptions(matmul_type=mm, overlap_dw=False), steps=4, ga=2)
+    side = run(LLamaOptions(matmul_type=mm, overlap_dw=True, use_cuda_graphs=graphs), steps=4, ga=2)
+    assert side[1]._dw_stream is not None and base[1]._dw_stream is None
+    assert side[2] == base[2], (side[2], base[2])
+    for n in base[3]:
+        assert torch.equal(base[3][n], side[3][n]), n
