@@ -84,6 +84,22 @@ def build(verbose: bool = False, force: bool = False) -> None:
         _compile(cmd, "link runtime", rlib, verbose)
 
 
+def build_tests(verbose: bool = False) -> Path:
+    """Native unit-test executable ``build/test_kernels`` (``csrc/tests/test_kernels.cu``), linked against the kernels library."""
+    build(verbose=verbose)
+    exe = PKG.parent / "build" / "test_kernels"
+    src = CSRC / "tests" / "test_kernels.cu"
+    klib = LIBDIR / "libllmq_b200_kernels.so"
+    if not exe.exists() or exe.stat().st_mtime < max(src.stat().st_mtime, klib.stat().st_mtime):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", str(src), "-o", str(exe),
+               "-L", str(LIBDIR), "-lllmq_b200_kernels", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../llmq_b200/lib"]
+        _compile(cmd, src, exe, verbose)
+    return exe
+
+
 if __name__ == "__main__":
+    if "--tests" in sys.argv:
+        print("built:", build_tests(verbose="-v" in sys.argv))
+        sys.exit(0)
     build(verbose="-v" in sys.argv, force="-f" in sys.argv)
     print("built:", *(p.name for p in LIBDIR.glob("*.so")))

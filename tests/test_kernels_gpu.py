@@ -327,3 +327,12 @@ def test_qk_norm():
     for g, r in zip(res[1], res[0]):
         close(g, r, rtol=2e-2, atol=2e-2)
     assert torch.equal(res[1][0][:, :, Hq + Hkv:].cpu(), qkv[:, :, Hq + Hkv:])
+
+
+def test_native_unit_tests():
+    """The C++ test executable (kernels against host references, no Python in between) passes."""
+    import subprocess
+    from llmq_b200.build import build_tests
+    exe = build_tests()
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ALL TESTS PASSED" in r.stdout, r.stdout + r.stderr
