@@ -84,6 +84,8 @@ def main():
     ap.add_argument("--lmhead-chunks", type=int, default=4)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (the result is then not the headline metric)")
     ap.add_argument("--collectives", default="auto")
+    ap.add_argument("--recompute", default="swiglu", choices=["none", "swiglu", "block"], help="headline config: swiglu")
+    ap.add_argument("--offload-master", action="store_true")
     ap.add_argument("--fuse-swiglu", type=int, default=None)
     ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--cuda-graphs", type=int, default=-1,
@@ -106,7 +108,8 @@ def main():
     cfg = create_config_from_name(args.model, "bf16")
     if args.layers:
         cfg = cfg.replace(num_hidden_layers=args.layers)
-    opts = LLamaOptions(recompute_swiglu=True, matmul_type=args.matmul_dtype, momentum_type="bf16", variance_type="bf16",
+    opts = LLamaOptions(recompute_swiglu=args.recompute == "swiglu", recompute_block=args.recompute == "block",
+                        offload_master=args.offload_master, matmul_type=args.matmul_dtype, momentum_type="bf16", variance_type="bf16",
                         lmhead_chunks=args.lmhead_chunks, collectives=args.collectives, use_cuda_graphs=(args.cuda_graphs == 1 or (args.cuda_graphs < 0 and args.gpus == 1)))
     if args.fuse_swiglu is not None:
         opts.fuse_swiglu = args.fuse_swiglu
@@ -180,20 +183,24 @@ def main():
     value = tokens / (ms_dev / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     if rank == 0:
+        # SOL % as the reference defines it (spec-sheet peaks: bf16 2200 / fp8 4500 TFLOP/s for B200)
+        from llmq_b200.utils.sol import estimate_speed_of_light
+        sol_ns = estimate_speed_of_light(cfg, T, torch.bfloat16, opts.matmul_dtype(), comm.world)
+        sol_pct = 100.0 * sol_ns / (1e9 / value) if sol_ns > 0 else None
         out = {
-            "metric": "train tokens/sec/box Qwen2.5-7B e4m3", "value": value, "unit": "tokens/s", "n_gpus": comm.world,
+            "metric": f"train tokens/sec/box {args.model} {args.matmul_dtype}", "value": value, "unit": "tokens/s", "n_gpus": comm.world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (value / (BASELINE_TOKS_PER_GPU * comm.world)) if BASELINE_TOKS_PER_GPU else None,
             "dtype": "bf16 model / e4m3 matmul", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model + ("" if not args.layers else f"[layers={args.layers}]"), "global_batch": B * comm.world * GA,
                        "seq_len": T, "per_gpu_batch": B, "grad_accum": GA,
-                       "parallelism": f"dp{comm.world}" + ("" if comm.world == 1 else f"-zero{zl}"), "recompute": "swiglu",
+                       "parallelism": f"dp{comm.world}" + ("" if comm.world == 1 else f"-zero{zl}"), "recompute": args.recompute,
                        "opt_moments": "bf16", "lmhead_chunks": args.lmhead_chunks,
                        "l2": "every step streams >60 GB of weights+activations (>> 126 MB L2), no flush needed"},
             "clocks": sampler.summary(),
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": 2 * B * T * 4 * GA,
                     "d2h_bytes_per_step": 32, "timing": "host wall clock around K steps incl. pinned H2D token copies and D2H loss/norm"},
-            "gpu_launches": launches, "loss": loss_host, "impl": "ours",
+            "gpu_launches": launches, "loss": loss_host, "sol_pct_of_spec_sheet_peak": sol_pct, "impl": "ours",
         }
         print(json.dumps(out))
     trainer.comm.shutdown()

@@ -46,6 +46,8 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar) {
     __syncwarp();
     if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
+// barriers 2-5: the four warps (one per warpgroup) that share 32 rows of the tile
+__device__ __forceinline__ void row_group_barrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory"); }
 __device__ __forceinline__ void compute_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kBwdComputeThreads) : "memory"); }
 
 // 2^x with the hardware approximation (-inf -> 0)
@@ -826,7 +828,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64
                         sMax[((t & 1) * kBwdWarpgroups + wg) * BQ + r] = mx;
                     }
                 }
-                compute_barrier();                              // every thread takes part, also after a failed wait
+                row_group_barrier(warp & 3);                              // every thread takes part, also after a failed wait
                 if (!ok) continue;
                 float m_tile = -INFINITY;
 #pragma unroll
@@ -877,7 +879,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64
             if (ok) ok = mbar_wait(p_free(t_last), (t_last >> 1) & 1, abort_flag);
             tc_fence_after_sync();
             sSum[wg * BQ + r] = l_part;
-            compute_barrier();
+            row_group_barrier(warp & 3);
             if (ok) {
                 float l = 0.f;
 #pragma unroll
@@ -902,7 +904,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64
                     if (wg == 0) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + row] = m_ref * p.scale + logf(l);
                 }
             }
-            compute_barrier();                                  // sSum is reused by the next head
+            row_group_barrier(warp & 3);                                  // sSum is reused by the next head
         }
         if (!ok && r == 0) atomicOr(p.status, kErrOther);
     }

@@ -195,6 +195,8 @@ class LlamaModel:
         if BT % chunks:
             raise ValueError("lmhead_chunks must divide batch * seq_len")
         t.logits = z(BT // chunks, V)
+        # second buffer: the LM-head gradients of a chunk run beside the next chunk's logits + classifier
+        t.logits2 = z(BT // chunks, V) if (dev.type == "cuda" and o.overlap_dw and chunks > 1) else None
         t.lnf_T = z(C, BT // chunks) if dev.type == "cuda" else None      # lnf chunk transposed, B operand of the LM-head dW GEMM
         t.att_scratch = torch.zeros(B * Hq * T, dtype=torch.float32, device=dev)
         t.norm_scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32, device=dev)
@@ -437,22 +439,37 @@ class LlamaModel:
         # lnf^T per chunk) are cheaper than letting the GEMM read them in place.
         use_t = write_grads and W.is_cuda and self.opts.lmhead_transposed_operands
         WT = self._head_transposed(W) if use_t else None
+        # The chain is logits GEMM -> classifier -> next chunk's logits GEMM; dW and dX of a chunk only need its
+        # classifier, so with a second logits buffer they run on the side stream under the next chunk's classifier.
+        side = self._dw_stream if (write_grads and t.logits2 is not None) else None
+        main = torch.cuda.current_stream(self.device) if side is not None else None
+        busy = [None, None]                                     # side-stream event of the last reader of each logits buffer
         for c in range(chunks):
             sl = slice(c * n, (c + 1) * n)
-            K.gemm(t.logits, self.lnf[sl], W)
-            K.fused_classifier(t.logits, losses[sl], lse[sl], tg[sl], dloss, z_reg=z_loss * dloss, write_dlogits=write_grads)
-            if write_grads:
+            logits = t.logits if (side is None or c % 2 == 0) else t.logits2
+            if side is not None and busy[c % 2] is not None:
+                main.wait_event(busy[c % 2])
+            K.gemm(logits, self.lnf[sl], W)
+            K.fused_classifier(logits, losses[sl], lse[sl], tg[sl], dloss, z_reg=z_loss * dloss, write_dlogits=write_grads)
+            if not write_grads:
+                continue
+
+            def grads_of_chunk(logits=logits, sl=sl, c=c):
                 if use_t:
                     K.transpose(t.lnf_T, self.lnf[sl])
-                    K.gemm(dW, t.logits, t.lnf_T, a_mn=True, accumulate=accumulate_dw or c > 0)
+                    K.gemm(dW, logits, t.lnf_T, a_mn=True, accumulate=accumulate_dw or c > 0)
+                    K.gemm(t.d_ln[sl], logits, WT)
                 else:
-                    K.gemm(dW, t.logits, self.lnf[sl], a_mn=True, b_mn=True, accumulate=accumulate_dw or c > 0)
-                if c == chunks - 1 and not cfg.tie_word_embeddings:
-                    self.grads.notify_non_block(head_name)
-                if use_t:
-                    K.gemm(t.d_ln[sl], t.logits, WT)
-                else:
-                    K.gemm(t.d_ln[sl], t.logits, W, b_mn=True)
+                    K.gemm(dW, logits, self.lnf[sl], a_mn=True, b_mn=True, accumulate=accumulate_dw or c > 0)
+                    K.gemm(t.d_ln[sl], logits, W, b_mn=True)
+
+            if side is None:
+                grads_of_chunk()
+            else:
+                busy[c % 2] = self._launch_dw(grads_of_chunk)
+        self._join_dw()
+        if write_grads and not cfg.tie_word_embeddings:
+            self.grads.notify_non_block(head_name)
         K.lse_stats(self.lse_stats, self.lse_tok.view(-1), accumulate=False)
 
     def _head_transposed(self, W: torch.Tensor) -> torch.Tensor:

@@ -66,10 +66,11 @@ def bench_gemm(a, tm):
     A = _rand((a.k, a.m) if a.a_mn else (a.m, a.k), dt)
     B = _rand((a.k, a.n) if a.b_mn else (a.n, a.k), dt)
     C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=DEV)
-    ms = tm.time(lambda: K.gemm(C, A, B, a_mn=a.a_mn, b_mn=a.b_mn, accumulate=a.accumulate))
+    bias = _rand((a.n,), torch.bfloat16) if a.bias else None
+    ms = tm.time(lambda: K.gemm(C, A, B, a_mn=a.a_mn, b_mn=a.b_mn, accumulate=a.accumulate, bias=bias))
     tf = 2.0 * a.m * a.n * a.k / ms / 1e9
     peak, _, src = _peaks()
-    print(json.dumps({"op": "gemm", "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype, "a_mn": a.a_mn, "b_mn": a.b_mn, "mode": a.mode,
+    print(json.dumps({"op": "gemm", "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype, "a_mn": a.a_mn, "b_mn": a.b_mn, "bias": a.bias, "mode": a.mode,
                       "ms": round(ms, 4), "tflops": round(tf, 1), f"frac_of_{src}_bf16_peak": round(tf / peak, 3)}))
 
 
@@ -155,6 +156,7 @@ def main():
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--accumulate", action="store_true")
+    ap.add_argument("--bias", action="store_true")
     ap.add_argument("--mode", type=int, default=0)
     ap.add_argument("--b", type=int, default=8)
     ap.add_argument("--t", type=int, default=2048)
