@@ -28,7 +28,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-BASELINE_TOKS_PER_GPU = None       # the reference publishes no B200 number (BASELINE.md section 1)
+BASELINE_TOKS_PER_GPU = None       # the reference publishes no B200 number
 
 
 class ClockSampler(threading.Thread):

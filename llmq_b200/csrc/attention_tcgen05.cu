@@ -99,6 +99,7 @@ struct AttnParams {
     bf16* dqkv;                  // backward: packed gradient
     const bf16* qkv;             // backward: packed inputs and the output gradient as plain pointers
     const bf16* d_out;
+    float* absmax;               // forward, optional: running abs-max of the output (for its fp8 quantisation)
     unsigned int* status;
 };
 
@@ -797,7 +798,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64
         uint32_t wq[16];
         load_q(kvh * G, wq);
         store_q(wq);
-        float m_ref = -INFINITY, l_part = 0.f;
+        float m_ref = -INFINITY, l_part = 0.f, omax = 0.f;
         for (int g = 0; g < G; ++g) {
             const int h = kvh * G + g;
             if (g + 1 < G) load_q(h + 1, wq);                   // prefetch: consumed when this head's walk is over
@@ -897,8 +898,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64
                         uint4 v;
                         __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
+                        for (int jj = 0; jj < 4; ++jj) {
                             vb[jj] = __floats2bfloat162_rn(__uint_as_float(ro[c + 2 * jj]) * inv, __uint_as_float(ro[c + 2 * jj + 1]) * inv);
+                            const float2 f = __bfloat1622float2(vb[jj]);
+                            omax = fmaxf(omax, fmaxf(fabsf(f.x), fabsf(f.y)));
+                        }
                         *reinterpret_cast<uint4*>(o + c) = v;
                     }
                     if (wg == 0) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.T + row] = m_ref * p.scale + logf(l);
@@ -907,6 +911,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_kv64,    // qkv, box 64
             row_group_barrier(warp & 3);                                  // sSum is reused by the next head
         }
         if (!ok && r == 0) atomicOr(p.status, kErrOther);
+        if (p.absmax) {
+            omax = warp_reduce_max(omax);
+            if ((tid & 31) == 0 && omax > 0.f) atomic_max_float(p.absmax, omax);
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -929,7 +937,7 @@ int set_smem(K kernel, int bytes) {
 }
 
 template <int HS>
-int fwd_impl(void* out, float* lse, const void* qkv, int B, int T, int Hq, int Hkv, unsigned int* status, cudaStream_t s) {
+int fwd_impl(void* out, float* lse, const void* qkv, int B, int T, int Hq, int Hkv, float* absmax, unsigned int* status, cudaStream_t s) {
     const int H = Hq + 2 * Hkv;
     CUtensorMap tkv;
     int rc = encode_btw(&tkv, qkv, B, T, static_cast<long long>(H) * HS, 64);
@@ -939,7 +947,7 @@ int fwd_impl(void* out, float* lse, const void* qkv, int B, int T, int Hq, int H
     if (rc) return rc;
     AttnParams p{};
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.scale = 1.f / sqrtf(static_cast<float>(HS));
-    p.out = static_cast<bf16*>(out); p.lse = lse; p.status = status; p.qkv = static_cast<const bf16*>(qkv);
+    p.out = static_cast<bf16*>(out); p.lse = lse; p.status = status; p.qkv = static_cast<const bf16*>(qkv); p.absmax = absmax;
     dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
     attn_fwd_kernel<HS><<<grid, kBwdThreads, smem, s>>>(tkv, p);
     return LLMQ_LAUNCH_CHECK();
@@ -989,12 +997,13 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
 }  // namespace
 
 // qkv (B,T,Hq+2Hkv,HS) bf16 -> out (B,T,Hq,HS) bf16, lse (B,Hq,T) fp32.  HS in {64, 128}.
+// absmax (optional): atomic maximum of |out|, for the fp8 quantisation of the output.
 extern "C" int llmq_attention_forward(void* out, float* lse, const void* qkv, int B, int T, int Hq, int Hkv, int HS,
-                                      unsigned int* status, cudaStream_t s) {
+                                      float* absmax, unsigned int* status, cudaStream_t s) {
     if (B <= 0 || T <= 0) return 0;
     if (Hq % Hkv) return -1;
-    if (HS == 64) return fwd_impl<64>(out, lse, qkv, B, T, Hq, Hkv, status, s);
-    if (HS == 128) return fwd_impl<128>(out, lse, qkv, B, T, Hq, Hkv, status, s);
+    if (HS == 64) return fwd_impl<64>(out, lse, qkv, B, T, Hq, Hkv, absmax, status, s);
+    if (HS == 128) return fwd_impl<128>(out, lse, qkv, B, T, Hq, Hkv, absmax, status, s);
     return -2;
 }
 

@@ -374,9 +374,7 @@ class LlamaModel:
         self._fwd_mm(qkv2d, a.ln1[l], a.ln1_q[l] if self.quant else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b, ready=p.ready["qkv_w"])
         K.rope(a.qkv[l], a.qkv[l], self.freqs, Hq, Hkv)
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
-        K.attention_forward(att4, a.lse[l], a.qkv[l], Hq, Hkv)
-        if self.quant:
-            K.abs_max(self._slot(l, S_ATT)[0], a.att[l])
+        K.attention_forward(att4, a.lse[l], a.qkv[l], Hq, Hkv, absmax=self._slot(l, S_ATT)[0] if self.quant else None)
         self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
         K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x.current(l), p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
                           absmax=self._slot(l, S_LN2)[0])

@@ -143,9 +143,41 @@ def bench_adamw(a, tm):
     print(json.dumps({"op": "adamw_bf16", "n": n, "ms": round(ms, 4), "gbs": round(gbs, 1), f"frac_of_{src}_hbm": round(gbs / bw, 3)}))
 
 
+def bench_p2p(a, tm):
+    """The peer-memory collective kernels with every "rank" living on this one GPU: the peer table holds local buffers,
+    so the kernels run exactly as on several GPUs but all traffic stays in local HBM (what the numbers show is the
+    kernels' own efficiency, not NVLink)."""
+    import ctypes
+    _, bw, src = _peaks()
+    w = a.world
+    rows, cols = a.rows, a.c
+    n_shard = rows * cols // w
+    shard = _rand((n_shard,), torch.bfloat16)
+    gathers = [torch.empty(rows * cols, dtype=torch.float8_e4m3fn, device=DEV) for _ in range(w)]
+    peers = (ctypes.c_void_p * 8)(*([g.data_ptr() for g in gathers] + [0] * (8 - w)))
+    am, sc = torch.full((1,), 4.0, device=DEV), torch.zeros(1, device=DEV)
+    sms = K.num_sms(torch.device(DEV, torch.cuda.current_device()))
+    k = L.kernels()
+    res = {}
+    ms = tm.time(lambda: L.check(k.llmq_p2p_quant_allgather(peers, ctypes.c_longlong(0), L.ptr(shard), ctypes.c_longlong(n_shard), 0, w, L.ptr(am),
+                                                             L.ptr(sc), 1, sms, L.stream_ptr()), "p2p_quant_allgather"))
+    res["quant_allgather_e4m3"] = (ms, n_shard * (2 + w))              # read bf16 shard, write one e4m3 copy per rank
+    grads = [_rand((rows * cols,), torch.bfloat16) for _ in range(w)]
+    gpeers = (ctypes.c_void_p * 8)(*([g.data_ptr() for g in grads] + [0] * (8 - w)))
+    dst = torch.zeros(n_shard, dtype=torch.bfloat16, device=DEV)
+    parts = torch.zeros(K.NORM_PARTIALS, device=DEV)
+    ms = tm.time(lambda: L.check(k.llmq_p2p_reduce_scatter(gpeers, None, ctypes.c_longlong(0), ctypes.c_longlong(n_shard), 0, w, L.ptr(dst), 1,
+                                                            ctypes.c_float(1.0 / w), L.ptr(parts), K.NORM_PARTIALS, ctypes.c_uint(7), sms,
+                                                            L.stream_ptr()), "p2p_reduce_scatter"))
+    res["reduce_scatter_sr_norm"] = (ms, n_shard * 2 * (w + 2))          # read one slice per rank + old shard, write shard
+    out = {kk: {"ms": round(v[0], 4), "gbs": round(v[1] / v[0] / 1e6, 1), f"frac_of_{src}_hbm": round(v[1] / v[0] / 1e6 / bw, 3)} for kk, v in res.items()}
+    print(json.dumps({"op": "p2p_single_gpu_emulation", "world": w, "elements": rows * cols, **out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "adamw"])
+    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "adamw", "p2p"])
+    ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
@@ -169,7 +201,7 @@ def main():
     ap.add_argument("--numel", type=int, default=1 << 28)
     a = ap.parse_args()
     tm = Timer(a.iters, a.warmup, not a.no_flush)
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw}[a.op](a, tm)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw, "p2p": bench_p2p}[a.op](a, tm)
 
 
 if __name__ == "__main__":

@@ -610,16 +610,20 @@ def bias_backward(dbias: torch.Tensor, dout: torch.Tensor, scratch: Optional[tor
 
 # =====================================================================================================
 # Attention
-def attention_forward(out: torch.Tensor, lse: torch.Tensor, qkv: torch.Tensor, Hq: int, Hkv: int) -> None:
-    """Causal GQA attention on packed qkv (B,T,Hq+2Hkv,HS): out (B,T,Hq,HS), lse (B,Hq,T) natural log."""
+def attention_forward(out: torch.Tensor, lse: torch.Tensor, qkv: torch.Tensor, Hq: int, Hkv: int,
+                      absmax: Optional[torch.Tensor] = None) -> None:
+    """Causal GQA attention on packed qkv (B,T,Hq+2Hkv,HS): out (B,T,Hq,HS), lse (B,Hq,T) natural log.
+    ``absmax`` (optional) is raised to max |out|."""
     B, T, H, HS = qkv.shape
     if qkv.is_cuda:
-        L.check(L.kernels().llmq_attention_forward(L.ptr(out), L.ptr(lse), L.ptr(qkv), B, T, Hq, Hkv, HS,
+        L.check(L.kernels().llmq_attention_forward(L.ptr(out), L.ptr(lse), L.ptr(qkv), B, T, Hq, Hkv, HS, L.ptr(absmax),
                                                    L.ptr(status_word(qkv.device)), L.stream_ptr()), "attention_forward")
         return
     o, l = _attention_ref(qkv.float(), Hq, Hkv)
     out.copy_(o.to(out.dtype))
     lse.copy_(l)
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, out.float().abs().max().reshape_as(absmax)))
 
 
 def _attention_ref(qkv: torch.Tensor, Hq: int, Hkv: int):

@@ -299,7 +299,9 @@ def test_attention(HS, Hq, Hkv, T):
     for dev in ("cpu", DEV):
         out = torch.zeros(B, T, Hq, HS, dtype=BF, device=dev)
         lse = torch.zeros(B, Hq, T, device=dev)
-        K.attention_forward(out, lse, qkv.to(dev), Hq, Hkv)
+        am = torch.zeros(1, device=dev)
+        K.attention_forward(out, lse, qkv.to(dev), Hq, Hkv, absmax=am)
+        assert abs(am.item() - out.float().abs().max().item()) < 1e-6
         dqkv = torch.zeros_like(qkv, device=dev)
         scratch = torch.zeros(B * Hq * T, device=dev)
         K.attention_backward(dqkv, scratch, dout.to(dev), out, lse, qkv.to(dev), Hq, Hkv)
