@@ -50,6 +50,11 @@ struct GemmParams {
     int ep_mode;
     void* ep_ptr;
     int ep_D;
+    // Optional split-K (one-CTA kernel only): the K loop of every tile is cut into k_splits parts handled by different
+    // CTAs; each writes its raw fp32 accumulator to partial[split][M][N] and a second kernel sums the parts and applies
+    // the normal epilogue.  For outputs with fewer tiles than SMs and a long K (weight gradients of small models).
+    int k_splits;
+    float* partial;
 };
 
 // Each lane of the calling warp owns one accumulator row (TMEM lane); `t_row` addresses column 0 of that row
@@ -237,6 +242,31 @@ __device__ __forceinline__ void epilogue_rows_swiglu_bwd(const GemmParams& p, ui
             }
             store32_bf16(urow + f0 + c, u);
             store32_bf16(urow + p.ep_D + f0 + c, g);
+        }
+    }
+}
+
+// Raw fp32 accumulator rows -> partial[split] (split-K); same lane / row convention as epilogue_rows.
+__device__ __forceinline__ void epilogue_rows_partial(const GemmParams& p, uint32_t t_row, int row, int col_base, int ncols, int split) {
+    using namespace sm100;
+    const bool row_ok = row < p.M;
+    float* prow = p.partial + (static_cast<long long>(split) * p.M + row) * p.N;
+#pragma unroll 1
+    for (int c = 0; c < ncols; c += 32) {
+        const int col0 = col_base + c;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c, r);
+        tmem_ld_wait();
+        if (row_ok) {
+            if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(prow + col0) & 15u) == 0)) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    *reinterpret_cast<float4*>(prow + col0 + g * 4) = make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                                                                                  __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+            } else {
+                for (int j = 0; j < 32; ++j) if (col0 + j < p.N) prow[col0 + j] = __uint_as_float(r[j]);
+            }
         }
     }
 }

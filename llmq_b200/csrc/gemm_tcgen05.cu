@@ -76,7 +76,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int k_iters = (p.K + bk - 1) / bk;
     const int tiles_m = (p.M + BM - 1) / BM;
     const int tiles_n = (p.N + BN - 1) / BN;
-    const int num_tiles = tiles_m * tiles_n;
+    const int splits = p.k_splits > 1 ? p.k_splits : 1;
+    const int k_per_split = (k_iters + splits - 1) / splits;
+    const int num_tiles = tiles_m * tiles_n * splits;           // work items: (tile, K split)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -102,8 +104,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int mn_chunk = ROW_BYTES / p.elem_bytes;     // M/N elements per 128-byte row (MN-major)
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
-                for (int k = 0; k < k_iters; ++k) {
+                int tm, tn; tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
+                const int k_begin = (t % splits) * k_per_split, k_end = min(k_iters, k_begin + k_per_split);
+                for (int k = k_begin; k < k_end; ++k) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrEmptyWait); ok = false; break; }
                     uint32_t sa = smem_base + stage * STAGE_BYTES;
                     uint32_t sb = sa + A_STAGE_BYTES;
@@ -150,12 +153,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { atomicOr(p.status, kErrTmemEmpty); ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int k = 0; k < k_iters; ++k) {
+                const int k_begin = (t % splits) * k_per_split, k_end = min(k_iters, k_begin + k_per_split);
+                for (int k = k_begin; k < k_end; ++k) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) { atomicOr(p.status, kErrFullWait); ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t alo = a_lo0 + stage * (STAGE_BYTES >> 4);
                     const uint32_t blo = b_lo0 + stage * (STAGE_BYTES >> 4);
-                    mma_issue<F8, false>(d_tmem, alo, a_hi, blo, b_hi, idesc, k > 0 ? 1u : 0u);
+                    mma_issue<F8, false>(d_tmem, alo, a_hi, blo, b_hi, idesc, k > k_begin ? 1u : 0u);
                     mma_issue<F8, false>(d_tmem, alo + a_inc, a_hi, blo + b_inc, b_hi, idesc, 1u);
                     mma_issue<F8, false>(d_tmem, alo + 2 * a_inc, a_hi, blo + 2 * b_inc, b_hi, idesc, 1u);
                     mma_issue<F8, false>(d_tmem, alo + 3 * a_inc, a_hi, blo + 3 * b_inc, b_hi, idesc, 1u);
@@ -177,10 +181,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-            int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            int tm, tn; tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { if (lane == 0) atomicOr(p.status, kErrTmemFull); ok = false; break; }
             tc_fence_after_sync();
-            epilogue_rows(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, tm * BM + q * 32 + lane, tn * BN, BN, alpha, tmax);
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+            if (splits > 1) epilogue_rows_partial(p, t_row, tm * BM + q * 32 + lane, tn * BN, BN, t % splits);
+            else            epilogue_rows(p, t_row, tm * BM + q * 32 + lane, tn * BN, BN, alpha, tmax);
             tc_fence_before_sync();
             mbar_arrive(tempty_bar(acc));                  // 128 arrivals release the accumulator
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -195,6 +201,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// Sum of the split-K parts + the normal epilogue (alpha, bias, accumulate, bf16 / fp32 store, abs-max).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p, float alpha_host) {
+    __shared__ float scratch[32];
+    float alpha = alpha_host;
+    if (p.scale_a) alpha *= *p.scale_a;
+    if (p.scale_b) alpha *= *p.scale_b;
+    const long long total = static_cast<long long>(p.M) * p.N;
+    float tmax = 0.f;
+    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
+        const int col = static_cast<int>(i % p.N);
+        const long long row = i / p.N;
+        float v = 0.f;
+        for (int s = 0; s < p.k_splits; ++s) v += p.partial[static_cast<long long>(s) * total + i];
+        v *= alpha;
+        if (p.bias) v += p.bias_dtype == 0 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : static_cast<const float*>(p.bias)[col];
+        if (p.c_dtype == 0) {
+            __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+            if (p.accumulate) v += __bfloat162float(*c);
+            *c = __float2bfloat16_rn(v);
+        } else {
+            float* c = static_cast<float*>(p.C) + row * p.ldc + col;
+            if (p.accumulate) v += *c;
+            *c = v;
+        }
+        tmax = fmaxf(tmax, fabsf(v));
+    }
+    if (p.absmax_out) block_absmax_commit(p.absmax_out, tmax, scratch);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -238,6 +273,11 @@ int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
 // Tile-shape selection: 0 = automatic, 1 = force the one-CTA kernel, 2 = force the CTA-pair kernel.
 static int g_gemm_mode = 0;
 extern "C" void llmq_gemm_set_mode(int mode) { g_gemm_mode = mode; }
+// Split-K workspace of the calling thread's next GEMMs: `floats` fp32 elements at `ws` (0 switches split-K off).
+// A GEMM uses it when its output has fewer than num_sms / 2 tiles of the one-CTA kernel and K is long enough.
+static thread_local float* g_splitk_ws = nullptr;
+static thread_local long long g_splitk_floats = 0;
+extern "C" void llmq_gemm_set_splitk_workspace(float* ws, long long floats) { g_splitk_ws = ws; g_splitk_floats = floats; }
 
 extern "C" int llmq_gemm_ready(const void*, const void*, void*, const void*, int, int, int, int, int, int, int, long long, long long, long long, int, int, int,
                                const float*, const float*, float, float*, unsigned int*, int, const unsigned int*, unsigned int, int, double, cudaStream_t);
@@ -365,8 +405,25 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
         attr_set[dev & 63] = true;
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    int grid = tiles < num_sms ? tiles : num_sms;
+    const int k_iters = (K + bk - 1) / bk;
+    int splits = 1;
+    if (g_splitk_ws && tiles * 2 <= num_sms && k_iters >= 16) {
+        splits = num_sms / tiles;
+        if (splits > 8) splits = 8;
+        if (splits > k_iters / 8) splits = k_iters / 8;
+        while (splits > 1 && static_cast<long long>(splits) * M * N > g_splitk_floats) --splits;
+        // every split must get at least one K step
+        while (splits > 1 && (splits - 1) * ((k_iters + splits - 1) / splits) >= k_iters) --splits;
+    }
+    if (splits > 1) { p.k_splits = splits; p.partial = g_splitk_ws; }
+    const int items = tiles * splits;
+    int grid = items < num_sms ? items : num_sms;
     if (eb == 1) gemm_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
     else         gemm_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (splits > 1) {
+        long long blocks = (static_cast<long long>(M) * N + 255) / 256;
+        if (blocks > 4LL * num_sms) blocks = 4LL * num_sms;
+        splitk_reduce_kernel<<<static_cast<unsigned int>(blocks), 256, 0, stream>>>(p, p.alpha);
+    }
     return static_cast<int>(cudaGetLastError());
 }

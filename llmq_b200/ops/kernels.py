@@ -11,6 +11,7 @@ The set of operations mirrors the kernel API of the reference (src/kernels/kerne
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Optional
 
@@ -35,9 +36,25 @@ def _dev_state(device):
             st = {
                 "sms": props.multi_processor_count,
                 "status": torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}"),
+                # fp32 scratch of the split-K GEMM path (small outputs with a long K: weight gradients of small models)
+                "splitk_ws": torch.empty(SPLITK_WS_FLOATS, dtype=torch.float32, device=f"cuda:{idx}"),
+                "splitk_tid": None,
             }
         _state[idx] = st
     return st
+
+
+SPLITK_WS_FLOATS = 16 << 20
+
+
+def _bind_splitk(st) -> None:
+    """The workspace is registered per calling thread (rank threads each drive their own device)."""
+    import threading
+    tid = threading.get_ident()
+    if st["splitk_tid"] != tid:
+        ws = st["splitk_ws"] if os.environ.get("LLMQ_GEMM_SPLITK", "1") != "0" else None
+        L.kernels().llmq_gemm_set_splitk_workspace(L.ptr(ws), ctypes.c_longlong(0 if ws is None else ws.numel()))
+        st["splitk_tid"] = tid
 
 
 def num_sms(device) -> int:
@@ -90,6 +107,7 @@ def gemm(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = Fa
     assert (b.shape == (K, N)) if b_mn else (b.shape == (N, K)), (b.shape, (N, K), b_mn)
     if out.is_cuda:
         st = _dev_state(out.device)
+        _bind_splitk(st)
         assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
         rflags, rgen, rrows, rlimit = ready if ready is not None else (0, 0, 0, 0.0)
         rc = L.kernels().llmq_gemm_ready(

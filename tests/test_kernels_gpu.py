@@ -63,6 +63,29 @@ def test_gemm_epilogue():
     close(outf, A.float() @ B.float().t(), rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("dt", ["bf16", "fp8"])
+@pytest.mark.parametrize("M,N,Kd,a_mn,b_mn", [(256, 256, 8192, 0, 0), (896, 1152, 4096, 1, 1), (200, 304, 2560, 0, 1)])
+def test_gemm_split_k(M, N, Kd, a_mn, b_mn, dt):
+    """Few output tiles and a long K: the K loop is split over several CTAs and summed by a second kernel."""
+    torch.manual_seed(21)
+    A, B = torch.randn(M, Kd) * 0.5, torch.randn(N, Kd) * 0.5
+    A, B = (A.to(BF), B.to(BF)) if dt == "bf16" else (A.to(F8), B.to(F8))
+    As = A.float().t().contiguous().to(A.dtype) if a_mn else A
+    Bs = B.float().t().contiguous().to(B.dtype) if b_mn else B
+    bias, C0 = torch.randn(N).to(BF), torch.randn(M, N).to(BF)
+    sa = torch.tensor([0.5])
+    ref = (A.float() @ B.float().t()) * 0.5 + bias.float() + C0.float()
+    out = C0.to(DEV)
+    am = torch.zeros(1, device=DEV)
+    K.gemm(out, As.to(DEV), Bs.to(DEV), a_mn=bool(a_mn), b_mn=bool(b_mn), bias=bias.to(DEV), accumulate=True, scale_a=sa.to(DEV), absmax=am)
+    K.check_status(torch.device(DEV))
+    close(out, ref, rtol=1e-2, atol=0.3)
+    assert abs(am.item() - out.float().abs().max().item()) < 8e-3 * am.item()          # abs-max is taken before the bf16 rounding
+    outf = torch.zeros(M, N, device=DEV)
+    K.gemm(outf, As.to(DEV), Bs.to(DEV), a_mn=bool(a_mn), b_mn=bool(b_mn))
+    close(outf, A.float() @ B.float().t(), rtol=1e-3, atol=2e-2)
+
+
 @pytest.mark.parametrize("C", [64, 896, 3584])
 @pytest.mark.parametrize("fused", [False, True])
 def test_rmsnorm_forward(C, fused):
