@@ -1,0 +1,56 @@
+"""The pyllmq-compatible import package and the torch custom-op kernel API, on CPU tensors (PyTorch reference paths)."""
+import numpy as np
+import torch
+
+import llmq_b200.kernels_api as ops
+import pyllmq
+
+
+def test_pyllmq_surface():
+    cfg = pyllmq.Config.from_name("Qwen2.5-0.5B")
+    assert cfg.hidden_size == 896 and cfg.num_hidden_layers == 24 and cfg.vocab_size == 151936
+    for name in ("LLMQTrainer", "LLamaOptions", "DataLoader", "TrainingRunLogger", "TrainingConfig", "CosineLRSchedule", "get_num_gpus"):
+        assert hasattr(pyllmq, name) or hasattr(pyllmq.training, name), name
+    tc = pyllmq.training.TrainingConfig()
+    assert tc.matmul_dtype in (None, "", "bf16", "e4m3") or isinstance(tc.matmul_dtype, str)
+
+
+def test_tiny_trainer_through_pyllmq():
+    cfg = pyllmq.Config(hidden_size=64, intermediate_size=128, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2,
+                        vocab_size=256, max_position_embeddings=128, tie_word_embeddings=True)
+    tr = pyllmq.LLMQTrainer(ngpu=1, config=cfg, options=pyllmq.LLamaOptions(), batch_size=2, seq_len=32, grad_accum=1, device="cpu")
+    tr.init_weights()
+    rng = np.random.default_rng(0)
+    tok = rng.integers(0, 256, size=(2, 33), dtype=np.int32)
+    first = None
+    for step in range(3):
+        tr.step(np.ascontiguousarray(tok[:, :-1]), np.ascontiguousarray(tok[:, 1:]))
+        r = tr.update(1e-2, 0.9, 0.95, step + 1, 0.0, 1.0)
+        first = first if first is not None else r["loss"]
+    assert r["loss"] < first and np.isfinite(r["norm"])
+
+
+def test_custom_ops_on_cpu_tensors():
+    torch.manual_seed(0)
+    x, w = torch.randn(6, 64).bfloat16(), (1 + 0.1 * torch.randn(64)).bfloat16()
+    out, rms = torch.zeros_like(x), torch.zeros(6)
+    torch.ops.llmq_b200.rmsnorm_forward(out, rms, x, w, None, 1e-6)
+    ref = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)).bfloat16().float() * w.float()
+    assert torch.allclose(out.float(), ref, atol=2e-2)
+    a, b = torch.randn(8, 32).bfloat16(), torch.randn(16, 32).bfloat16()
+    c = torch.zeros(8, 16, dtype=torch.bfloat16)
+    ops.matmul(c, a, b, None, None, None, None, "TN", False)
+    assert torch.allclose(c.float(), a.float() @ b.float().t(), atol=0.25, rtol=2e-2)
+    up = torch.randn(4, 2 * 16).bfloat16()
+    sw, am = torch.zeros(4, 16, dtype=torch.bfloat16), torch.zeros(1)
+    torch.ops.llmq_b200.swiglu_forward(sw, up, am)
+    u, g = up[:, :16].float(), up[:, 16:].float()
+    assert torch.allclose(sw.float(), u * g * torch.sigmoid(g), atol=3e-2) and am.item() > 0
+    q, scale = torch.zeros(6, 64, dtype=torch.float8_e4m3fn), torch.zeros(1)
+    amx = x.float().abs().max().reshape(1)
+    torch.ops.llmq_b200.quantize_with_abs_max(q, scale, x, amx)
+    assert torch.allclose(q.float() * scale, x.float(), atol=0.07 * amx.item())
+    p_, g_, m_, v_ = torch.randn(64).bfloat16(), torch.randn(64).bfloat16(), torch.zeros(64), torch.zeros(64)
+    before = p_.clone()
+    ops.adamw_update(p_, g_, m_, v_, 1e-2, 0.9, 0.95, 1, 1e-8, 0.0)
+    assert not torch.equal(before, p_) and m_.abs().sum() > 0
