@@ -280,7 +280,7 @@ class LlamaModel:
             elif dinp is not None:
                 K.gemm(dinp, dout, W, b_mn=True, ready=ready)
             if dw_rs is not None:
-                dw_rs(dout, inp)
+                self._launch_dw(lambda: dw_rs(dout, inp))
             else:
                 self._launch_dw(lambda: K.gemm(dW, dout, inp, a_mn=True, b_mn=True, accumulate=accumulate))
             if dbias is not None:
@@ -293,7 +293,7 @@ class LlamaModel:
         elif dinp is not None:
             K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
         if dw_rs is not None:
-            dw_rs(dout_q, inp_q, sc, inp_scale)
+            self._launch_dw(lambda: dw_rs(dout_q, inp_q, sc, inp_scale))
         else:
             self._launch_dw(lambda: K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate))
         if dbias is not None:

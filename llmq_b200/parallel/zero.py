@@ -380,8 +380,8 @@ class GradientManager:
         # reduce-scatter inside (main stream), so the two streams never touch the same word
         self.norm_partials = torch.zeros(2 * K.NORM_PARTIALS, dtype=torch.float32, device=device) if self.fused is not None else None
         # Weight-gradient GEMMs with the reduce-scatter inside the kernel.  Off unless LLMQ_GEMM_RS=1: the kernel's tail
-        # has to wait for the peers on the main stream, which measured 563 ms against 536 ms per step (Qwen2.5-7B, 2 GPUs)
-        # for the plain GEMM followed by the pull reduce-scatter kernel on the side stream.
+        # has to wait for the peers while it holds every SM, which measured 521 ms against 497 ms per step (Qwen2.5-7B,
+        # 2 GPUs) for the plain GEMM followed by the pull reduce-scatter kernel on the collectives stream.
         self.gemm_rs = self.fused is not None and os.environ.get("LLMQ_GEMM_RS", "0") == "1"
         self._rs_names: set = set()
         self._fdone: Dict[int, tuple] = {}           # channel -> (generation, event) of the last reduction reading a buffer
