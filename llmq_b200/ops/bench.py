@@ -74,6 +74,27 @@ def bench_gemm(a, tm):
                       "ms": round(ms, 4), "tflops": round(tf, 1), f"frac_of_{src}_bf16_peak": round(tf / peak, 3)}))
 
 
+def bench_gemm_mx(a, tm):
+    """Block-scaled e4m3 GEMM and its two quantisers (along rows / along columns with transpose)."""
+    x = _rand((a.m, a.k), torch.bfloat16)
+    w = _rand((a.n, a.k), torch.bfloat16)
+    aq, asf = K.quantize_mx(x, operand="a")
+    bq, bsf = K.quantize_mx(w, operand="b")
+    C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=DEV)
+    ms = tm.time(lambda: K.gemm_mx(C, aq, asf, bq, bsf, accumulate=a.accumulate))
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    peak, bw, src = _peaks()
+    out = {"op": "gemm_mx", "m": a.m, "n": a.n, "k": a.k, "ms": round(ms, 4), "tflops": round(tf, 1), f"frac_of_{src}_bf16_peak": round(tf / peak, 3)}
+    nbytes = a.m * a.k * 3 + a.m * a.k // 32
+    ms_q = tm.time(lambda: K.quantize_mx(x, operand="a", q_out=aq, sf_out=asf))
+    out["quantize_rows_ms"] = round(ms_q, 4); out[f"quantize_rows_frac_of_{src}_bw"] = round(nbytes / ms_q / 1e6 / bw, 3)
+    if a.m % 128 == 0:
+        tq, tsf = K.quantize_mx(x, transpose=True, operand="b")
+        ms_t = tm.time(lambda: K.quantize_mx(x, transpose=True, operand="b", q_out=tq, sf_out=tsf))
+        out["quantize_cols_ms"] = round(ms_t, 4); out[f"quantize_cols_frac_of_{src}_bw"] = round(nbytes / ms_t / 1e6 / bw, 3)
+    print(json.dumps(out))
+
+
 def bench_attention(a, tm):
     qkv = _rand((a.b, a.t, a.hq + 2 * a.hkv, a.hs), torch.bfloat16)
     out = torch.empty(a.b, a.t, a.hq, a.hs, dtype=torch.bfloat16, device=DEV)
@@ -176,7 +197,7 @@ def bench_p2p(a, tm):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "adamw", "p2p"])
+    ap.add_argument("op", choices=["gemm", "gemm_mx", "attention", "elementwise", "adamw", "p2p"])
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -201,7 +222,7 @@ def main():
     ap.add_argument("--numel", type=int, default=1 << 28)
     a = ap.parse_args()
     tm = Timer(a.iters, a.warmup, not a.no_flush)
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw, "p2p": bench_p2p}[a.op](a, tm)
+    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw, "p2p": bench_p2p}[a.op](a, tm)
 
 
 if __name__ == "__main__":

@@ -165,6 +165,88 @@ def gemm_swiglu_supported(M: int, D: int, t: torch.Tensor) -> bool:
 
 
 # =====================================================================================================
+# Block-scaled (MX) e4m3: one UE8M0 scale per 32 elements of the contraction axis (csrc/quant_mx.cu, csrc/gemm_mx_tcgen05.cu)
+MX_TILE_A, MX_TILE_B = 128, 224        # rows per scale-factor tile of the GEMM's A / B operand
+
+
+def mx_sf_offsets(rows: int, K: int, tile_rows: int) -> torch.Tensor:
+    """Byte offset of the scale of (row, 32-element block) in the tiled scale-factor buffer, as an int64 [rows, K/32] tensor."""
+    chunks = (tile_rows + 127) // 128
+    n_tiles = (rows + tile_rows - 1) // tile_rows
+    r = torch.arange(rows).unsqueeze(1)
+    kb = torch.arange(K // 32).unsqueeze(0)
+    tile, rt = r // tile_rows, r % tile_rows
+    rr = rt % 128
+    return (((kb // 4) * n_tiles + tile) * chunks + rt // 128) * 512 + (rr % 32) * 16 + (rr // 32) * 4 + kb % 4
+
+
+def mx_sf_bytes(rows: int, K: int, tile_rows: int) -> int:
+    return (K // 128) * ((rows + tile_rows - 1) // tile_rows) * ((tile_rows + 127) // 128) * 512
+
+
+def quantize_mx(x: torch.Tensor, *, transpose: bool = False, operand: str = "a", q_out: Optional[torch.Tensor] = None,
+                sf_out: Optional[torch.Tensor] = None):
+    """bf16 ``x[R, C]`` -> (e4m3 values, uint8 scale buffer) for :func:`gemm_mx`.  ``transpose`` quantises along the rows and
+    returns the transposed matrix ``[C, R]`` (the operand of a GEMM that contracts over R); ``operand`` ("a" / "b") picks the
+    scale-factor tiling of the GEMM side the result feeds.  The contraction length must be a multiple of 128."""
+    R, C = x.shape
+    rows, K = (C, R) if transpose else (R, C)
+    tile = MX_TILE_A if operand == "a" else MX_TILE_B
+    assert K % 128 == 0, "MX operands need a contraction length that is a multiple of 128"
+    if q_out is None:
+        q_out = torch.empty((rows, K), dtype=F8, device=x.device)
+    if sf_out is None:
+        sf_out = torch.empty(mx_sf_bytes(rows, K, tile), dtype=torch.uint8, device=x.device)
+    assert q_out.shape == (rows, K) and q_out.is_contiguous() and sf_out.numel() >= mx_sf_bytes(rows, K, tile)
+    if x.is_cuda:
+        assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+        rc = L.kernels().llmq_quantize_mx(L.ptr(q_out), L.ptr(sf_out), L.ptr(x), _ll(R), _ll(C), _ll(x.stride(0)), int(transpose), tile,
+                                          L.stream_ptr())
+        L.check(rc, "quantize_mx")
+        return q_out, sf_out
+    xs = (x.t() if transpose else x).float().reshape(rows, K // 32, 32)
+    amax = xs.abs().amax(-1)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax.double() / 448.0)).clamp(-127, 126), torch.full_like(amax, -127.0, dtype=torch.float64))
+    q_out.copy_((xs * torch.exp2(-e).float().unsqueeze(-1)).clamp(-448, 448).reshape(rows, K).to(F8))
+    sf_out.zero_()
+    sf_out[mx_sf_offsets(rows, K, tile).reshape(-1)] = (e + 127).to(torch.uint8).reshape(-1)
+    return q_out, sf_out
+
+
+def dequantize_mx(q: torch.Tensor, sf: torch.Tensor, operand: str = "a") -> torch.Tensor:
+    """fp32 values of a block-scaled operand (reference / debugging)."""
+    rows, K = q.shape
+    off = mx_sf_offsets(rows, K, MX_TILE_A if operand == "a" else MX_TILE_B).to(sf.device)
+    e = sf[off.reshape(-1)].reshape(rows, K // 32).float() - 127.0
+    return (q.float().reshape(rows, K // 32, 32) * torch.exp2(e).unsqueeze(-1)).reshape(rows, K)
+
+
+def gemm_mx(out: torch.Tensor, a: torch.Tensor, a_sf: torch.Tensor, b: torch.Tensor, b_sf: torch.Tensor, *,
+            bias: Optional[torch.Tensor] = None, accumulate: bool = False, alpha: float = 1.0,
+            absmax: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] (+)= alpha * dq(a)[M, K] @ dq(b)[N, K]^T + bias with block-scaled e4m3 operands from :func:`quantize_mx`."""
+    M, N = out.shape
+    K = a.shape[1]
+    assert a.shape == (M, K) and b.shape == (N, K) and K % 128 == 0
+    if out.is_cuda:
+        st = _dev_state(out.device)
+        rc = L.kernels().llmq_gemm_mx(L.ptr(a), L.ptr(b), L.ptr(a_sf), L.ptr(b_sf), L.ptr(out), L.ptr(bias), M, N, K, _ll(a.stride(0)),
+                                      _ll(b.stride(0)), _ll(out.stride(0)), 0 if out.dtype == torch.bfloat16 else 1,
+                                      0 if (bias is None or bias.dtype == torch.bfloat16) else 1, int(accumulate), _f(alpha), L.ptr(absmax),
+                                      L.ptr(st["status"]), st["sms"], L.stream_ptr())
+        L.check(rc, "gemm_mx")
+        return
+    r = alpha * (dequantize_mx(a, a_sf, "a") @ dequantize_mx(b, b_sf, "b").t())
+    if bias is not None:
+        r = r + bias.float()
+    if accumulate:
+        r = r + out.float()
+    out.copy_(r.to(out.dtype))
+    if absmax is not None:
+        absmax.copy_(torch.maximum(absmax, out.float().abs().max().reshape_as(absmax)))
+
+
+# =====================================================================================================
 # RMSNorm
 def rmsnorm_forward(y: Optional[torch.Tensor], rstd: Optional[torch.Tensor], inp: torch.Tensor, weight: torch.Tensor, eps: float,
                     *, residual_out: Optional[torch.Tensor] = None, inp2: Optional[torch.Tensor] = None,
