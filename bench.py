@@ -191,7 +191,7 @@ def main():
             "metric": f"train tokens/sec/box {args.model} {args.matmul_dtype}", "value": value, "unit": "tokens/s", "n_gpus": comm.world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (value / (BASELINE_TOKS_PER_GPU * comm.world)) if BASELINE_TOKS_PER_GPU else None,
-            "dtype": "bf16 model / e4m3 matmul", "data": "synthetic uniform-random tokens, random-init weights",
+            "dtype": f"bf16 model / {args.matmul_dtype} matmul", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model + ("" if not args.layers else f"[layers={args.layers}]"), "global_batch": B * comm.world * GA,
                        "seq_len": T, "per_gpu_batch": B, "grad_accum": GA,
                        "parallelism": f"dp{comm.world}" + ("" if comm.world == 1 else f"-zero{zl}"), "recompute": args.recompute,

@@ -82,15 +82,28 @@ class LlamaModel:
         self.quant = opts.matmul_dtype() in F8_TYPES
         self.qdtype = opts.matmul_dtype()
         self.gdtype = opts.grad_dtype() if self.quant else self.dtype
+        # block-scaled e4m3: bf16 plumbing, every block GEMM quantises its operands per 32 elements of its contraction axis
+        self.mx = bool(opts.block_scaled)
+        if self.mx:
+            if self.quant or self.dtype != torch.bfloat16:
+                raise ValueError("block_scaled needs a bf16 model without a per-tensor fp8 matmul_type")
+            dims = {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size, "qkv_channels": cfg.qkv_channels,
+                    "batch * seq_len": batch_size * seq_len}
+            bad = [f"{k}={v}" for k, v in dims.items() if v % 128]
+            if bad:
+                raise ValueError("block_scaled needs contraction lengths that are multiples of 128: " + ", ".join(bad))
+            if os.environ.get("LLMQ_GEMM_POLL", "0") == "1":
+                raise ValueError("block_scaled quantises whole weight matrices and cannot poll for arriving weight rows (LLMQ_GEMM_POLL)")
         if seq_len > cfg.max_position_embeddings:
             raise ValueError("sequence length exceeds max_position_embeddings")
         self.fused = self._make_fused()
         self._marks: List = []
+        # (the block-scaled path shares one pair of operand buffers between all GEMMs, so it stays on one stream)
         self._dw_stream = (torch.cuda.Stream(self.device, priority=-1)
-                           if (opts.overlap_dw and self.device.type == "cuda") else None)
+                           if (opts.overlap_dw and self.device.type == "cuda" and not self.mx) else None)
         self._dw_events: List = []
         # SwiGLU inside the epilogues of the up-projection GEMM and of the down-projection's dX GEMM
-        self._fuse_swiglu = (opts.fuse_swiglu and self.device.type == "cuda" and self.dtype == torch.bfloat16
+        self._fuse_swiglu = (opts.fuse_swiglu and not self.mx and self.device.type == "cuda" and self.dtype == torch.bfloat16
                              and batch_size * seq_len >= 256 and cfg.intermediate_size % 128 == 0)
         # per-block CUDA graphs: only where a block body contains nothing but kernels on fixed buffers
         self.graphs = None
@@ -201,6 +214,15 @@ class LlamaModel:
         t.att_scratch = torch.zeros(B * Hq * T, dtype=torch.float32, device=dev)
         t.norm_scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32, device=dev)
         t.bias_scratch = torch.zeros(64 * QC, dtype=torch.float32, device=dev)
+        if self.mx:
+            # one A-role and one B-role operand buffer (values + tiled scales), sized for the largest use
+            feat = max(C, QC, 2 * D)
+            a_uses = [(BT, feat), (feat, BT)]
+            b_uses = [(2 * D, C), (C, 2 * D), (QC, C), (C, QC), (C, D), (D, C), (C, BT), (D, BT)]
+            t.mx_a_q = torch.zeros(BT * feat, dtype=torch.float8_e4m3fn, device=dev)
+            t.mx_a_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_A) for r, k in a_uses), dtype=torch.uint8, device=dev)
+            t.mx_b_q = torch.zeros(max(r * k for r, k in b_uses), dtype=torch.float8_e4m3fn, device=dev)
+            t.mx_b_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_B) for r, k in b_uses), dtype=torch.uint8, device=dev)
         self.tmp = t
         self.host_scalars = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
 
@@ -258,7 +280,22 @@ class LlamaModel:
         self.weights.invalidate()
 
     # ================================================================================== quantised matmuls
+    def _mx_gemm(self, out, a, b, *, a_t=False, b_t=False, bias=None, accumulate=False):
+        """out (+)= op(a) @ op(b)^T with block-scaled e4m3 copies of both operands; ``a_t`` / ``b_t`` contract over the rows
+        of the stored matrix (quantised along the rows, used transposed)."""
+        t = self.tmp
+        a, b = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+        ra, ka = (a.shape[1], a.shape[0]) if a_t else a.shape
+        rb, kb = (b.shape[1], b.shape[0]) if b_t else b.shape
+        aq, bq = t.mx_a_q[:ra * ka].view(ra, ka), t.mx_b_q[:rb * kb].view(rb, kb)
+        K.quantize_mx(a, transpose=a_t, operand="a", q_out=aq, sf_out=t.mx_a_sf)
+        K.quantize_mx(b, transpose=b_t, operand="b", q_out=bq, sf_out=t.mx_b_sf)
+        K.gemm_mx(out.reshape(-1, out.shape[-1]), aq, t.mx_a_sf, bq, t.mx_b_sf, bias=bias, accumulate=accumulate)
+
     def _fwd_mm(self, out, act, act_q, slot, W, w_scale, bias=None, ready=None):
+        if self.mx:
+            self._mx_gemm(out, act, W, bias=bias)
+            return
         if not self.quant:
             K.gemm(out, act, W, bias=bias, ready=ready)
             return
@@ -274,6 +311,13 @@ class LlamaModel:
         ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside.
         ``swiglu_inout`` ([up | gate] -> [d_up | d_gate], in place): the input-gradient GEMM applies the SwiGLU backward
         in its epilogue instead of writing ``dinp``."""
+        if self.mx:
+            if dinp is not None:
+                self._mx_gemm(dinp, dout, W, b_t=True)
+            self._mx_gemm(dW, dout, inp, a_t=True, b_t=True, accumulate=accumulate)
+            if dbias is not None:
+                K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
+            return
         if not self.quant:
             if swiglu_inout is not None:
                 K.gemm_swiglu_backward(swiglu_inout, dout, W, absmax=swiglu_absmax)
@@ -581,7 +625,7 @@ class LlamaModel:
         BT, q = self.B * self.T, self.quant
         sc_of = lambda s: self._slot(l, s)[1]
         fused_dw = getattr(self.grads, "fused_dw", None)
-        rs = (lambda name: fused_dw(l, name)) if fused_dw is not None else (lambda name: None)
+        rs = (lambda name: fused_dw(l, name)) if (fused_dw is not None and not self.mx) else (lambda name: None)
         # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
         fuse_sw = self._fuse_swiglu and bool(int(self.opts.fuse_swiglu) & 2) and p.ready["down_w"] is None
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),

@@ -31,6 +31,10 @@ class LLamaOptions:
     # kernels; off by default: with four epilogue warps per CTA the extra math takes as long as the memory pass it saves
     # (Qwen2.5-7B step: 495.6 ms without, 494.3 forward only, 498.9 backward only, 497.8 both).
     fuse_swiglu: int = 0
+    # block-scaled (MX) e4m3 matmuls: every GEMM operand of the transformer blocks is quantised with one power-of-two scale
+    # per 32 elements of the contraction axis (tcgen05 kind::mxf8f6f4.block_scale); activations and weights stay bf16.
+    # Also selected by matmul_type = "mxe4m3" / "mxfp8".
+    block_scaled: bool = False
     lmhead_transposed_operands: bool = True   # LM-head backward reads W^T / lnf^T copies (K-major GEMM operands)
     trigger_timing_events: bool = False
     # placement of state
@@ -61,6 +65,8 @@ class LLamaOptions:
     variance_type: torch.dtype = torch.float32
 
     def __post_init__(self):
+        if isinstance(self.matmul_type, str) and self.matmul_type.lower() in ("mxe4m3", "mxfp8", "mx"):
+            self.block_scaled, self.matmul_type = True, None
         for name in ("model_type", "matmul_type", "gradient_type", "master_dtype", "momentum_type", "variance_type"):
             v = getattr(self, name)
             if v is not None and v != "" and not isinstance(v, torch.dtype):

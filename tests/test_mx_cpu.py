@@ -43,3 +43,45 @@ def test_gemm_matches_fp32_matmul_of_dequantised_operands():
     ref = a.float() @ b.float().t()
     rel = (out - ref).norm() / ref.norm()
     assert rel < 0.05, rel
+
+
+def _tiny_model(block_scaled, device="cpu", heads=(4, 2), hidden=128, ffn=256, B=2, T=64):
+    from llmq_b200.config import create_config_from_name
+    from llmq_b200.models.llama import LlamaModel
+    from llmq_b200.options import LLamaOptions
+    cfg = create_config_from_name("tiny-qwen2", torch.bfloat16).replace(hidden_size=hidden, intermediate_size=ffn, num_attention_heads=heads[0],
+                                                                        num_key_value_heads=heads[1])
+    m = LlamaModel(cfg, LLamaOptions(matmul_type="mxe4m3" if block_scaled else None), device=device, batch_size=B, seq_len=T)
+    m.init_weights(0)
+    return m
+
+
+def _grad_cosines(ma, mb):
+    ga, gb = ma.get_gradients(), mb.get_gradients()
+    cos = []
+    for n in ga:
+        a, b = ga[n].flatten().float().cpu(), gb[n].flatten().float().cpu()
+        if a.norm() > 0:
+            cos.append(float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12)))
+    return cos
+
+
+def test_block_scaled_training_step_tracks_bf16():
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, 512, (2, 65), generator=g, dtype=torch.int32)
+    x, y = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
+    res = []
+    models = [_tiny_model(False), _tiny_model(True)]
+    assert models[1].mx and not models[1].quant
+    for m in models:
+        m.forward(x)
+        m.backward(x, y, 0.0, 1, 0)
+        res.append(m.update(lr=0.0, step=1))
+    assert abs(res[0]["loss"] - res[1]["loss"]) < 2e-2
+    cos = _grad_cosines(*models)
+    assert min(cos) > 0.95 and sum(cos) / len(cos) > 0.99, cos
+
+
+def test_block_scaled_rejects_unaligned_shapes():
+    with pytest.raises(ValueError, match="multiples of 128"):
+        _tiny_model(True, hidden=64, ffn=172)
