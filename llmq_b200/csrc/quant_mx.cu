@@ -94,9 +94,36 @@ quantize_mx_rows_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const
     if (active && (lane & 3u) == 0) *reinterpret_cast<uint32_t*>(sf + lay.offset(row, kb)) = word;
 }
 
-// Tile of 128 source rows (one K stage) x 64 source columns through shared memory; thread (column, block) quantises
-// 32 values of one source column and writes 32 contiguous bytes of the transposed output.
-constexpr int TC = 64, TR = 128, TPAD = 8;
+// Tile of 128 source rows (one K stage) x 128 source columns through shared memory; thread (column pair, block) quantises
+// 32 values of two neighbouring source columns and writes 32 contiguous bytes of two rows of the transposed output.
+constexpr int TC = 128, TR = 128, TPAD = 8;
+
+// 32 source rows [kb * 32, kb * 32 + 32) of the column pair `cp` of the tile -> e4m3 blocks + scale bytes
+__device__ __forceinline__ void quantise_column_pair(const bf16 (*tile)[TC + TPAD], int cp, int kb, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                     long long c0, long long r0, long long R, const SfLayout& lay) {
+    float v0[32], v1[32];
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tile[kb * 32 + i][2 * cp]));
+        v0[i] = f.x; v1[i] = f.y;
+        a0 = fmaxf(a0, fabsf(f.x)); a1 = fmaxf(a1, fabsf(f.y));
+    }
+    float inv;
+    uint4 lo, hi;
+    const long long col = c0 + 2 * cp;
+    uint32_t e = mx_scale(a0, inv);
+    quantise32(v0, inv, lo, hi);
+    uint4* dst = reinterpret_cast<uint4*>(q + col * R + r0 + kb * 32);
+    dst[0] = lo; dst[1] = hi;
+    sf[lay.offset(col, r0 / 32 + kb)] = static_cast<uint8_t>(e);
+    e = mx_scale(a1, inv);
+    quantise32(v1, inv, lo, hi);
+    dst = reinterpret_cast<uint4*>(q + (col + 1) * R + r0 + kb * 32);
+    dst[0] = lo; dst[1] = hi;
+    sf[lay.offset(col + 1, r0 / 32 + kb)] = static_cast<uint8_t>(e);
+}
+
 __global__ void __launch_bounds__(256)
 quantize_mx_cols_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const bf16* __restrict__ x, long long R, long long C, long long ld,
                         SfLayout lay) {
@@ -110,22 +137,53 @@ quantize_mx_cols_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const
         *reinterpret_cast<uint4*>(&tile[r][cg * 8]) = raw;
     }
     __syncthreads();
-    const int col = threadIdx.x % TC, kb = threadIdx.x / TC;
-    if (c0 + col >= C) return;
-    float v[32];
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        v[i] = __bfloat162float(tile[kb * 32 + i][col]);
-        amax = fmaxf(amax, fabsf(v[i]));
+    const int cp = threadIdx.x % (TC / 2), kb = threadIdx.x / (TC / 2);
+    if (c0 + 2 * cp >= C) return;               // C is even: both columns of a pair exist or neither
+    quantise_column_pair(tile, cp, kb, q, sf, c0, r0, R, lay);
+}
+
+// Both forms from one read of the source: the tile goes through shared memory once; every thread then quantises 32-row
+// blocks of two source columns (-> transposed output) and two 32-column blocks of a source row.
+__global__ void __launch_bounds__(256)
+quantize_mx_both_kernel(uint8_t* __restrict__ q_rows, uint8_t* __restrict__ sf_rows, uint8_t* __restrict__ q_cols, uint8_t* __restrict__ sf_cols,
+                        const bf16* __restrict__ x, long long R, long long C, long long ld, SfLayout lay_rows, SfLayout lay_cols) {
+    __shared__ __align__(16) bf16 tile[TR][TC + TPAD];
+    const long long c0 = static_cast<long long>(blockIdx.x) * TC;
+    const long long r0 = static_cast<long long>(blockIdx.y) * TR;
+    for (int i = threadIdx.x; i < TR * TC / 8; i += 256) {
+        const int r = i / (TC / 8), cg = i % (TC / 8);
+        *reinterpret_cast<uint4*>(&tile[r][cg * 8]) = __ldcs(reinterpret_cast<const uint4*>(x + (r0 + r) * ld + c0 + cg * 8));
     }
-    float inv;
-    const uint32_t e = mx_scale(amax, inv);
-    uint4 lo, hi;
-    quantise32(v, inv, lo, hi);
-    uint4* dst = reinterpret_cast<uint4*>(q + (c0 + col) * R + r0 + kb * 32);
-    dst[0] = lo; dst[1] = hi;
-    sf[lay.offset(c0 + col, r0 / 32 + kb)] = static_cast<uint8_t>(e);
+    __syncthreads();
+    quantise_column_pair(tile, threadIdx.x % (TC / 2), threadIdx.x / (TC / 2), q_cols, sf_cols, c0, r0, R, lay_cols);
+    // row blocks: 32 source columns of one source row; the tile holds 4 per row, two per thread
+    const int row = threadIdx.x / 2;
+    uint32_t e2 = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int blk = (threadIdx.x % 2) * 2 + h;
+        float v[32];
+        float amax = 0.f;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(&tile[row][blk * 32 + g * 8]);
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(hh[j]);
+                v[g * 8 + 2 * j] = f.x; v[g * 8 + 2 * j + 1] = f.y;
+                amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
+        }
+        float inv;
+        uint4 lo, hi;
+        e2 |= mx_scale(amax, inv) << (8 * h);
+        quantise32(v, inv, lo, hi);
+        uint4* dst = reinterpret_cast<uint4*>(q_rows + (r0 + row) * C + c0 + blk * 32);
+        dst[0] = lo; dst[1] = hi;
+    }
+    // the tile spans one K stage of the row form (128 columns): blocks 2 * (t % 2) and + 1 are neighbouring bytes
+    *reinterpret_cast<uint16_t*>(sf_rows + lay_rows.offset(r0 + row, c0 / 32 + (threadIdx.x % 2) * 2)) = static_cast<uint16_t>(e2);
 }
 
 }  // namespace
@@ -155,5 +213,28 @@ extern "C" int llmq_quantize_mx(void* q, void* sf, const void* x, long long R, l
         quantize_mx_cols_kernel<<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<const bf16*>(x), R, C,
                                                           ld, lay);
     }
+    return LLMQ_LAUNCH_CHECK();
+}
+
+// Row form (q_rows [R, C], scales tiled by tile_rows_r) and column form (q_cols [C, R], tiled by tile_rows_c) of the same
+// bf16 matrix from one pass over it.  R and C multiples of 128.
+extern "C" int llmq_quantize_mx_both(void* q_rows, void* sf_rows, int tile_rows_r, void* q_cols, void* sf_cols, int tile_rows_c, const void* x,
+                                     long long R, long long C, long long ld, cudaStream_t stream) {
+    if (R <= 0 || C <= 0) return 0;
+    if (R % 128 || C % 128 || ld % 8) return -5;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q_rows) & 15u) || (reinterpret_cast<uintptr_t>(q_cols) & 15u)) return -3;
+    for (int t : {tile_rows_r, tile_rows_c}) if (t < 32 || t > 256 || t % 32) return -5;
+    const SfLayout lr = make_layout(R, tile_rows_r), lc = make_layout(C, tile_rows_c);
+    if (R % tile_rows_r || tile_rows_r % 128) {
+        cudaError_t e = cudaMemsetAsync(sf_rows, 0, static_cast<size_t>(lr.bytes(C)), stream);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    if (C % tile_rows_c || tile_rows_c % 128) {
+        cudaError_t e = cudaMemsetAsync(sf_cols, 0, static_cast<size_t>(lc.bytes(R)), stream);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    dim3 grid(static_cast<unsigned int>(C / TC), static_cast<unsigned int>(R / TR));
+    quantize_mx_both_kernel<<<grid, 256, 0, stream>>>(static_cast<uint8_t*>(q_rows), static_cast<uint8_t*>(sf_rows), static_cast<uint8_t*>(q_cols),
+                                                      static_cast<uint8_t*>(sf_cols), static_cast<const bf16*>(x), R, C, ld, lr, lc);
     return LLMQ_LAUNCH_CHECK();
 }

@@ -121,6 +121,24 @@ def matmul(c: T, a: T, b: T, bias: Optional[T], scale_a: Optional[T], scale_b: O
            absmax=absmax)
 
 
+@_op("llmq_b200::matmul_mx", mutates_args=("c", "absmax"))
+def matmul_mx(c: T, a: T, a_scales: T, b: T, b_scales: T, bias: Optional[T], absmax: Optional[T], accumulate: bool = False) -> None:
+    """c[M,N] (+)= dq(a)[M,K] @ dq(b)[N,K]^T with block-scaled e4m3 operands (one power-of-two scale per 32 elements along K) from
+    ``quantize_mx``.  No counterpart in the reference, whose fp8 matmuls are per-tensor scaled."""
+    K.gemm_mx(c, a, a_scales, b, b_scales, bias=bias, accumulate=accumulate, absmax=absmax)
+
+
+@_op("llmq_b200::quantize_mx", mutates_args=("out", "scales"))
+def quantize_mx(out: T, scales: T, x: T, transpose: bool = False, operand: str = "a") -> None:
+    """Block-scaled e4m3 form of bf16 ``x[R, C]``: along the rows, or (``transpose``) along the columns as ``out[C, R]``.
+    ``scales`` holds ``mx_scale_bytes`` bytes in the GEMM's tiled layout for its ``a`` or ``b`` side."""
+    K.quantize_mx(x, transpose=transpose, operand=operand, q_out=out, sf_out=scales)
+
+
+def mx_scale_bytes(rows: int, k: int, operand: str = "a") -> int:
+    return K.mx_sf_bytes(rows, k, K.MX_TILE_A if operand == "a" else K.MX_TILE_B)
+
+
 @_op("llmq_b200::backward_bias", mutates_args=("dbias", "dbias_buffer"))
 def backward_bias(dbias: T, dout: T, scale_a: Optional[T], scale_b: Optional[T], dbias_buffer: T, accumulate: bool = True) -> None:
     K.bias_backward(dbias, dout, dbias_buffer, scale_a=scale_a, scale_b=scale_b, accumulate=accumulate)

@@ -221,6 +221,8 @@ class LlamaModel:
             b_uses = [(2 * D, C), (C, 2 * D), (QC, C), (C, QC), (C, D), (D, C), (C, BT), (D, BT)]
             t.mx_a_q = torch.zeros(BT * feat, dtype=torch.float8_e4m3fn, device=dev)
             t.mx_a_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_A) for r, k in a_uses), dtype=torch.uint8, device=dev)
+            t.mx_a2_q = torch.zeros(BT * feat, dtype=torch.float8_e4m3fn, device=dev)       # column form of an output gradient
+            t.mx_a2_sf = torch.zeros_like(t.mx_a_sf)
             t.mx_b_q = torch.zeros(max(r * k for r, k in b_uses), dtype=torch.float8_e4m3fn, device=dev)
             t.mx_b_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_B) for r, k in b_uses), dtype=torch.uint8, device=dev)
         self.tmp = t
@@ -312,9 +314,22 @@ class LlamaModel:
         ``swiglu_inout`` ([up | gate] -> [d_up | d_gate], in place): the input-gradient GEMM applies the SwiGLU backward
         in its epilogue instead of writing ``dinp``."""
         if self.mx:
+            # dout feeds two GEMMs with different contraction axes: its row form and its column form come from one pass
+            t = self.tmp
+            d2 = dout.reshape(-1, dout.shape[-1])
+            BT, OC = d2.shape
+            d_rows, d_cols = t.mx_a_q[:BT * OC].view(BT, OC), t.mx_a2_q[:BT * OC].view(OC, BT)
             if dinp is not None:
-                self._mx_gemm(dinp, dout, W, b_t=True)
-            self._mx_gemm(dW, dout, inp, a_t=True, b_t=True, accumulate=accumulate)
+                K.quantize_mx_both(d2, q_rows=d_rows, sf_rows=t.mx_a_sf, q_cols=d_cols, sf_cols=t.mx_a2_sf)
+                wq = t.mx_b_q[:W.numel()].view(W.shape[1], W.shape[0])
+                K.quantize_mx(W, transpose=True, operand="b", q_out=wq, sf_out=t.mx_b_sf)
+                K.gemm_mx(dinp.reshape(BT, -1), d_rows, t.mx_a_sf, wq, t.mx_b_sf)
+            else:
+                K.quantize_mx(d2, transpose=True, operand="a", q_out=d_cols, sf_out=t.mx_a2_sf)
+            i2 = inp.reshape(BT, -1)
+            iq = t.mx_b_q[:i2.numel()].view(i2.shape[1], BT)
+            K.quantize_mx(i2, transpose=True, operand="b", q_out=iq, sf_out=t.mx_b_sf)
+            K.gemm_mx(dW, d_cols, t.mx_a2_sf, iq, t.mx_b_sf, accumulate=accumulate)
             if dbias is not None:
                 K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
             return

@@ -92,6 +92,11 @@ def bench_gemm_mx(a, tm):
         tq, tsf = K.quantize_mx(x, transpose=True, operand="b")
         ms_t = tm.time(lambda: K.quantize_mx(x, transpose=True, operand="b", q_out=tq, sf_out=tsf))
         out["quantize_cols_ms"] = round(ms_t, 4); out[f"quantize_cols_frac_of_{src}_bw"] = round(nbytes / ms_t / 1e6 / bw, 3)
+        if a.k % 128 == 0:
+            bufs = K.quantize_mx_both(x)
+            ms_b = tm.time(lambda: K.quantize_mx_both(x, q_rows=bufs[0], sf_rows=bufs[1], q_cols=bufs[2], sf_cols=bufs[3]))
+            out["quantize_both_ms"] = round(ms_b, 4)
+            out[f"quantize_both_frac_of_{src}_bw"] = round((a.m * a.k * 4 + a.m * a.k // 16) / ms_b / 1e6 / bw, 3)
     print(json.dumps(out))
 
 

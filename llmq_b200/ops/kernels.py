@@ -213,6 +213,31 @@ def quantize_mx(x: torch.Tensor, *, transpose: bool = False, operand: str = "a",
     return q_out, sf_out
 
 
+def quantize_mx_both(x: torch.Tensor, *, row_operand: str = "a", col_operand: str = "a", q_rows=None, sf_rows=None, q_cols=None, sf_cols=None):
+    """Row form and column (transposed) form of ``x[R, C]`` from one pass over it: ``(q_rows[R, C], sf_rows, q_cols[C, R], sf_cols)``.
+    R and C must be multiples of 128."""
+    R, C = x.shape
+    assert R % 128 == 0 and C % 128 == 0
+    tr, tc = (MX_TILE_A if row_operand == "a" else MX_TILE_B), (MX_TILE_A if col_operand == "a" else MX_TILE_B)
+    if q_rows is None:
+        q_rows = torch.empty((R, C), dtype=F8, device=x.device)
+    if q_cols is None:
+        q_cols = torch.empty((C, R), dtype=F8, device=x.device)
+    if sf_rows is None:
+        sf_rows = torch.empty(mx_sf_bytes(R, C, tr), dtype=torch.uint8, device=x.device)
+    if sf_cols is None:
+        sf_cols = torch.empty(mx_sf_bytes(C, R, tc), dtype=torch.uint8, device=x.device)
+    if x.is_cuda:
+        assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and q_rows.is_contiguous() and q_cols.is_contiguous()
+        rc = L.kernels().llmq_quantize_mx_both(L.ptr(q_rows), L.ptr(sf_rows), tr, L.ptr(q_cols), L.ptr(sf_cols), tc, L.ptr(x), _ll(R), _ll(C),
+                                               _ll(x.stride(0)), L.stream_ptr())
+        L.check(rc, "quantize_mx_both")
+    else:
+        quantize_mx(x, operand=row_operand, q_out=q_rows, sf_out=sf_rows)
+        quantize_mx(x, transpose=True, operand=col_operand, q_out=q_cols, sf_out=sf_cols)
+    return q_rows, sf_rows, q_cols, sf_cols
+
+
 def dequantize_mx(q: torch.Tensor, sf: torch.Tensor, operand: str = "a") -> torch.Tensor:
     """fp32 values of a block-scaled operand (reference / debugging)."""
     rows, K = q.shape

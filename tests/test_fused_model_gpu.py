@@ -34,13 +34,17 @@ def _worker(rank, world, port, q):
         g = torch.Generator().manual_seed(5 + rank)
         tok = torch.randint(0, 1024, (2, B, T + 1), generator=g, dtype=torch.int32)
         results = {}
-        for zero, ga in CASES:
-            for mode in ("nccl", "fused", "fused+gemm_rs"):
+        runs = [(zero, ga, mode) for zero, ga in CASES for mode in ("nccl", "fused", "fused+gemm_rs")]
+        runs += [(3, 2, "mx-nccl"), (3, 2, "mx-fused")]          # block-scaled e4m3 matmuls on sharded bf16 weights
+        for zero, ga, mode in runs:
+            if True:
+                mx = mode.startswith("mx-")
+                coll = mode[3:] if mx else mode.split("+")[0]
                 os.environ["LLMQ_GEMM_RS"] = "1" if mode.endswith("gemm_rs") else "0"
-                opts = LLamaOptions(matmul_type="e4m3", collectives=mode.split("+")[0], momentum_type="bf16", variance_type="bf16")
+                opts = LLamaOptions(matmul_type="mxe4m3" if mx else "e4m3", collectives=coll, momentum_type="bf16", variance_type="bf16")
                 opts.set_zero_level(zero)
                 m = LlamaModel(cfg, opts, comm, dev, B, T)
-                assert (m.fused is not None) == mode.startswith("fused")
+                assert (m.fused is not None) == (coll == "fused") and m.mx == mx
                 assert m.grads.gemm_rs == mode.endswith("gemm_rs")
                 m.init_weights(3)
                 out = []
@@ -86,3 +90,9 @@ def test_fused_training_matches_nccl():
                 assert abs(l0 - l1) < 5e-3, (zero, mode, a, b)
                 assert abs(n0 - n1) < 2e-2 * max(1.0, n0), (zero, mode, a, b)
         assert a[-1][0] < a[0][0]
+    a, b = r0[(3, 2, "mx-nccl")], r0[(3, 2, "mx-fused")]
+    for (l0, n0), (l1, n1) in zip(a, b):
+        assert abs(l0 - l1) < 5e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0), (a, b)
+    assert a[-1][0] < a[0][0]
+    # the block-scaled recipe follows the per-tensor one closely on this model
+    assert abs(a[0][0] - r0[(3, 2, "nccl")][0][0]) < 5e-2

@@ -81,3 +81,12 @@ def test_block_scaled_model_step_matches_cpu_path():
     assert abs(res[0]["loss"] - res[1]["loss"]) < 4e-2, res         # bf16 activations: attention / norms round differently on the two paths
     cos = _grad_cosines(*models)
     assert min(cos) > 0.97 and sum(cos) / len(cos) > 0.99, cos
+
+
+def test_quantize_mx_both_equals_the_two_single_passes():
+    x = _blocky(384, 256, 9).to(DEV)
+    qr, sr, qc, sc = K.quantize_mx_both(x, row_operand="a", col_operand="b")
+    qr1, sr1 = K.quantize_mx(x, operand="a")
+    qc1, sc1 = K.quantize_mx(x, transpose=True, operand="b")
+    assert torch.equal(qr.view(torch.uint8), qr1.view(torch.uint8)) and torch.equal(sr, sr1)
+    assert torch.equal(qc.view(torch.uint8), qc1.view(torch.uint8)) and torch.equal(sc, sc1)

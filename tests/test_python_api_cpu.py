@@ -54,3 +54,17 @@ def test_custom_ops_on_cpu_tensors():
     before = p_.clone()
     ops.adamw_update(p_, g_, m_, v_, 1e-2, 0.9, 0.95, 1, 1e-8, 0.0)
     assert not torch.equal(before, p_) and m_.abs().sum() > 0
+
+
+def test_block_scaled_custom_ops():
+    torch.manual_seed(1)
+    a, b = torch.randn(128, 256).bfloat16(), torch.randn(224, 256).bfloat16()
+    aq, bq = torch.zeros(128, 256, dtype=torch.float8_e4m3fn), torch.zeros(224, 256, dtype=torch.float8_e4m3fn)
+    asf = torch.zeros(ops.mx_scale_bytes(128, 256, "a"), dtype=torch.uint8)
+    bsf = torch.zeros(ops.mx_scale_bytes(224, 256, "b"), dtype=torch.uint8)
+    torch.ops.llmq_b200.quantize_mx(aq, asf, a, False, "a")
+    torch.ops.llmq_b200.quantize_mx(bq, bsf, b, False, "b")
+    c = torch.zeros(128, 224)
+    torch.ops.llmq_b200.matmul_mx(c, aq, asf, bq, bsf, None, None, False)
+    ref = a.float() @ b.float().t()
+    assert (c - ref).norm() / ref.norm() < 0.05
