@@ -2,7 +2,8 @@
 //
 //   C[M,N] (+)= alpha * A * B^T (+ bias[N]),   fp32 accumulation in tensor memory.
 //
-// Operands are bf16 or 8-bit floats (e4m3 / e5m2).  Each operand may be stored K-major
+// Operands are bf16, 8-bit floats (e4m3 / e5m2) or - one-CTA kernel only - fp32 multiplied as tf32 (the GEMMs of an
+// fp32 model: src/kernels/matmul.cpp:46-153 of the reference runs those through cuBLASLt).  Each operand may be stored K-major
 // (row = M/N index, K contiguous) or MN-major (row = K index, M/N contiguous); the MN-major
 // form is what lets the backward GEMMs (dX = dY * W, dW = dY^T * X) read the very same tensors
 // as the forward pass without any transpose kernel.  alpha is the product of two optional
@@ -51,7 +52,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / gsz;
 }
 
-template <bool F8>
+// Kind: MMA kind of ptx_sm100.cuh's mma_issue (0 bf16, 1 8-bit floats, 2 tf32 on fp32 operands).
+template <int Kind>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -159,10 +161,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tc_fence_after_sync();
                     const uint32_t alo = a_lo0 + stage * (STAGE_BYTES >> 4);
                     const uint32_t blo = b_lo0 + stage * (STAGE_BYTES >> 4);
-                    mma_issue<F8, false>(d_tmem, alo, a_hi, blo, b_hi, idesc, k > k_begin ? 1u : 0u);
-                    mma_issue<F8, false>(d_tmem, alo + a_inc, a_hi, blo + b_inc, b_hi, idesc, 1u);
-                    mma_issue<F8, false>(d_tmem, alo + 2 * a_inc, a_hi, blo + 2 * b_inc, b_hi, idesc, 1u);
-                    mma_issue<F8, false>(d_tmem, alo + 3 * a_inc, a_hi, blo + 3 * b_inc, b_hi, idesc, 1u);
+                    mma_issue<Kind, false>(d_tmem, alo, a_hi, blo, b_hi, idesc, k > k_begin ? 1u : 0u);
+                    mma_issue<Kind, false>(d_tmem, alo + a_inc, a_hi, blo + b_inc, b_hi, idesc, 1u);
+                    mma_issue<Kind, false>(d_tmem, alo + 2 * a_inc, a_hi, blo + 2 * b_inc, b_hi, idesc, 1u);
+                    mma_issue<Kind, false>(d_tmem, alo + 3 * a_inc, a_hi, blo + 3 * b_inc, b_hi, idesc, 1u);
                     mma_commit(empty_bar(stage));          // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -262,7 +264,8 @@ int llmq_encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, long
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
     cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
-    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                             : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
     CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
@@ -354,8 +357,10 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
                      const float* scale_a, const float* scale_b, float alpha, float* absmax_out, unsigned int* status,
                      int num_sms, const unsigned int* ready_flags, unsigned int ready_gen, int ready_rows_per_src,
                      double ready_limit_s, const GemmParams* rs, cudaStream_t stream) {
-    const int eb = ab_dtype == 0 ? 2 : 1;
-    if ((b_dtype == 0 ? 2 : 1) != eb) return -2;
+    auto width = [](int dt) { return dt == 0 ? 2 : (dt == 1 || dt == 2) ? 1 : (dt == 3 ? 4 : 0); };
+    const int eb = width(ab_dtype);
+    if (eb == 0 || width(b_dtype) != eb) return -2;
+    if (eb == 4 && (rs != nullptr || ready_flags != nullptr)) return -2;      // fp32 operands: one-CTA kernel without fused collectives
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     // TMA needs 16-byte aligned bases and row pitches
     if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) return -3;
@@ -368,7 +373,8 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
     else             rc = llmq_encode_tmap_2d(&ta, A, eb, K, M, lda, bk);
     if (rc) return rc;
     // The CTA-pair kernel stages 128 rows of B per CTA; the one-CTA kernel stages all 256.
-    const bool pair_kernel = rs != nullptr || ready_flags != nullptr || g_gemm_mode == 2 || (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32);
+    const bool pair_kernel = eb != 4 && (rs != nullptr || ready_flags != nullptr || g_gemm_mode == 2 ||
+                                         (g_gemm_mode == 0 && M >= 256 && static_cast<long long>(M) * N >= 256LL * 256 * 32));
     if (!b_mn_major) rc = llmq_encode_tmap_2d(&tb, B, eb, N, K, ldb, pair_kernel ? 128 : BN);
     else             rc = llmq_encode_tmap_2d(&tb, B, eb, K, N, ldb, bk);
     if (rc) return rc;
@@ -376,8 +382,8 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
     GemmParams p{};
     p.M = M; p.N = N; p.K = K; p.elem_bytes = eb;
     p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
-    p.a_fmt = ab_dtype == 0 ? 1 : (ab_dtype == 1 ? 0 : 1);
-    p.b_fmt = b_dtype == 0 ? 1 : (b_dtype == 1 ? 0 : 1);
+    p.a_fmt = ab_dtype == 3 ? 2 : (ab_dtype == 0 ? 1 : (ab_dtype == 1 ? 0 : 1));
+    p.b_fmt = b_dtype == 3 ? 2 : (b_dtype == 0 ? 1 : (b_dtype == 1 ? 0 : 1));
     p.C = C; p.ldc = ldc; p.c_dtype = c_dtype; p.accumulate = accumulate;
     p.bias = bias; p.bias_dtype = bias_dtype;
     p.scale_a = scale_a; p.scale_b = scale_b; p.alpha = alpha;
@@ -399,8 +405,9 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
         attr_set[dev & 63] = true;
     }
@@ -418,8 +425,9 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
     if (splits > 1) { p.k_splits = splits; p.partial = g_splitk_ws; }
     const int items = tiles * splits;
     int grid = items < num_sms ? items : num_sms;
-    if (eb == 1) gemm_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
-    else         gemm_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (eb == 1)      gemm_tcgen05_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    else if (eb == 2) gemm_tcgen05_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    else              gemm_tcgen05_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
     if (splits > 1) {
         long long blocks = (static_cast<long long>(M) * N + 255) / 256;
         if (blocks > 4LL * num_sms) blocks = 4LL * num_sms;

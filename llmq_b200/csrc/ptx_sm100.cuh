@@ -167,7 +167,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 }
 
 // Instruction descriptor (dense, fp32 accumulate).
-//   fmt: kind::f16 -> 0 = f16, 1 = bf16;   kind::f8f6f4 -> 0 = e4m3, 1 = e5m2
+//   fmt: kind::f16 -> 0 = f16, 1 = bf16;   kind::f8f6f4 -> 0 = e4m3, 1 = e5m2;   kind::tf32 -> 2
 __host__ __device__ constexpr uint32_t make_instr_desc(uint32_t a_fmt, uint32_t b_fmt, bool a_mn_major, bool b_mn_major,
                                                        uint32_t m, uint32_t n) {
     return (1u << 4)                       // D format: f32
@@ -320,10 +320,17 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
 // swizzle bits) is loop invariant and the low half is "start address | LBO << 16", so stepping through
 // K or through pipeline stages is one 32-bit add per operand.  This keeps the single issuing thread far
 // ahead of the tensor core; rebuilding 64-bit descriptors per MMA costs more cycles than the MMA runs.
-template <bool F8, bool Pair>
+// Kind: 0 = f16 (bf16 / fp16 operands), 1 = f8f6f4 (8-bit floats), 2 = tf32 (fp32 operands, 10-bit mantissa products).
+template <int Kind, bool Pair>
 __device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                           uint32_t idesc, uint32_t accumulate) {
-    if constexpr (F8 && !Pair) {
+    constexpr bool F8 = Kind == 1;
+    if constexpr (Kind == 2) {
+        static_assert(!Pair, "the tf32 kind is only wired into the one-CTA kernel");
+        asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n}\n"
+                     ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+    } else if constexpr (F8 && !Pair) {
         asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
                      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n}\n"
                      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");

@@ -94,79 +94,81 @@ quantize_mx_rows_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const
     if (active && (lane & 3u) == 0) *reinterpret_cast<uint32_t*>(sf + lay.offset(row, kb)) = word;
 }
 
-// Tile of 128 source rows (one K stage) x 128 source columns through shared memory; thread (column pair, block) quantises
-// 32 values of two neighbouring source columns and writes 32 contiguous bytes of two rows of the transposed output.
-constexpr int TC = 128, TR = 128, TPAD = 8;
+// Tile of 128 source rows (one K stage of the column form) x 64 source columns.  Input and outputs are staged in shared
+// memory so that every global access is a run of full 32-byte sectors: the column form leaves as 64 rows x 128 bytes, the
+// row form as 128 rows x 64 bytes.
+constexpr int TC = 64, TR = 128, TPAD = 8;
 
-// 32 source rows [kb * 32, kb * 32 + 32) of the column pair `cp` of the tile -> e4m3 blocks + scale bytes
-__device__ __forceinline__ void quantise_column_pair(const bf16 (*tile)[TC + TPAD], int cp, int kb, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
-                                                     long long c0, long long r0, long long R, const SfLayout& lay) {
-    float v0[32], v1[32];
-    float a0 = 0.f, a1 = 0.f;
+struct MxTileSmem {
+    bf16 in[TR][TC + TPAD];             // source tile
+    uint8_t out_c[TC][TR + 16];         // transposed e4m3 tile (column form), 16 bytes of padding against bank conflicts
+    uint8_t out_r[TR][TC + 16];         // e4m3 tile in source orientation (row form)
+    uint32_t sf_c[TC];                  // the four block scales of every source column
+};
+
+__device__ __forceinline__ void load_tile(MxTileSmem& sm, const bf16* __restrict__ x, long long r0, long long c0, long long C, long long ld) {
+    for (int i = threadIdx.x; i < TR * TC / 8; i += 256) {
+        const int r = i / (TC / 8), cg = i % (TC / 8);
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (c0 + cg * 8 < C) raw = __ldcs(reinterpret_cast<const uint4*>(x + (r0 + r) * ld + c0 + cg * 8));
+        *reinterpret_cast<uint4*>(&sm.in[r][cg * 8]) = raw;
+    }
+}
+
+// thread (column, block): 32 source rows of one source column -> shared memory; then the tile leaves in 128-byte rows
+__device__ __forceinline__ void column_form(MxTileSmem& sm, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, long long r0, long long c0,
+                                            long long R, long long C, const SfLayout& lay) {
+    const int col = threadIdx.x % TC, kb = threadIdx.x / TC;
+    float v[32];
+    float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tile[kb * 32 + i][2 * cp]));
-        v0[i] = f.x; v1[i] = f.y;
-        a0 = fmaxf(a0, fabsf(f.x)); a1 = fmaxf(a1, fabsf(f.y));
+        v[i] = __bfloat162float(sm.in[kb * 32 + i][col]);
+        amax = fmaxf(amax, fabsf(v[i]));
     }
     float inv;
     uint4 lo, hi;
-    const long long col = c0 + 2 * cp;
-    uint32_t e = mx_scale(a0, inv);
-    quantise32(v0, inv, lo, hi);
-    uint4* dst = reinterpret_cast<uint4*>(q + col * R + r0 + kb * 32);
-    dst[0] = lo; dst[1] = hi;
-    sf[lay.offset(col, r0 / 32 + kb)] = static_cast<uint8_t>(e);
-    e = mx_scale(a1, inv);
-    quantise32(v1, inv, lo, hi);
-    dst = reinterpret_cast<uint4*>(q + (col + 1) * R + r0 + kb * 32);
-    dst[0] = lo; dst[1] = hi;
-    sf[lay.offset(col + 1, r0 / 32 + kb)] = static_cast<uint8_t>(e);
+    const uint32_t e = mx_scale(amax, inv);
+    quantise32(v, inv, lo, hi);
+    *reinterpret_cast<uint4*>(&sm.out_c[col][kb * 32]) = lo;
+    *reinterpret_cast<uint4*>(&sm.out_c[col][kb * 32 + 16]) = hi;
+    reinterpret_cast<uint8_t*>(&sm.sf_c[col])[kb] = static_cast<uint8_t>(e);
+    __syncthreads();
+    for (int i = threadIdx.x; i < TC * TR / 16; i += 256) {
+        const int row = i / (TR / 16), ch = i % (TR / 16);
+        if (c0 + row < C) *reinterpret_cast<uint4*>(q + (c0 + row) * R + r0 + ch * 16) = *reinterpret_cast<const uint4*>(&sm.out_c[row][ch * 16]);
+    }
+    if (threadIdx.x < TC && c0 + threadIdx.x < C)
+        *reinterpret_cast<uint32_t*>(sf + lay.offset(c0 + threadIdx.x, r0 / 32)) = sm.sf_c[threadIdx.x];
 }
 
 __global__ void __launch_bounds__(256)
 quantize_mx_cols_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const bf16* __restrict__ x, long long R, long long C, long long ld,
                         SfLayout lay) {
-    __shared__ __align__(16) bf16 tile[TR][TC + TPAD];
+    __shared__ __align__(16) MxTileSmem sm;
     const long long c0 = static_cast<long long>(blockIdx.x) * TC;
     const long long r0 = static_cast<long long>(blockIdx.y) * TR;
-    for (int i = threadIdx.x; i < TR * TC / 8; i += 256) {
-        const int r = i / (TC / 8), cg = i % (TC / 8);
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (c0 + cg * 8 < C) raw = __ldcs(reinterpret_cast<const uint4*>(x + (r0 + r) * ld + c0 + cg * 8));
-        *reinterpret_cast<uint4*>(&tile[r][cg * 8]) = raw;
-    }
+    load_tile(sm, x, r0, c0, C, ld);
     __syncthreads();
-    const int cp = threadIdx.x % (TC / 2), kb = threadIdx.x / (TC / 2);
-    if (c0 + 2 * cp >= C) return;               // C is even: both columns of a pair exist or neither
-    quantise_column_pair(tile, cp, kb, q, sf, c0, r0, R, lay);
+    column_form(sm, q, sf, r0, c0, R, C, lay);
 }
 
-// Both forms from one read of the source: the tile goes through shared memory once; every thread then quantises 32-row
-// blocks of two source columns (-> transposed output) and two 32-column blocks of a source row.
+// Both forms from one read of the source.
 __global__ void __launch_bounds__(256)
 quantize_mx_both_kernel(uint8_t* __restrict__ q_rows, uint8_t* __restrict__ sf_rows, uint8_t* __restrict__ q_cols, uint8_t* __restrict__ sf_cols,
                         const bf16* __restrict__ x, long long R, long long C, long long ld, SfLayout lay_rows, SfLayout lay_cols) {
-    __shared__ __align__(16) bf16 tile[TR][TC + TPAD];
+    __shared__ __align__(16) MxTileSmem sm;
     const long long c0 = static_cast<long long>(blockIdx.x) * TC;
     const long long r0 = static_cast<long long>(blockIdx.y) * TR;
-    for (int i = threadIdx.x; i < TR * TC / 8; i += 256) {
-        const int r = i / (TC / 8), cg = i % (TC / 8);
-        *reinterpret_cast<uint4*>(&tile[r][cg * 8]) = __ldcs(reinterpret_cast<const uint4*>(x + (r0 + r) * ld + c0 + cg * 8));
-    }
+    load_tile(sm, x, r0, c0, C, ld);
     __syncthreads();
-    quantise_column_pair(tile, threadIdx.x % (TC / 2), threadIdx.x / (TC / 2), q_cols, sf_cols, c0, r0, R, lay_cols);
-    // row blocks: 32 source columns of one source row; the tile holds 4 per row, two per thread
-    const int row = threadIdx.x / 2;
-    uint32_t e2 = 0;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int blk = (threadIdx.x % 2) * 2 + h;
+    {   // row form: thread (row, half) quantises 32 source columns of one source row
+        const int row = threadIdx.x / 2, blk = threadIdx.x % 2;
         float v[32];
         float amax = 0.f;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(&tile[row][blk * 32 + g * 8]);
+            const uint4 raw = *reinterpret_cast<const uint4*>(&sm.in[row][blk * 32 + g * 8]);
             const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -177,13 +179,19 @@ quantize_mx_both_kernel(uint8_t* __restrict__ q_rows, uint8_t* __restrict__ sf_r
         }
         float inv;
         uint4 lo, hi;
-        e2 |= mx_scale(amax, inv) << (8 * h);
+        const uint32_t e = mx_scale(amax, inv);
         quantise32(v, inv, lo, hi);
-        uint4* dst = reinterpret_cast<uint4*>(q_rows + (r0 + row) * C + c0 + blk * 32);
-        dst[0] = lo; dst[1] = hi;
+        *reinterpret_cast<uint4*>(&sm.out_r[row][blk * 32]) = lo;
+        *reinterpret_cast<uint4*>(&sm.out_r[row][blk * 32 + 16]) = hi;
+        // the two blocks of a row sit in neighbouring lanes and in neighbouring scale bytes (64 columns = half a K stage)
+        const uint32_t pair = e | (__shfl_xor_sync(0xffffffffu, e, 1) << 8);
+        if (blk == 0) *reinterpret_cast<uint16_t*>(sf_rows + lay_rows.offset(r0 + row, c0 / 32)) = static_cast<uint16_t>(pair);
     }
-    // the tile spans one K stage of the row form (128 columns): blocks 2 * (t % 2) and + 1 are neighbouring bytes
-    *reinterpret_cast<uint16_t*>(sf_rows + lay_rows.offset(r0 + row, c0 / 32 + (threadIdx.x % 2) * 2)) = static_cast<uint16_t>(e2);
+    column_form(sm, q_cols, sf_cols, r0, c0, R, C, lay_cols);       // contains the barrier that also covers out_r
+    for (int i = threadIdx.x; i < TR * TC / 16; i += 256) {
+        const int row = i / (TC / 16), ch = i % (TC / 16);
+        *reinterpret_cast<uint4*>(q_rows + (r0 + row) * C + c0 + ch * 16) = *reinterpret_cast<const uint4*>(&sm.out_r[row][ch * 16]);
+    }
 }
 
 }  // namespace

@@ -1,6 +1,6 @@
 // Native unit tests of the kernel library: each case runs a kernel through its C entry point and compares it with a
 // plain C++ reference on the host (role of the reference's Catch2 suite, src/testing/test-swiglu.cu, test-rope.cu,
-// test-classifier.cu, test-gemm.cpp).  Build: python -m llmq_b200.build --tests ; run: build/test_kernels
+// test-classifier.cu, test-gemm.cpp), plus the block-scaled e4m3 quantiser and GEMM.  Build: python -m llmq_b200.build --tests ; run: build/test_kernels
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -18,6 +18,11 @@ int llmq_rope_table(float*, int, int, float, cudaStream_t);
 int llmq_fused_classifier(void*, float*, float*, const int*, float, float, int, int, long long, int, int, cudaStream_t);
 int llmq_gemm(const void*, const void*, void*, const void*, int, int, int, int, int, int, int, long long, long long, long long, int, int, int,
               const float*, const float*, float, float*, unsigned int*, int, cudaStream_t);
+int llmq_quantize_mx(void*, void*, const void*, long long, long long, long long, int, int, cudaStream_t);
+long long llmq_mx_sf_bytes(long long, long long, int);
+int llmq_gemm_mx_tile_n();
+int llmq_gemm_mx(const void*, const void*, const void*, const void*, void*, const void*, int, int, int, long long, long long, long long, int, int, int,
+                 float, float*, unsigned int*, int, cudaStream_t);
 }
 
 namespace {
@@ -169,6 +174,53 @@ void test_gemm(bool fp8) {
     report("gemm status word", static_cast<double>(to_host(dstatus, 1)[0]), 0.0);
     cudaFree(da); cudaFree(db); cudaFree(dbias); cudaFree(dc); cudaFree(dstatus);
 }
+// Block-scaled e4m3: device quantiser -> host dequantisation through the tiled scale layout -> GEMM against a double sum.
+std::vector<float> dequant_mx(const std::vector<__nv_fp8_e4m3>& q, const std::vector<unsigned char>& sf, int rows, int K, int tile_rows) {
+    const int chunks = (tile_rows + 127) / 128, n_tiles = (rows + tile_rows - 1) / tile_rows;
+    std::vector<float> out(q.size());
+    for (int r = 0; r < rows; ++r) for (int k = 0; k < K; ++k) {
+        const int kb = k / 32, tile = r / tile_rows, rt = r % tile_rows, rr = rt % 128;
+        const size_t off = ((static_cast<size_t>(kb / 4) * n_tiles + tile) * chunks + rt / 128) * 512 + (rr % 32) * 16 + (rr / 32) * 4 + kb % 4;
+        out[static_cast<size_t>(r) * K + k] = static_cast<float>(q[static_cast<size_t>(r) * K + k]) * std::ldexp(1.0f, static_cast<int>(sf[off]) - 127);
+    }
+    return out;
+}
+
+void test_gemm_mx() {
+    const int M = 200, N = 300, K = 384, TN = llmq_gemm_mx_tile_n();
+    Rng r{9ull};
+    std::vector<float> a(static_cast<size_t>(M) * K), b(static_cast<size_t>(N) * K);
+    // blocks of very different magnitude: a per-tensor scale would flush the small ones to zero
+    for (size_t i = 0; i < a.size(); ++i) a[i] = bf(r.next() * std::ldexp(1.0f, static_cast<int>(i / 32 % 13) - 6));
+    for (size_t i = 0; i < b.size(); ++i) b[i] = bf(r.next() * std::ldexp(1.0f, static_cast<int>(i / 32 % 11) - 5));
+    auto da = to_dev(as_bf16(a)); auto db = to_dev(as_bf16(b));
+    const size_t sfa_bytes = llmq_mx_sf_bytes(M, K, 128), sfb_bytes = llmq_mx_sf_bytes(N, K, TN);
+    __nv_fp8_e4m3 *qa, *qb; unsigned char *sfa, *sfb; float* dc; unsigned int* dstatus;
+    CK(cudaMalloc(&qa, a.size())); CK(cudaMalloc(&qb, b.size())); CK(cudaMalloc(&sfa, sfa_bytes)); CK(cudaMalloc(&sfb, sfb_bytes));
+    CK(cudaMalloc(&dc, sizeof(float) * M * N)); CK(cudaMalloc(&dstatus, 4)); CK(cudaMemset(dstatus, 0, 4));
+    int rc = llmq_quantize_mx(qa, sfa, da, M, K, K, 0, 128, 0);
+    rc |= llmq_quantize_mx(qb, sfb, db, N, K, K, 0, TN, 0);
+    rc |= llmq_gemm_mx(qa, qb, sfa, sfb, dc, nullptr, M, N, K, K, K, N, 1, 0, 0, 1.f, nullptr, dstatus, g_sms, 0);
+    if (rc) { printf("block-scaled gemm launch failed (%d)\n", rc); ++g_failed; return; }
+    auto c = to_host(dc, static_cast<size_t>(M) * N);
+    auto fa = dequant_mx(to_host(qa, a.size()), to_host(sfa, sfa_bytes), M, K, 128);
+    auto fb = dequant_mx(to_host(qb, b.size()), to_host(sfb, sfb_bytes), N, K, TN);
+    double err = 0, qerr = 0;
+    for (size_t i = 0; i < a.size(); i += 32) {          // every block reproduces its values to e4m3 precision of its own maximum
+        double mx = 0, e = 0;
+        for (int j = 0; j < 32; ++j) { mx = std::fmax(mx, std::fabs(a[i + j])); e = std::fmax(e, std::fabs(a[i + j] - fa[i + j])); }
+        qerr = std::fmax(qerr, mx > 0 ? e / mx : 0.0);
+    }
+    for (int i = 0; i < M; ++i) for (int j = 0; j < N; ++j) {
+        double acc = 0;
+        for (int k = 0; k < K; ++k) acc += static_cast<double>(fa[static_cast<size_t>(i) * K + k]) * fb[static_cast<size_t>(j) * K + k];
+        err = std::fmax(err, std::fabs(c[static_cast<size_t>(i) * N + j] - acc) / (1.0 + std::fabs(acc)));
+    }
+    report("quantize mx (per-block error)", qerr, 0.0626);
+    report("gemm mx e4m3", err, 1e-3);      // fp32 accumulation over blocks whose magnitudes span 2^22
+    report("gemm mx status word", static_cast<double>(to_host(dstatus, 1)[0]), 0.0);
+    cudaFree(da); cudaFree(db); cudaFree(qa); cudaFree(qb); cudaFree(sfa); cudaFree(sfb); cudaFree(dc); cudaFree(dstatus);
+}
 }  // namespace
 
 int main() {
@@ -182,6 +234,7 @@ int main() {
     test_classifier();
     test_gemm(false);
     test_gemm(true);
+    test_gemm_mx();
     CK(cudaDeviceSynchronize());
     printf("%s\n", g_failed ? "SOME TESTS FAILED" : "ALL TESTS PASSED");
     return g_failed ? 1 : 0;

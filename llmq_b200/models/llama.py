@@ -79,7 +79,8 @@ class LlamaModel:
             opts.model_type = cfg.dtype
         self.dtype = opts.model_type
         self.B, self.T = batch_size, seq_len
-        self.quant = opts.matmul_dtype() in F8_TYPES
+        # GEMM operands in their own dtype: fp8 (per-tensor scaled), or bf16 under an fp32 model (mixed precision: scale 1)
+        self.quant = opts.matmul_dtype() in F8_TYPES or (opts.matmul_dtype() == torch.bfloat16 and self.dtype == torch.float32)
         self.qdtype = opts.matmul_dtype()
         self.gdtype = opts.grad_dtype() if self.quant else self.dtype
         # block-scaled e4m3: bf16 plumbing, every block GEMM quantises its operands per 32 elements of its contraction axis

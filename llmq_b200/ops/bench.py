@@ -61,7 +61,7 @@ def _rand(shape, dtype):
 
 
 def bench_gemm(a, tm):
-    dt = {"bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn, "e4m3": torch.float8_e4m3fn}[a.dtype]
+    dt = {"bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn, "e4m3": torch.float8_e4m3fn, "fp32": torch.float32}[a.dtype]
     L.kernels().llmq_gemm_set_mode(a.mode)
     A = _rand((a.k, a.m) if a.a_mn else (a.m, a.k), dt)
     B = _rand((a.k, a.n) if a.b_mn else (a.n, a.k), dt)

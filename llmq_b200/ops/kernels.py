@@ -75,6 +75,18 @@ def check_status(device) -> None:
         raise L.KernelError(f"a device-side wait timed out (status 0x{v:x}); the step result is invalid")
 
 
+_scratch_bufs = {}
+
+
+def _scratch(tag: str, device, shape, dtype) -> torch.Tensor:
+    """Device scratch per (tag, device, shape, dtype), allocated on first use (conversion paths of the fp32 model)."""
+    key = (tag, str(device), tuple(shape), dtype)
+    buf = _scratch_bufs.get(key)
+    if buf is None:
+        buf = _scratch_bufs[key] = torch.empty(tuple(shape), dtype=dtype, device=device)
+    return buf
+
+
 def _ll(v):
     return ctypes.c_longlong(int(v))
 
@@ -105,10 +117,22 @@ def gemm(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = Fa
     K = a.shape[0] if a_mn else a.shape[1]
     assert (a.shape[1] if a_mn else a.shape[0]) == M, (a.shape, out.shape, a_mn)
     assert (b.shape == (K, N)) if b_mn else (b.shape == (N, K)), (b.shape, (N, K), b_mn)
+    if out.is_cuda and a.dtype == torch.float32 and (a_mn or b_mn):
+        # fp32 operands (tf32 MMA kind) are only fed K-major: transpose the other forms into scratch first
+        assert a.is_contiguous() and b.is_contiguous()
+        if a_mn:
+            at = _scratch("gemm_a_T", a.device, (M, K), torch.float32)
+            transpose(at, a)
+            a, a_mn = at, False
+        if b_mn:
+            bt = _scratch("gemm_b_T", b.device, (N, K), torch.float32)
+            transpose(bt, b)
+            b, b_mn = bt, False
     if out.is_cuda:
         st = _dev_state(out.device)
         _bind_splitk(st)
         assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+        assert a.dtype == b.dtype or (_is_f8(a.dtype) and _is_f8(b.dtype)), (a.dtype, b.dtype)
         rflags, rgen, rrows, rlimit = ready if ready is not None else (0, 0, 0, 0.0)
         rc = L.kernels().llmq_gemm_ready(
             L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(bias), M, N, K, L.dtype_code(a.dtype), L.dtype_code(b.dtype),
@@ -740,7 +764,17 @@ def attention_forward(out: torch.Tensor, lse: torch.Tensor, qkv: torch.Tensor, H
     """Causal GQA attention on packed qkv (B,T,Hq+2Hkv,HS): out (B,T,Hq,HS), lse (B,Hq,T) natural log.
     ``absmax`` (optional) is raised to max |out|."""
     B, T, H, HS = qkv.shape
+    if qkv.is_cuda and qkv.dtype == torch.float32:
+        # fp32 model: the tensor-core kernel works on bf16 copies (fp32 softmax statistics and accumulation inside)
+        qh, oh = _attn_half("qkv", qkv), _attn_half("out", out)
+        convert(qh, qkv)
+        attention_forward(oh, lse, qh, Hq, Hkv)
+        convert(out, oh)
+        if absmax is not None:
+            abs_max(absmax, out)
+        return
     if qkv.is_cuda:
+        assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
         L.check(L.kernels().llmq_attention_forward(L.ptr(out), L.ptr(lse), L.ptr(qkv), B, T, Hq, Hkv, HS, L.ptr(absmax),
                                                    L.ptr(status_word(qkv.device)), L.stream_ptr()), "attention_forward")
         return
@@ -749,6 +783,11 @@ def attention_forward(out: torch.Tensor, lse: torch.Tensor, qkv: torch.Tensor, H
     lse.copy_(l)
     if absmax is not None:
         absmax.copy_(torch.maximum(absmax, out.float().abs().max().reshape_as(absmax)))
+
+
+def _attn_half(tag: str, like: torch.Tensor) -> torch.Tensor:
+    """bf16 scratch of the shape of ``like``."""
+    return _scratch("attn_" + tag, like.device, like.shape, torch.bfloat16)
 
 
 def _attention_ref(qkv: torch.Tensor, Hq: int, Hkv: int):
@@ -769,7 +808,16 @@ def attention_backward(dqkv: torch.Tensor, scratch: Optional[torch.Tensor], dout
                        qkv: torch.Tensor, Hq: int, Hkv: int) -> None:
     """Packed gradient of :func:`attention_forward`; ``scratch`` holds B*Hq*T floats."""
     B, T, H, HS = qkv.shape
+    if qkv.is_cuda and qkv.dtype == torch.float32:
+        qh, oh, dh, gh = _attn_half("qkv", qkv), _attn_half("out", out), _attn_half("dout", dout), _attn_half("dqkv", dqkv)
+        convert(qh, qkv)
+        convert(oh, out)
+        convert(dh, dout)
+        attention_backward(gh, scratch, dh, oh, lse, qh, Hq, Hkv)
+        convert(dqkv, gh)
+        return
     if qkv.is_cuda:
+        assert qkv.dtype == torch.bfloat16 and dqkv.dtype == torch.bfloat16
         assert scratch is not None and scratch.numel() >= B * Hq * T
         L.check(L.kernels().llmq_attention_backward(L.ptr(dqkv), L.ptr(scratch), L.ptr(dout), L.ptr(out), L.ptr(lse), L.ptr(qkv), B, T, Hq, Hkv,
                                                     HS, L.ptr(status_word(qkv.device)), L.stream_ptr()), "attention_backward")

@@ -28,6 +28,23 @@ def _check_status():
     K.check_status(torch.device(DEV, 0))
 
 
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 32), (384, 272, 200), (1008, 896, 1024)])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_fp32_operands_tf32(M, N, Kd, a_mn, b_mn, accumulate):
+    """fp32 operands go through the tf32 MMA kind: products carry a 10-bit mantissa, accumulation is fp32."""
+    torch.manual_seed(2)
+    A, Bm, bias = torch.randn(M, Kd), torch.randn(N, Kd), torch.randn(N)
+    prev = torch.randn(M, N)
+    ref = A.double() @ Bm.double().t() + bias.double() + (prev.double() if accumulate else 0)
+    As = A.t().contiguous() if a_mn else A
+    Bs = Bm.t().contiguous() if b_mn else Bm
+    out = prev.clone().to(DEV)
+    K.gemm(out, As.to(DEV), Bs.to(DEV), a_mn=bool(a_mn), b_mn=bool(b_mn), bias=bias.to(DEV), accumulate=accumulate)
+    err = (out.cpu().double() - ref).abs().max().item()
+    assert err <= 2e-3 * (A.abs().max() * Bm.abs().max()).item() * Kd ** 0.5, err
+
+
 @pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (384, 272, 192), (1008, 896, 1024)])
 @pytest.mark.parametrize("dt", ["bf16", "fp8"])
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])

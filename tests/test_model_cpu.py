@@ -148,3 +148,21 @@ def test_validate_and_bf16():
     m.backward(x[0], y[0], 0.0, 1, 0)
     r = m.update(lr=1e-3, step=1)
     assert abs(r["loss"] - loss) < 5e-2 and r["norm"] > 0
+
+
+def test_fp32_model_with_bf16_matmuls_tracks_fp32():
+    """Mixed precision: fp32 weights / activations, GEMM operands rounded to bf16 (``--model-dtype fp32 --matmul-dtype bf16``)."""
+    _, m32 = make()
+    _, mx = make(LLamaOptions(matmul_type="bf16"))
+    assert mx.quant and mx.qdtype == torch.bfloat16 and mx.dtype == torch.float32
+    x, y = data(7)
+    for m in (m32, mx):
+        m.forward(x[0])
+        m.backward(x[0], y[0], 0.0, 1, 0)
+    r32, rx = m32.update(lr=0.0, step=1), mx.update(lr=0.0, step=1)
+    assert abs(r32["loss"] - rx["loss"]) < 2e-3
+    g32, gx = m32.get_gradients(), mx.get_gradients()
+    for n in g32:
+        a, b = g32[n].flatten().float(), gx[n].flatten().float()
+        if a.norm() > 0:
+            assert torch.dot(a, b) / (a.norm() * b.norm() + 1e-12) > 0.999, n

@@ -68,6 +68,40 @@ def test_step_matches_oracle(mm, hs, tied):
     assert sum(rel) / len(rel) < 0.05
 
 
+@pytest.mark.parametrize("mm", [None, "bf16"])
+def test_fp32_model_matches_oracle(mm):
+    """--model-dtype fp32 on the GPU: tf32 tensor-core GEMMs on fp32 operands (or bf16 GEMM operands with ``matmul_type=bf16``,
+    the mixed-precision variant), bf16 copies inside attention, everything else in fp32."""
+    cfg = cfg_small(True, 64).replace(dtype=torch.float32)
+    m = LlamaModel(cfg, LLamaOptions(matmul_type=mm), device="cuda:0", batch_size=B, seq_len=T)
+    assert m.dtype == torch.float32 and m.quant == (mm == "bf16")
+    m.init_weights(0)
+    ref_p = {n: t.detach().float().cpu().clone().requires_grad_(True) for n, t, _, _ in m.weights.master_items()}
+    x, y = data(1, 1)
+    loss, ce = loss_ref(cfg, ref_p, x[0], y[0])
+    loss.backward()
+    m.forward(x[0])
+    m.backward(x[0], y[0], 0.0, 1, 0)
+    got = m.get_gradients()
+    r = m.update(lr=0.0, step=1)
+    K.check_status(torch.device("cuda:0"))
+    assert abs(r["loss"] - ce.item()) < 5e-3, (r, ce.item())
+    cos = []
+    for n, g in got.items():
+        assert g.dtype == torch.float32
+        a, b = g.float().cpu().flatten(), ref_p[n].grad.flatten()
+        if b.norm() > 0:
+            cos.append((torch.dot(a, b) / (a.norm() * b.norm() + 1e-12)).item())
+    assert min(cos) > 0.99 and sum(cos) / len(cos) > 0.999, cos
+    # and it trains
+    first = r["loss"]
+    for s in range(2, 5):
+        m.forward(x[0])
+        m.backward(x[0], y[0], 0.0, 1, 0)
+        r = m.update(lr=1e-3, step=s)
+    assert r["loss"] < first
+
+
 @pytest.mark.parametrize("mm", [None, "e4m3"])
 @pytest.mark.parametrize("kw", [dict(recompute_swiglu=True), dict(recompute_block=True), dict(recompute_att=True, recompute_ffn=True),
                                 dict(recompute_rms_norm=True, recompute_qkv=True), dict(shard_weights=True, shard_gradients=True),

@@ -73,6 +73,11 @@ def test_block_scaled_model_step_matches_cpu_path():
     x, y = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
     kw = dict(heads=(4, 2), hidden=256, ffn=512, B=2, T=128)
     models = [_tiny_model(True, "cpu", **kw), _tiny_model(True, DEV, **kw)]
+    # the normal-init streams of the two devices differ: give both models the same weights
+    for (n0, w0, _, _), (n1, w1, _, _) in zip(models[0].weights.master_items(), models[1].weights.master_items()):
+        assert n0 == n1
+        w0.copy_(w1.cpu())
+    models[0].on_weights_changed()
     res = []
     for m in models:
         m.forward(x)
