@@ -99,9 +99,9 @@ class LlamaModel:
             raise ValueError("sequence length exceeds max_position_embeddings")
         self.fused = self._make_fused()
         self._marks: List = []
-        # (the block-scaled path shares one pair of operand buffers between all GEMMs, so it stays on one stream)
         self._dw_stream = (torch.cuda.Stream(self.device, priority=-1)
-                           if (opts.overlap_dw and self.device.type == "cuda" and not self.mx) else None)
+                           if (opts.overlap_dw and self.device.type == "cuda") else None)
+        self._mx_dw_event = None                  # block-scaled path: last weight-gradient GEMM that reads the shared operand buffers
         self._dw_events: List = []
         # SwiGLU inside the epilogues of the up-projection GEMM and of the down-projection's dX GEMM
         self._fuse_swiglu = (opts.fuse_swiglu and not self.mx and self.device.type == "cuda" and self.dtype == torch.bfloat16
@@ -224,6 +224,8 @@ class LlamaModel:
             t.mx_a_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_A) for r, k in a_uses), dtype=torch.uint8, device=dev)
             t.mx_a2_q = torch.zeros(BT * feat, dtype=torch.float8_e4m3fn, device=dev)       # column form of an output gradient
             t.mx_a2_sf = torch.zeros_like(t.mx_a_sf)
+            t.mx_b2_q = torch.zeros(BT * max(C, D), dtype=torch.float8_e4m3fn, device=dev)  # transposed layer input (second stream)
+            t.mx_b2_sf = torch.zeros(max(K.mx_sf_bytes(r, BT, K.MX_TILE_B) for r in (C, D)), dtype=torch.uint8, device=dev)
             t.mx_b_q = torch.zeros(max(r * k for r, k in b_uses), dtype=torch.float8_e4m3fn, device=dev)
             t.mx_b_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_B) for r, k in b_uses), dtype=torch.uint8, device=dev)
         self.tmp = t
@@ -320,6 +322,9 @@ class LlamaModel:
             d2 = dout.reshape(-1, dout.shape[-1])
             BT, OC = d2.shape
             d_rows, d_cols = t.mx_a_q[:BT * OC].view(BT, OC), t.mx_a2_q[:BT * OC].view(OC, BT)
+            # d_cols and the transposed input are read by the weight-gradient GEMM on the second stream: the previous one
+            # must have finished with those buffers before they are rewritten
+            self._wait_dw(self._mx_dw_event)
             if dinp is not None:
                 K.quantize_mx_both(d2, q_rows=d_rows, sf_rows=t.mx_a_sf, q_cols=d_cols, sf_cols=t.mx_a2_sf)
                 wq = t.mx_b_q[:W.numel()].view(W.shape[1], W.shape[0])
@@ -328,9 +333,12 @@ class LlamaModel:
             else:
                 K.quantize_mx(d2, transpose=True, operand="a", q_out=d_cols, sf_out=t.mx_a2_sf)
             i2 = inp.reshape(BT, -1)
-            iq = t.mx_b_q[:i2.numel()].view(i2.shape[1], BT)
-            K.quantize_mx(i2, transpose=True, operand="b", q_out=iq, sf_out=t.mx_b_sf)
-            K.gemm_mx(dW, d_cols, t.mx_a2_sf, iq, t.mx_b_sf, accumulate=accumulate)
+            iq = t.mx_b2_q[:i2.numel()].view(i2.shape[1], BT)
+
+            def dw():
+                K.quantize_mx(i2, transpose=True, operand="b", q_out=iq, sf_out=t.mx_b2_sf)
+                K.gemm_mx(dW, d_cols, t.mx_a2_sf, iq, t.mx_b2_sf, accumulate=accumulate)
+            self._mx_dw_event = self._launch_dw(dw)
             if dbias is not None:
                 K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
             return
@@ -393,6 +401,7 @@ class LlamaModel:
         for e in self._dw_events:
             main.wait_event(e)
         self._dw_events = []
+        self._mx_dw_event = None
 
     # ================================================================================== forward
     def forward(self, inputs: torch.Tensor, micro_step: int = 0) -> None:
