@@ -123,6 +123,11 @@ class LlamaModel:
         """In-kernel NVLink collectives when asked for ("fused") or possible ("auto"): several ranks, one per process,
         CUDA devices with symmetric-memory support.  "nccl" keeps the library collectives."""
         mode = self.opts.collectives
+        if self.dtype == torch.float32 and self.comm.world > 1 and mode != "nccl":
+            # the peer-memory kernels move bf16 / fp8 tensors; fp32 models use the library collectives
+            if mode == "fused":
+                raise RuntimeError("fused collectives are not available for fp32 models; use collectives='nccl'")
+            return None
         if mode == "nccl" or self.comm.world == 1 or self.device.type != "cuda" or not hasattr(self.comm, "dist"):
             if mode == "fused" and self.comm.world > 1:
                 raise RuntimeError("fused collectives need one CUDA rank per process (torch.distributed / NCCL plumbing)")
