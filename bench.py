@@ -86,6 +86,7 @@ def main():
     ap.add_argument("--collectives", default="auto")
     ap.add_argument("--recompute", default="swiglu", choices=["none", "swiglu", "block"], help="headline config: swiglu")
     ap.add_argument("--offload-master", action="store_true")
+    ap.add_argument("--offload-opt", action="store_true", help="Adam moments in pinned host memory (the 14B configuration)")
     ap.add_argument("--fuse-swiglu", type=int, default=None)
     ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--cuda-graphs", type=int, default=-1,
@@ -117,6 +118,7 @@ def main():
         opts.overlap_dw = bool(args.overlap_dw)
     zl = args.zero_level or (1 if args.gpus == 1 else 3)
     opts.set_zero_level(zl)
+    opts.offload_opt_m = opts.offload_opt_v = args.offload_opt
     B, T, GA = args.batch, args.seq_len, args.grad_accum
     trainer = api.LLMQTrainer(ngpu=args.gpus, config=cfg, options=opts, batch_size=B, seq_len=T, grad_accum=GA)
     trainer.init_weights()
@@ -196,6 +198,7 @@ def main():
                        "seq_len": T, "per_gpu_batch": B, "grad_accum": GA,
                        "parallelism": f"dp{comm.world}" + ("" if comm.world == 1 else f"-zero{zl}"), "recompute": args.recompute,
                        "opt_moments": "bf16", "lmhead_chunks": args.lmhead_chunks,
+                       "offload": [n for n, on in (("master", args.offload_master), ("adam_m", args.offload_opt), ("adam_v", args.offload_opt)) if on],
                        "l2": "every step streams >60 GB of weights+activations (>> 126 MB L2), no flush needed"},
             "clocks": sampler.summary(),
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": 2 * B * T * 4 * GA,

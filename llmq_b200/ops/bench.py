@@ -200,9 +200,74 @@ def bench_p2p(a, tm):
     print(json.dumps({"op": "p2p_single_gpu_emulation", "world": w, "elements": rows * cols, **out}))
 
 
+def bench_fused_gemm(a, tm):
+    """The two GEMMs that carry a collective, with every "rank" on this one GPU (rank 0 runs, the peer tables point at
+    local buffers, the peers' arrivals are booked in advance), against the plain GEMM of the same shape:
+
+    * GEMM -> reduce-scatter (weight gradient, both operands MN-major): the epilogue stores every row block into its
+      owner's landing buffer and bumps the owner's counter; the tail sums this rank's slots into the shard.
+    * all-gather -> GEMM (first consumer of gathered weights): the TMA producer polls one arrival flag per source
+      rank before it loads that rank's rows of B.
+
+    What the numbers show is what the collective part costs inside the kernel; no byte crosses NVLink here."""
+    import ctypes
+    dev = torch.device(DEV, torch.cuda.current_device())
+    st = K._dev_state(dev)
+    k = L.kernels()
+    w = a.world
+    peak, _, src = _peaks()
+    f8 = torch.float8_e4m3fn
+    out = {"op": "fused_gemm_single_gpu_emulation", "world": w}
+    # ---- dW = dY^T @ X, reduce-scattered over rows
+    M, N, Kd = a.m, a.n, a.k
+    At, Bt = _rand((Kd, M), f8), _rand((Kd, N), f8)
+    ones = torch.ones(1, device=DEV)
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ms_plain = tm.time(lambda: K.gemm(plain, At, Bt, a_mn=True, b_mn=True, scale_a=ones, scale_b=ones))
+    landing = [torch.zeros(w, M // w, N, dtype=torch.bfloat16, device=DEV) for _ in range(w)]
+    counters = torch.zeros(w, 64, dtype=torch.int32, device=DEV)               # one counter per "rank", 256 bytes apart
+    shard = torch.zeros(M // w, N, dtype=torch.bfloat16, device=DEV)
+    parts = torch.zeros(K.NORM_PARTIALS, device=DEV)
+    land_arr = (ctypes.c_void_p * 8)(*([t.data_ptr() for t in landing] + [0] * (8 - w)))
+    cnt_arr = (ctypes.c_void_p * 8)(*([counters[i].data_ptr() for i in range(w)] + [0] * (8 - w)))
+    arrivals = int(k.llmq_gemm_rs_arrivals(M, N, w))
+    state = {"target": 0}
+
+    def run_rs():
+        # the other ranks' share of the arrivals at rank 0 is booked before the launch
+        state["target"] += arrivals
+        counters[0, 0] += arrivals - arrivals // w
+        L.check(k.llmq_gemm_rs(L.ptr(At), L.ptr(Bt), L.ptr(landing[0]), M, N, Kd, 1, 1, 1, 1, ctypes.c_longlong(M), ctypes.c_longlong(N), 0,
+                               L.ptr(ones), L.ptr(ones), ctypes.c_float(1.0), L.ptr(st["status"]), st["sms"], land_arr, cnt_arr, 0, w,
+                               ctypes.c_uint(state["target"] & 0xFFFFFFFF), L.ptr(shard), 0, ctypes.c_float(1.0), L.ptr(parts), K.NORM_PARTIALS,
+                               ctypes.c_uint(5), ctypes.c_double(2.0), L.stream_ptr()), "gemm_rs")
+
+    ms_rs = tm.time(run_rs)
+    err = (shard.float() - plain[: M // w].float()).abs().max().item()
+    tf = 2.0 * M * N * Kd / 1e9
+    out["gemm_rs"] = {"m": M, "n": N, "k": Kd, "ms": round(ms_rs, 4), "tflops": round(tf / ms_rs, 1), "plain_gemm_ms": round(ms_plain, 4),
+                      "plain_tflops": round(tf / ms_plain, 1), "max_abs_diff_vs_plain": err,
+                      "nvlink_bytes_per_rank": M * N * 2 * (w - 1) // w, "nvlink_ms_at_770GBs": round(M * N * 2 * (w - 1) / w / 770e6, 4)}
+    del landing, plain
+    # ---- Y = X @ W^T with the rows of W arriving from `w` sources
+    M2, N2, K2 = a.rows, a.n2, a.c
+    X, W = _rand((M2, K2), f8), _rand((N2, K2), f8)
+    Y = torch.empty(M2, N2, dtype=torch.bfloat16, device=DEV)
+    flags = torch.full((8,), 3, dtype=torch.int32, device=DEV)
+    ms0 = tm.time(lambda: K.gemm(Y, X, W, scale_a=ones, scale_b=ones))
+    ms1 = tm.time(lambda: K.gemm(Y, X, W, scale_a=ones, scale_b=ones, ready=(flags.data_ptr(), 3, N2 // w, 2.0)))
+    tf2 = 2.0 * M2 * N2 * K2 / 1e9
+    out["gemm_ready"] = {"m": M2, "n": N2, "k": K2, "ms": round(ms1, 4), "tflops": round(tf2 / ms1, 1), "plain_gemm_ms": round(ms0, 4),
+                         "plain_tflops": round(tf2 / ms0, 1), "nvlink_bytes_per_rank": N2 * K2 * (w - 1) // w,
+                         "nvlink_ms_at_770GBs": round(N2 * K2 * (w - 1) / w / 770e6, 4)}
+    out[f"{src}_bf16_peak_tflops"] = peak
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "gemm_mx", "attention", "elementwise", "adamw", "p2p"])
+    ap.add_argument("op", choices=["gemm", "gemm_mx", "attention", "elementwise", "adamw", "p2p", "fused_gemm"])
+    ap.add_argument("--n2", type=int, default=4608, help="fused_gemm: output columns of the all-gather -> GEMM case (QKV projection)")
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -227,7 +292,8 @@ def main():
     ap.add_argument("--numel", type=int, default=1 << 28)
     a = ap.parse_args()
     tm = Timer(a.iters, a.warmup, not a.no_flush)
-    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw, "p2p": bench_p2p}[a.op](a, tm)
+    {"gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "attention": bench_attention, "elementwise": bench_elementwise, "adamw": bench_adamw, "p2p": bench_p2p,
+     "fused_gemm": bench_fused_gemm}[a.op](a, tm)
 
 
 if __name__ == "__main__":
