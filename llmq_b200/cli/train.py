@@ -131,7 +131,8 @@ def run_training(cfg: TrainingConfig, argv=None) -> dict:
     step_tokens = B * T * GA * world
     steps = cfg.steps if cfg.steps > 0 else max(1, cfg.epochs * (train_loader.num_tokens // step_tokens))
 
-    logger = TrainingRunLogger(cfg.log_file, verbosity=cfg.verbosity, rank=rank, final_step=steps)
+    logger = TrainingRunLogger(cfg.log_file, callback=_wandb_callback(cfg) if (cfg.use_wandb and rank == 0) else None,
+                               verbosity=cfg.verbosity, rank=rank, final_step=steps)
     logger.log_cmd(argv if argv is not None else sys.argv)
     logger.log_options({k: v for k, v in vars(cfg).items()})
     if trainer.device.type == "cuda":
@@ -233,6 +234,28 @@ def run_training(cfg: TrainingConfig, argv=None) -> dict:
 def _child(rank: int, world: int, port: int, cfg: TrainingConfig, argv):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     run_training(cfg, argv)
+
+
+def _wandb_callback(cfg, wandb=None):
+    """Live export (``--use-wandb``): every log line goes to a Weights & Biases run as it is written, with the same
+    mapping as the offline exporter (role of ``make_wandb_log_callback`` in the reference's binding/python/training.py)."""
+    from ..scripts.export_wandb import log_line_to_metrics
+    if wandb is None:
+        try:
+            import wandb
+        except ImportError as e:
+            raise RuntimeError("--use-wandb needs the wandb package; export the log file later with pyllmq-export-wandb instead") from e
+    run = wandb.init(project=cfg.wandb_project, name=cfg.wandb_name or cfg.name)
+
+    def on_line(obj: dict) -> None:
+        if obj.get("log") == "option":
+            run.config.update({obj.get("name", "option"): obj.get("value")}, allow_val_change=True)
+            return
+        got = log_line_to_metrics(obj)
+        if got:
+            run.log({k: v for k, v in got[1].items() if v is not None}, step=got[0])
+
+    return on_line
 
 
 def main(argv=None) -> int:

@@ -67,6 +67,9 @@ class TrainingConfig:
     new_data: bool = False
     log_gpu_util: int = 25
     verbosity: int = 0
+    use_wandb: bool = False
+    wandb_project: str = "LLMQ"
+    wandb_name: str = ""
     # recompute
     recompute_swiglu: bool = False
     recompute_norm: bool = False
@@ -200,6 +203,12 @@ def add_training_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     flag("--new-data", dest="new_data", help="do not restore the data-loader position")
     g.add_argument("--log-gpu-util", type=int, default=d.log_gpu_util)
     g.add_argument("--verbosity", type=int, default=d.verbosity)
+    g.add_argument("-qq", "--silent", dest="verbosity", action="store_const", const=-2, help="no console output")
+    g.add_argument("-q", "--quiet", dest="verbosity", action="store_const", const=-1, help="minimal console output")
+    g.add_argument("-v", "--verbose", dest="verbosity", action="store_const", const=1, help="detailed console output")
+    flag("--use-wandb", dest="use_wandb", help="send every log line to Weights & Biases while training (needs the wandb package)")
+    g.add_argument("--wandb-project", default=d.wandb_project)
+    g.add_argument("--wandb-name", default=d.wandb_name, help="run name (default: --name)")
     g = p.add_argument_group("recompute")
     for n in ("swiglu", "norm", "ffn", "qkv", "att", "block"):
         flag(f"--recompute-{n}", dest=f"recompute_{n}")
@@ -214,6 +223,7 @@ def add_training_args(p: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g = p.add_argument_group("offload")
     for n in ("master", "opt-m", "opt-v", "gradients", "quants"):
         flag(f"--offload-{n}", dest="offload_" + n.replace("-", "_"))
+    flag("--offload-grads", dest="offload_gradients", help="same as --offload-gradients")
     flag("--persistent-quants", dest="persistent_quants")
     flag("--use-zero-copy", dest="use_zero_copy")
     flag("--write-combined", dest="write_combined")

@@ -78,3 +78,43 @@ def test_train_resume_and_export(tmp_path):
     assert sorted(a.names()) == sorted(b.names())
     for n in a.names():
         assert torch.equal(a.read(n), b.read(n)), n
+
+
+def test_python_front_end_flags_and_wandb_callback():
+    """Flags of the reference's Python front end (``binding/python/training.py:183-197``): ``--offload-grads``, the
+    ``-q / -qq / -v`` verbosity shortcuts and live Weights & Biases logging, checked against a stand-in for wandb."""
+    cfg = parse_training_config(["--from-scratch", "--synthetic-data", "--offload-grads", "-qq", "--use-wandb", "--wandb-project", "P",
+                                 "--name", "r1"])
+    assert cfg.offload_gradients and cfg.verbosity == -2 and cfg.use_wandb and cfg.wandb_project == "P"
+    assert parse_training_config(["-q"]).verbosity == -1 and parse_training_config(["-v"]).verbosity == 1
+
+    class Run:
+        def __init__(self):
+            self.logged, self.config = [], {}
+
+        def log(self, metrics, step=None):
+            self.logged.append((step, metrics))
+
+    class Config(dict):
+        def update(self, d, allow_val_change=False):
+            super().update(d)
+
+    class FakeWandb:
+        def __init__(self):
+            self.run = Run()
+            self.run.config = Config()
+
+        def init(self, project=None, name=None):
+            self.args = (project, name)
+            return self.run
+
+    w = FakeWandb()
+    cb = train._wandb_callback(cfg, wandb=w)
+    assert w.args == ("P", "r1")
+    cb({"log": "option", "name": "lr", "value": 1e-3})
+    cb({"log": "step", "step": 4, "step_tokens": 2048, "duration_ms": 10.0, "loss": 3.0, "norm": 1.0, "lr": 1e-3})
+    cb({"log": "cmd", "argv": []})
+    assert w.run.config["lr"] == 1e-3 and len(w.run.logged) == 1
+    step, metrics = w.run.logged[0]
+    assert step == 4 and metrics["train/loss"] == 3.0 and metrics["train/tokens_per_second"] == pytest.approx(204800.0)
+    assert all(v is not None for v in metrics.values())

@@ -133,3 +133,40 @@ def test_gpu_tracker_against_fake_nvml(monkeypatch):
         assert set_cpu_affinity(0, nvml=fake) in (True, False)
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_tokenize_named_dataset(tmp_path):
+    """``--dataset``: the named presets with an injected loader and tokenizer (no hub, no network)."""
+    class Tok:
+        eos_token_id, bos_token_id = 1, None
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [3 + (ord(c) % 50) for c in text]}
+
+        def __len__(self):
+            return 64
+
+    calls = []
+
+    def fake_load(*hub, **kw):
+        calls.append((hub, kw))
+        if hub[0] == "openai/gsm8k":
+            rows = [{"question": "q%d" % i, "answer": "a%d" % i} for i in range(6)]
+            return {"train": rows, "test": rows[:2]}
+        return {"train": ({"text": "doc %03d " % i * 5} for i in range(40))}
+
+    files = tokenize_data.generate_tokenized_dataset("gsm8k", "qwen", str(tmp_path), load_dataset=fake_load, tokenizer=Tok())
+    assert [os.path.relpath(f, tmp_path) for f in files] == ["gsm8k-qwen/train.bin", "gsm8k-qwen/eval.bin"]
+    assert DataLoader(files[:1], 512).num_tokens == 6 * 512 and DataLoader(files[1:], 512).num_tokens == 2 * 512    # padded to the preset's 512
+    assert calls[0] == (("openai/gsm8k", "main"), {})
+    spec = dict(tokenize_data.DATASETS["fineweb-1b"], eval=100, subsample=900)
+    tokenize_data.DATASETS["unit-stream"] = spec
+    try:
+        files = tokenize_data.generate_tokenized_dataset("unit-stream", "llama", str(tmp_path), load_dataset=fake_load, tokenizer=Tok())
+    finally:
+        del tokenize_data.DATASETS["unit-stream"]
+    assert os.path.basename(files[0]) == "eval.bin" and os.path.basename(files[1]) == "train-000.bin" and calls[1][1] == {"streaming": True}
+    n_eval, n_train = DataLoader(files[:1], 8).num_tokens, DataLoader(files[1:], 8).num_tokens
+    assert 0 < n_eval <= 100 and 900 <= n_eval + n_train < 900 + 41
+    with pytest.raises(ValueError):
+        tokenize_data.generate_tokenized_dataset("nope", "qwen", str(tmp_path), load_dataset=fake_load, tokenizer=Tok())
