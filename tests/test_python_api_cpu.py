@@ -1,5 +1,6 @@
 """The pyllmq-compatible import package and the torch custom-op kernel API, on CPU tensors (PyTorch reference paths)."""
 import numpy as np
+import pytest
 import torch
 
 import llmq_b200.kernels_api as ops
@@ -68,3 +69,23 @@ def test_block_scaled_custom_ops():
     torch.ops.llmq_b200.matmul_mx(c, aq, asf, bq, bsf, None, None, False)
     ref = a.float() @ b.float().t()
     assert (c - ref).norm() / ref.norm() < 0.05
+
+
+def test_reference_matmul_signature():
+    """``pyllmq.kernels.matmul`` with the reference's argument list (handle, workspace, integer transpose mode)."""
+    import pyllmq.kernels as pk
+    h = pk.create_cublas_handle()
+    g = torch.Generator().manual_seed(0)
+    A, Bm = torch.randn(6, 10, generator=g), torch.randn(10, 4, generator=g)     # c = A @ Bm
+    bias, ws = torch.randn(4, generator=g), torch.empty(16)
+    forms = {pk.MM_NN: (A, Bm), pk.MM_TN: (A.t().contiguous(), Bm), pk.MM_NT: (A, Bm.t().contiguous()),
+             pk.MM_TT: (A.t().contiguous(), Bm.t().contiguous())}
+    for mode, (a, b) in forms.items():
+        c = torch.zeros(6, 4)
+        pk.matmul(c, a, b, bias, None, None, h, ws, mode)
+        assert torch.allclose(c, A @ Bm + bias, atol=1e-5), mode
+        pk.matmul(c, a, b, None, None, None, h, ws, mode, True)
+        assert torch.allclose(c, 2 * (A @ Bm) + bias, atol=1e-5), mode
+    with pytest.raises(ValueError):
+        pk.matmul(torch.zeros(6, 4), A, Bm, None, None, None, h, ws, 7)
+    pk.destroy_cublas_handle(h)
