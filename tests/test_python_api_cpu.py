@@ -89,3 +89,46 @@ def test_reference_matmul_signature():
     with pytest.raises(ValueError):
         pk.matmul(torch.zeros(6, 4), A, Bm, None, None, None, h, ws, 7)
     pk.destroy_cublas_handle(h)
+
+
+def test_reference_argument_lists():
+    """The calls of ``pyllmq.kernels`` that take the reference's extra arguments (handles, workspaces, bucket tables)
+    give what the plain ops give."""
+    import pyllmq.kernels as pk
+    g = torch.Generator().manual_seed(3)
+    B, T, C, V, Hq, Hkv, HS = 2, 16, 32, 50, 4, 2, 8
+    tok = torch.randint(0, V, (B, T), generator=g, dtype=torch.int32)
+    wte, wpe = torch.randn(V, C, generator=g), torch.randn(T, C, generator=g)
+    out = torch.empty(B, T, C)
+    pk.encoder_forward(out, tok, wte, wpe)
+    assert torch.allclose(out, wte[tok.long()] + wpe)
+    dout = torch.randn(B, T, C, generator=g)
+    d1, d2 = torch.zeros(V, C), torch.zeros(V, C)
+    pk.encoder_backward(d1, None, None, None, dout, tok, tok.clone(), 5)
+    ops.encoder_backward(d2, dout, tok)
+    assert torch.equal(d1, d2) and d1.abs().sum() > 0
+    # RMSNorm backward with a separate residual gradient
+    x, w = torch.randn(B, T, C, generator=g), torch.randn(C, generator=g)
+    y, rstd = torch.empty_like(x), torch.empty(B * T)
+    ops.rmsnorm_forward(y, rstd, x, w, None, 1e-6)
+    dres = torch.randn(B, T, C, generator=g)
+    scratch = torch.empty(ops.get_rmsnorm_backward_scratch_size(C, "cpu") // 4)
+    a, dwa = torch.full_like(x, 7.0), torch.zeros(C)
+    pk.rmsnorm_backward(a, dwa, scratch, dres, dout, x, w, rstd, None)
+    b, dwb = dres.clone(), torch.zeros(C)
+    ops.rmsnorm_backward(b, dwb, scratch, dout, x, w, rstd, None)
+    assert torch.equal(a, b) and torch.equal(dwa, dwb)
+    # attention with workspace / handle arguments
+    qkv = torch.randn(B, T, Hq + 2 * Hkv, HS, generator=g)
+    o1, s1, o2, s2 = torch.empty(B, T, Hq, HS), torch.empty(B, Hq, T), torch.empty(B, T, Hq, HS), torch.empty(B, Hq, T)
+    ws = torch.empty(4 * B * Hq * T, dtype=torch.uint8)
+    pk.attention_forward(o1, s1, qkv, ws, 0, Hq, Hkv)
+    ops.attention_forward(o2, s2, qkv, Hq, Hkv)
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    do = torch.randn(B, T, Hq, HS, generator=g)
+    g1, g2 = torch.empty_like(qkv), torch.empty_like(qkv)
+    pk.attention_backward(g1, s1, o1, do, qkv, ws, 0, Hq, Hkv)
+    ops.attention_backward(g2, torch.empty(B * Hq * T), s2, o2, do, qkv, Hq, Hkv)
+    assert torch.equal(g1, g2)
+    pk.attention_backward(g1, s1, o1, do, qkv, None, 0, Hq, Hkv)                 # no workspace: scratch is allocated
+    assert torch.equal(g1, g2)
