@@ -132,3 +132,32 @@ def test_reference_argument_lists():
     assert torch.equal(g1, g2)
     pk.attention_backward(g1, s1, o1, do, qkv, None, 0, Hq, Hkv)                 # no workspace: scratch is allocated
     assert torch.equal(g1, g2)
+
+
+def test_fixed_reference_ten_steps():
+    """Regression guard in the manner of the reference's fixed-reference runs (``scripts/modal_test_app.py:101-143``
+    there): ten optimizer steps of the tiny Qwen2 model on seeded tokens against stored loss / gradient-norm values.
+    The stored numbers are CPU fp32, so the comparison has a small tolerance instead of exact equality; two runs in
+    one process must agree exactly."""
+    from llmq_b200.config import create_config_from_name
+    want = [(6.257861, 0.812518), (6.236615, 0.778743), (6.267263, 0.797388), (6.280034, 0.81367), (6.263968, 0.810399),
+            (6.239417, 0.801177), (6.256784, 0.792924), (6.239585, 0.784477), (6.253052, 0.783787), (6.251751, 0.805303)]
+
+    def run():
+        tr = pyllmq.LLMQTrainer(ngpu=1, config=create_config_from_name("tiny-qwen2", torch.float32), options=pyllmq.LLamaOptions(),
+                                batch_size=2, seq_len=64, grad_accum=2, device="cpu")
+        tr.init_weights()
+        rng = np.random.default_rng(42)
+        out = []
+        for step in range(10):
+            for _ in range(2):
+                tok = rng.integers(0, 512, size=(2, 65), dtype=np.int32)
+                tr.step(np.ascontiguousarray(tok[:, :-1]), np.ascontiguousarray(tok[:, 1:]))
+            r = tr.update(1e-3, 0.9, 0.95, step + 1, 0.1, 1.0)
+            out.append((r["loss"], r["norm"]))
+        return out
+
+    a, b = run(), run()
+    assert a == b
+    for (l, n), (wl, wn) in zip(a, want):
+        assert abs(l - wl) < 5e-4 and abs(n - wn) < 5e-4, (a, want)
