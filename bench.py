@@ -87,6 +87,8 @@ def main():
     ap.add_argument("--recompute", default="swiglu", choices=["none", "swiglu", "block"], help="headline config: swiglu")
     ap.add_argument("--offload-master", action="store_true")
     ap.add_argument("--offload-opt", action="store_true", help="Adam moments in pinned host memory (the 14B configuration)")
+    ap.add_argument("--persistent-quants", action="store_true",
+                    help="ZeRO-3: keep the quantised weight shards on the device for the whole optimizer step (master weights are read once)")
     ap.add_argument("--fuse-swiglu", type=int, default=None)
     ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--cuda-graphs", type=int, default=-1,
@@ -119,6 +121,7 @@ def main():
     zl = args.zero_level or (1 if args.gpus == 1 else 3)
     opts.set_zero_level(zl)
     opts.offload_opt_m = opts.offload_opt_v = args.offload_opt
+    opts.persistent_quants = args.persistent_quants
     B, T, GA = args.batch, args.seq_len, args.grad_accum
     trainer = api.LLMQTrainer(ngpu=args.gpus, config=cfg, options=opts, batch_size=B, seq_len=T, grad_accum=GA)
     trainer.init_weights()
@@ -199,6 +202,7 @@ def main():
                        "parallelism": f"dp{comm.world}" + ("" if comm.world == 1 else f"-zero{zl}"), "recompute": args.recompute,
                        "opt_moments": "bf16", "lmhead_chunks": args.lmhead_chunks,
                        "offload": [n for n, on in (("master", args.offload_master), ("adam_m", args.offload_opt), ("adam_v", args.offload_opt)) if on],
+                       "persistent_quants": args.persistent_quants,
                        "l2": "every step streams >60 GB of weights+activations (>> 126 MB L2), no flush needed"},
             "clocks": sampler.summary(),
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": 2 * B * T * 4 * GA,

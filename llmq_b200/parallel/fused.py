@@ -136,6 +136,16 @@ class FusedCollectives:
                                                      self.rank, self.world, L.ptr(absmax), L.ptr(scale_out), 1 if quant else 0, self.sms,
                                                      L.stream_ptr()), "p2p_quant_allgather")
 
+    def push_allgather(self, full: torch.Tensor, shard: torch.Tensor) -> None:
+        """Stores this rank's shard, which already has ``full``'s dtype (e.g. a kept e4m3 shard, on the device or in
+        pinned host memory), into its slot of ``full`` on every rank: the copy form of the kernel on the raw bytes."""
+        seg, off = self.heap.locate(full)
+        nbytes = shard.numel() * shard.element_size()
+        if shard.dtype != full.dtype or nbytes % 16 or not shard.is_contiguous():
+            raise TypeError("push all-gather takes a contiguous shard of the destination's dtype, a multiple of 16 bytes")
+        L.check(L.kernels().llmq_p2p_quant_allgather(seg.peer_array, ctypes.c_longlong(off), L.ptr(shard), ctypes.c_longlong(nbytes // 2),
+                                                     self.rank, self.world, None, None, 0, self.sms, L.stream_ptr()), "p2p_quant_allgather")
+
     def reduce_scatter(self, full: torch.Tensor, dst: torch.Tensor, *, accumulate: bool, scale: float,
                        norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
         """dst (+)= scale * sum over ranks of rows [rank*n/w, (rank+1)*n/w) of ``full`` (bf16, in the heap)."""

@@ -245,9 +245,17 @@ class WeightsManager:
                     master = self.master_blocks[l][s.name]
                     if self.quantized:
                         st = self._stat(l, s.name)
-                        f.quant_allgather(full, master, st[0:1], st[1:2])
+                        q = self.quant_shards[l][s.name] if self.quant_shards is not None else None
+                        if q is not None and self.quant_version[l] == self.version:
+                            f.push_allgather(full, q)                    # kept e4m3 shard: the master is not read again
+                        else:
+                            f.quant_allgather(full, master, st[0:1], st[1:2])
+                            if q is not None:
+                                q.copy_(self.comm.local_shard(full), non_blocking=True)      # own slot, as just pushed
                     else:
                         f.quant_allgather(full, master)
+            if self.quant_shards is not None:
+                self.quant_version[l] = self.version
             gen_mat = f.signal(ch_mat)
             ev = torch.cuda.Event()
             ev.record(f.stream)

@@ -36,13 +36,17 @@ def _worker(rank, world, port, q):
         results = {}
         runs = [(zero, ga, mode) for zero, ga in CASES for mode in ("nccl", "fused", "fused+gemm_rs")]
         runs += [(3, 2, "mx-nccl"), (3, 2, "mx-fused")]          # block-scaled e4m3 matmuls on sharded bf16 weights
+        runs += [(3, 2, "pq-fused"), (3, 2, "pqhost-fused")]     # quantised shards kept for the whole step (device / pinned host)
         for zero, ga, mode in runs:
             if True:
                 mx = mode.startswith("mx-")
-                coll = mode[3:] if mx else mode.split("+")[0]
+                pq = mode.startswith("pq")
+                coll = mode.split("-")[1] if (mx or pq) else mode.split("+")[0]
                 os.environ["LLMQ_GEMM_RS"] = "1" if mode.endswith("gemm_rs") else "0"
                 opts = LLamaOptions(matmul_type="mxe4m3" if mx else "e4m3", collectives=coll, momentum_type="bf16", variance_type="bf16")
                 opts.set_zero_level(zero)
+                if pq:
+                    opts.persistent_quants, opts.offload_quants, opts.offload_master = True, mode.startswith("pqhost"), mode.startswith("pqhost")
                 m = LlamaModel(cfg, opts, comm, dev, B, T)
                 assert (m.fused is not None) == (coll == "fused") and m.mx == mx
                 assert m.grads.gemm_rs == mode.endswith("gemm_rs")
@@ -94,5 +98,9 @@ def test_fused_training_matches_nccl():
     for (l0, n0), (l1, n1) in zip(a, b):
         assert abs(l0 - l1) < 5e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0), (a, b)
     assert a[-1][0] < a[0][0]
+    # kept quantised shards change where the bytes come from, not the bytes
+    for mode in ("pq-fused", "pqhost-fused"):
+        for (l0, n0), (l1, n1) in zip(r0[(3, 2, "fused")], r0[(3, 2, mode)]):
+            assert abs(l0 - l1) < 1e-4 and abs(n0 - n1) < 1e-3 * max(1.0, n0), (mode, r0[(3, 2, mode)], r0[(3, 2, "fused")])
     # the block-scaled recipe follows the per-tensor one closely on this model
     assert abs(a[0][0] - r0[(3, 2, "nccl")][0][0]) < 5e-2
