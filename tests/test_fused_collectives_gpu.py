@@ -139,9 +139,14 @@ def test_fused_collectives_match_nccl(multimem):
     procs = [ctx.Process(target=_worker, args=(r, world, port, multimem, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=240) for _ in range(world)]
+    res = []
+    try:
+        for _ in range(world):
+            res.append(q.get(timeout=240))
+    except Exception:                                   # a rank that never answered: report what the others said
+        pass
     for p in procs:
         p.join(timeout=60)
         if p.is_alive():
             p.kill()
-    assert all(r[1] == "ok" for r in res), res
+    assert len(res) == world and all(r[1] == "ok" for r in res), res
