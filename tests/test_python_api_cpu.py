@@ -161,3 +161,10 @@ def test_fixed_reference_ten_steps():
     assert a == b
     for (l, n), (wl, wn) in zip(a, want):
         assert abs(l - wl) < 5e-4 and abs(n - wn) < 5e-4, (a, want)
+
+
+def test_script_modules_under_reference_paths():
+    import pyllmq.scripts.tokenize_data as tk
+    import pyllmq.scripts.train as tr
+    from pyllmq.scripts import demo, export_wandb, plot_training_run
+    assert all(callable(m.main) for m in (tk, tr, demo, export_wandb, plot_training_run))
