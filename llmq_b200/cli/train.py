@@ -239,23 +239,13 @@ def _child(rank: int, world: int, port: int, cfg: TrainingConfig, argv):
 def _wandb_callback(cfg, wandb=None):
     """Live export (``--use-wandb``): every log line goes to a Weights & Biases run as it is written, with the same
     mapping as the offline exporter (role of ``make_wandb_log_callback`` in the reference's binding/python/training.py)."""
-    from ..scripts.export_wandb import log_line_to_metrics
     if wandb is None:
         try:
             import wandb
         except ImportError as e:
             raise RuntimeError("--use-wandb needs the wandb package; export the log file later with pyllmq-export-wandb instead") from e
-    run = wandb.init(project=cfg.wandb_project, name=cfg.wandb_name or cfg.name)
-
-    def on_line(obj: dict) -> None:
-        if obj.get("log") == "option":
-            run.config.update({obj.get("name", "option"): obj.get("value")}, allow_val_change=True)
-            return
-        got = log_line_to_metrics(obj)
-        if got:
-            run.log({k: v for k, v in got[1].items() if v is not None}, step=got[0])
-
-    return on_line
+    from ..scripts.export_wandb import make_wandb_log_callback
+    return make_wandb_log_callback(wandb.init(project=cfg.wandb_project, name=cfg.wandb_name or cfg.name))
 
 
 def main(argv=None) -> int:

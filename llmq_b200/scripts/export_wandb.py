@@ -31,6 +31,26 @@ def read_log(path: str) -> list:
     return json.loads(text)
 
 
+def log_line_to_wandb(run, entry: dict) -> None:
+    """Sends one log entry (a dict as written to the JSON log) to a Weights & Biases run."""
+    if entry.get("log") == "option":
+        run.config.update({entry.get("name", "option"): entry.get("value")}, allow_val_change=True)
+        return
+    got = log_line_to_metrics(entry)
+    if got:
+        run.log({k: v for k, v in got[1].items() if v is not None}, step=got[0])
+
+
+def make_wandb_log_callback(run):
+    """Per-line callback for ``TrainingRunLogger`` (takes the entry as a dict or as its JSON text)."""
+    import json
+
+    def callback(entry):
+        log_line_to_wandb(run, json.loads(entry) if isinstance(entry, (str, bytes)) else entry)
+
+    return callback
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description="Export a training log to wandb")
     p.add_argument("log_file")
