@@ -1,7 +1,7 @@
 """The kernels that carry a collective, on ONE GPU: rank 0 of an emulated group runs, the peer tables point at local
 buffers and the peers' arrivals are booked before the launch, so every code path of the kernel executes (peer stores,
 counter bumps, the summing tail, the producer's flag polls) without a second device.  The multi-GPU versions of these
-checks live in test_fused_collectives_gpu.py and need two or more GPUs."""
+checks live in test_y_multi_gpu_collectives.py and need two or more GPUs."""
 import ctypes
 
 import pytest
