@@ -27,6 +27,7 @@ from ..ops import kernels as K
 from ..options import LLamaOptions
 from ..parallel.comm import Communicator, LocalComm
 from ..parallel.offload import ResidualStore, Stager
+from ..utils import nvtx
 from ..parallel.zero import F8_TYPES, MATRICES, GradientManager, OptimizerStateManager, WeightsManager
 
 # abs-max slots per layer: index -> (absmax, scale)
@@ -414,6 +415,7 @@ class LlamaModel:
         cfg, a, w = self.cfg, self.acts, self.weights
         L = cfg.num_hidden_layers
         self._mark("start")
+        r_fwd = nvtx.push("forward", self.device)
         if inputs is not None:                    # None: the caller already placed the tokens in self.inputs
             self.inputs.copy_(inputs.reshape(self.B, self.T), non_blocking=True)
         K.encoder_forward(a.x.write_target(0), self.inputs, w.get_embeddings())
@@ -423,6 +425,7 @@ class LlamaModel:
         for l in range(L):
             if l + 1 < L:
                 w.gather_block(l + 1)
+            r_layer = nvtx.push(f"Layer {l}", self.device)
             p = w.get_block(l)
             am, _ = self._slot(l, S_LN1)
             if l == 0:
@@ -436,9 +439,11 @@ class LlamaModel:
             else:
                 self._forward_block(l, p)
             w.release_block(l)
+            nvtx.pop(r_layer)
         K.rmsnorm_forward(self.lnf, self.rstd_f, a.res_att[L - 1], w.get_lnf(), cfg.rms_norm_eps, residual_out=a.x.write_target(L),
                           inp2=self.tmp.proj)
         a.x.written(L)
+        nvtx.pop(r_fwd)
 
     def _forward_block(self, l: int, p) -> None:
         cfg, a, t = self.cfg, self.acts, self.tmp
@@ -470,11 +475,13 @@ class LlamaModel:
     @torch.no_grad()
     def validate(self, inputs: torch.Tensor, targets: torch.Tensor):
         """Returns (mean loss, mean loss over the first 1024 positions) of one batch, averaged over ranks."""
-        self.forward(inputs)
-        self.targets.copy_(targets.reshape(self.B, self.T), non_blocking=True)
-        self.losses.zero_()
-        self._lmhead(write_grads=False, dloss=0.0, z_loss=0.0, accumulate_dw=False)
-        return self._reduce_loss(None)
+        with nvtx.range("validate", self.device):
+            self.forward(inputs)
+            self.targets.copy_(targets.reshape(self.B, self.T), non_blocking=True)
+            self.losses.zero_()
+            with nvtx.range("lm-head", self.device):
+                self._lmhead(write_grads=False, dloss=0.0, z_loss=0.0, accumulate_dw=False)
+            return self._reduce_loss(None)
 
     def _reduce_loss(self, positions_per_rank: Optional[float]):
         """Mean loss and mean loss over the first 1024 positions.  ``positions_per_rank`` is the number of
@@ -568,7 +575,9 @@ class LlamaModel:
         g.start_micro_step(micro_step, grad_accum)
         dloss = 1.0 / (self.B * self.T * grad_accum)
         self._mark("forward")
-        self._lmhead(write_grads=True, dloss=dloss, z_loss=z_loss, accumulate_dw=micro_step > 0)
+        r_bwd = nvtx.push("backward", self.device)
+        with nvtx.range("lm-head", self.device):
+            self._lmhead(write_grads=True, dloss=dloss, z_loss=z_loss, accumulate_dw=micro_step > 0)
         self._mark("lm-head")
         # final norm: t.d_ln holds d(lnf); produce d(residual stream) in t.d_res
         t.d_res.zero_()
@@ -577,6 +586,7 @@ class LlamaModel:
         g.notify_non_block("lnf_w")
         w.gather_block(L - 1)
         for l in range(L - 1, -1, -1):
+            r_layer = nvtx.push(f"Layer {l}", self.device)
             dw, acc = g.get_block_full(l)
             a.x.prefetch(l - 1)
             if l > 0:
@@ -596,11 +606,13 @@ class LlamaModel:
                                accumulate_dweight=True)
             w.release_block(l)
             g.notify_block(l)
+            nvtx.pop(r_layer)
         if not cfg.tie_word_embeddings and micro_step == 0:
             g.nb_full["embed"].zero_()             # untied: nothing has written this buffer yet in this step
         K.encoder_backward(g.nb_full["embed"], t.d_res, self.inputs)
         g.notify_non_block("embed")
         g.end_micro_step()
+        nvtx.pop(r_bwd)
         self._mark("backward")
 
     def _recompute_block(self, l: int, p) -> None:
@@ -690,6 +702,7 @@ class LlamaModel:
                weight_decay: float = 0.1, grad_clip: float = 1.0, grad_accum: int = 1) -> Dict[str, float]:
         """Clips by the global norm, applies AdamW to the local shards, returns {loss, loss_1k, norm, z_max, z_mean}."""
         w, g, o = self.weights, self.grads, self.opt_state
+        r_upd = nvtx.push("update", self.device)
         g.wait_all()
         # ---- global gradient norm over the local shards
         self.norm_partials.zero_()
@@ -757,6 +770,7 @@ class LlamaModel:
         self._mark("optimizer")
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
+        nvtx.pop(r_upd)
         res = {"loss": loss, "loss_1k": loss1k, "norm": float(hs[0]), "z_max": float(hs[2]), "z_mean": float(hs[3]) / ntok}
         if self.opts.trigger_timing_events:
             res["time_breakdown"] = self.time_breakdown()

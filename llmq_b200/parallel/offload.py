@@ -12,6 +12,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from ..utils import nvtx
+
 
 class Stager:
     """Double-buffered staging for a sequence of work items (parity = item index & 1)."""
@@ -40,7 +42,7 @@ class Stager:
             return t, None
         key = (kind, parity)
         buf = self._buf(key, t)
-        with torch.cuda.stream(self.h2d):
+        with nvtx.range("offload fetch", self.device), torch.cuda.stream(self.h2d):
             if key in self.free:
                 self.h2d.wait_event(self.free[key])         # the previous content has been written back
             if parity in self.consumed:
@@ -63,7 +65,7 @@ class Stager:
             return
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(self.d2h):
+        with nvtx.range("offload store", self.device), torch.cuda.stream(self.d2h):
             self.d2h.wait_event(ready)
             host.copy_(staged, non_blocking=True)
             ev = torch.cuda.Event()

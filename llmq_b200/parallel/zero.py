@@ -24,6 +24,7 @@ import torch
 from ..config import TransformerConfig
 from ..ops import kernels as K
 from ..options import LLamaOptions
+from ..utils import nvtx
 from .comm import Communicator, _WorkList
 
 F8_TYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
@@ -194,6 +195,10 @@ class WeightsManager:
             return
         if buf.in_use:
             raise RuntimeError(f"weight buffer for layer {l} is still in use by layer {buf.layer}")
+        with nvtx.range(f"gather_block {l}", self.device):
+            self._gather_block(l, buf)
+
+    def _gather_block(self, l: int, buf) -> None:
         if self.fused is not None and self.comm.world > 1:
             self._gather_block_fused(l, buf)
             return

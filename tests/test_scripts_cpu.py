@@ -170,3 +170,41 @@ def test_tokenize_named_dataset(tmp_path):
     assert 0 < n_eval <= 100 and 900 <= n_eval + n_train < 900 + 41
     with pytest.raises(ValueError):
         tokenize_data.generate_tokenized_dataset("nope", "qwen", str(tmp_path), load_dataset=fake_load, tokenizer=Tok())
+
+
+def test_nvtx_ranges(monkeypatch):
+    """Range helper: silent on CPU devices, balanced push / pop on a CUDA device, and it switches itself off when the
+    NVTX call is not available."""
+    import torch
+    from llmq_b200.utils import nvtx
+
+    calls = []
+
+    class Fake:
+        @staticmethod
+        def range_push(name):
+            calls.append(("push", name))
+
+        @staticmethod
+        def range_pop():
+            calls.append(("pop",))
+
+    monkeypatch.setattr(nvtx, "_backend", lambda: Fake)
+    monkeypatch.setitem(nvtx._state, "on", True)
+    with nvtx.range("forward", torch.device("cpu")):
+        pass
+    assert calls == []
+    with nvtx.range("forward", torch.device("cuda", 0)):
+        r = nvtx.push("Layer 3")
+        nvtx.pop(r)
+    assert calls == [("push", "forward"), ("push", "Layer 3"), ("pop",), ("pop",)]
+
+    class Broken:
+        @staticmethod
+        def range_push(name):
+            raise RuntimeError("no NVTX")
+
+    monkeypatch.setattr(nvtx, "_backend", lambda: Broken)
+    with nvtx.range("update", torch.device("cuda", 0)):
+        pass
+    assert nvtx._state["on"] is False and nvtx.push("x") is False
