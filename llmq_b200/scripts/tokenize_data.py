@@ -61,9 +61,34 @@ def encode_record(tok, rec: dict, text_key: str, seq_len: Optional[int]) -> Tupl
     return np.array(ids + [eos], dtype=np.int32), None
 
 
+def default_workers() -> int:
+    """Half the cores, at most 8 (the reference's pool size)."""
+    return max(1, min((os.cpu_count() or 2) // 2, 8))
+
+
+def _encode_stream(records: Iterable[dict], tok, text_key: str, seq_len: Optional[int], workers: int):
+    """Encoded records in input order.  With several workers the tokenizer runs in a thread pool (the Rust tokenizers
+    release the interpreter lock) with a bounded window of documents in flight, so a streamed dataset is never read
+    ahead as a whole."""
+    if workers <= 1:
+        for rec in records:
+            yield encode_record(tok, rec, text_key, seq_len)
+        return
+    import collections
+    from concurrent.futures import ThreadPoolExecutor
+    window = collections.deque()
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        for rec in records:
+            window.append(pool.submit(encode_record, tok, rec, text_key, seq_len))
+            if len(window) >= 8 * workers:
+                yield window.popleft().result()
+        while window:
+            yield window.popleft().result()
+
+
 def tokenize_records(records: Iterable[dict], out_prefix: str, tok, vocab_size: int, text_key="text", seq_len=None,
                      max_tokens_per_file=100_000_000, masking=False, single_file: bool = False, max_tokens: Optional[int] = None,
-                     first_file: Optional[Tuple[str, int]] = None) -> list:
+                     first_file: Optional[Tuple[str, int]] = None, workers: int = 1) -> list:
     """Writes the records to ``{out_prefix}-000.bin``, ``-001.bin``, ... (or ``{out_prefix}.bin`` with ``single_file``).
 
     ``first_file`` = (path, tokens): the first that many tokens go to a file of their own (an eval set cut off the
@@ -85,8 +110,7 @@ def tokenize_records(records: Iterable[dict], out_prefix: str, tok, vocab_size: 
         w.__enter__()
 
     open_next()
-    for rec in records:
-        t, m = encode_record(tok, rec, text_key, seq_len)
+    for t, m in _encode_stream(records, tok, text_key, seq_len, workers):
         if not single_file and w.n_tokens + len(t) > limit and w.n_tokens > 0:
             w.__exit__(None, None, None)
             open_next()
@@ -99,9 +123,9 @@ def tokenize_records(records: Iterable[dict], out_prefix: str, tok, vocab_size: 
 
 
 def tokenize_files(inputs, out_prefix: str, tok, vocab_size: int, text_key="text", seq_len=None, max_tokens_per_file=100_000_000,
-                   masking=False) -> list:
+                   masking=False, workers: int = 1) -> list:
     recs = (rec for path in inputs for rec in iter_documents(path, text_key))
-    return tokenize_records(recs, out_prefix, tok, vocab_size, text_key, seq_len, max_tokens_per_file, masking)
+    return tokenize_records(recs, out_prefix, tok, vocab_size, text_key, seq_len, max_tokens_per_file, masking, workers=workers)
 
 
 # Named datasets of the reference's tool (scripts/tokenize_data.py:255-300 there): hub id, configuration, how a record
@@ -144,7 +168,7 @@ def _records(split, spec):
 
 
 def generate_tokenized_dataset(dataset: str, model: str, out_dir: str = "data", seq_len: Optional[int] = None, *, load_dataset=None,
-                               tokenizer=None) -> list:
+                               tokenizer=None, workers: int = 1) -> list:
     """``--dataset NAME --model qwen|llama``: tokenises a named hub dataset into ``{out_dir}/{NAME}-{model}/``
     (``train.bin`` / ``train-000.bin``... and ``eval.bin``).  ``load_dataset`` / ``tokenizer`` can be passed in
     (tests do); by default they come from the ``datasets`` and ``transformers`` packages and their local caches."""
@@ -166,7 +190,7 @@ def generate_tokenized_dataset(dataset: str, model: str, out_dir: str = "data", 
     elif seq_len <= 0:
         seq_len = None
     vocab, tiny = len(tok), bool(spec.get("tiny"))
-    common = dict(text_key="text", seq_len=seq_len, masking=masking)
+    common = dict(text_key="text", seq_len=seq_len, masking=masking, workers=workers)
     if isinstance(spec["eval"], int):
         return tokenize_records(_records(d["train"], spec), os.path.join(dst, "train"), tok, vocab, max_tokens=spec.get("subsample"),
                                 first_file=(os.path.join(dst, "eval.bin"), spec["eval"]), **common)
@@ -187,15 +211,16 @@ def main(argv=None) -> int:
                    help="pad / cut prompt-response pairs to this many tokens (-1: no padding; default: the dataset's own)")
     p.add_argument("--masking", action="store_true", help="write a training mask (response tokens only)")
     p.add_argument("--max-tokens-per-file", type=int, default=100_000_000)
+    p.add_argument("--workers", type=int, default=default_workers(), help="tokenizer threads")
     a = p.parse_args(argv)
     if a.dataset:
-        print("wrote", *generate_tokenized_dataset(a.dataset, a.model, a.out_dir, a.seq_len))
+        print("wrote", *generate_tokenized_dataset(a.dataset, a.model, a.out_dir, a.seq_len, workers=a.workers))
         return 0
     if not a.inputs:
         p.error("give input files or --dataset")
     tok = _load_tokenizer(TOKENIZERS.get(a.model.lower(), a.model))
     files = tokenize_files(a.inputs, os.path.join(a.out_dir, a.split), tok, len(tok), a.text_key,
-                           a.seq_len if a.seq_len and a.seq_len > 0 else None, a.max_tokens_per_file, a.masking)
+                           a.seq_len if a.seq_len and a.seq_len > 0 else None, a.max_tokens_per_file, a.masking, workers=a.workers)
     print("wrote", *files)
     return 0
 

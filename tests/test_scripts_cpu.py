@@ -65,6 +65,10 @@ def test_tokenize_files_with_masks(tmp_path):
     txt.write_text("first document\nline two\n\nsecond document\n")
     files = tokenize_data.tokenize_files([str(txt)], str(tmp_path / "data" / "plain"), Tok(), 64)
     assert DataLoader(files, 8).num_tokens == len("first document\nline two\n") + 1 + len("second document\n") + 1
+    # several tokenizer threads give the same files, document order included
+    serial = tokenize_data.tokenize_files([str(src)], str(tmp_path / "w1" / "train"), Tok(), 64, seq_len=32, masking=True)
+    threaded = tokenize_data.tokenize_files([str(src)], str(tmp_path / "w4" / "train"), Tok(), 64, seq_len=32, masking=True, workers=4)
+    assert [open(f, "rb").read() for f in serial] == [open(f, "rb").read() for f in threaded]
 
 
 class FakeNVML:
