@@ -4,6 +4,7 @@
 // QMAX is 448 for e4m3 and 57344 for e5m2 (the reference uses 448 for both, which wastes the e5m2 range).
 #include "api.h"
 #include "common.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -89,6 +90,113 @@ transpose_kernel(Q* __restrict__ out, float* __restrict__ scale_out, const T* __
     }
 }
 
+// 4 x 4 byte transpose: words a..d hold bytes [x0 x1 x2 x3] of four consecutive rows; col[k] = [a_k b_k c_k d_k].
+__device__ __forceinline__ void transpose_4x4_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&col)[4]) {
+    uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+    uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+    col[0] = __byte_perm(t0, t1, 0x5410);
+    col[1] = __byte_perm(t0, t1, 0x7632);
+    col[2] = __byte_perm(t2, t3, 0x5410);
+    col[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+// One 128 x 128 tile per CTA: reads in[rows][cols] (bf16/fp32: quantised with the given abs-max; 1-byte types: copied),
+// optionally writes the row-major 1-byte copy, and writes the transposed 1-byte copy out_t[cols][rows] so that the
+// weight-gradient GEMMs can read both operands K-major (the reference's quantize_and_transpose_with_abs_max,
+// src/kernels/quant.cu:100-193, and its fp8 transpose_kernel).  The tile sits in shared memory as 128 rows of 32 words;
+// word w of row r lives at w ^ (((r >> 4) & 7) << 2), which makes both the row-major stores and the column reads
+// (16 rows of one word column per thread) free of bank conflicts.  Every global access is a 16-byte vector (8 bytes for
+// the row-major copy of 2-byte inputs); rows and cols must be multiples of 16.
+template <typename T, typename Q>
+__global__ void __launch_bounds__(256)
+tile_transpose_kernel(Q* __restrict__ out_rows, Q* __restrict__ out_t, float* __restrict__ scale_out, const T* __restrict__ in,
+                      const float* __restrict__ absmax, int rows, int cols) {
+    static_assert(sizeof(Q) == 1, "1-byte outputs only");
+    __shared__ __align__(16) uint32_t tile[128 * 32];
+    const int t = threadIdx.x;
+    const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
+    float mul = 1.f;
+    if constexpr (sizeof(T) > 1) {
+        float am = fmaxf(*absmax, 1e-10f);
+        mul = QMax<Q>::value / am;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0 && scale_out) *scale_out = am / QMax<Q>::value;
+    }
+    if constexpr (sizeof(T) == 2) {
+        // 16 threads per row (8 elements each), 16 rows per pass
+        const int cc = t & 15, rr = t >> 4;
+        uint4 v[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            int r = r0 + p * 16 + rr, c = c0 + cc * 8;
+            v[p] = (r < rows && c < cols) ? __ldcs(reinterpret_cast<const uint4*>(in + static_cast<long long>(r) * cols + c)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            int lr = p * 16 + rr, r = r0 + lr, c = c0 + cc * 8;
+            const T* e = reinterpret_cast<const T*>(&v[p]);
+            uint2 w;
+            if constexpr (std::is_same<Q, e4m3>::value) {
+                float f[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] = to_float(e[k]) * mul;
+                w = pack_e4m3x8(f);
+            } else {
+                alignas(8) Q q[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) q[k] = from_float<Q>(to_float(e[k]) * mul);
+                w = *reinterpret_cast<uint2*>(q);
+            }
+            if (out_rows && r < rows && c < cols) *reinterpret_cast<uint2*>(out_rows + static_cast<long long>(r) * cols + c) = w;
+            *reinterpret_cast<uint2*>(&tile[lr * 32 + ((cc * 2) ^ (((lr >> 4) & 7) << 2))]) = w;
+        }
+    } else if constexpr (sizeof(T) == 4) {
+        // 32 threads per row (4 elements each), 8 rows per pass
+        const int cc = t & 31, rr = t >> 5;
+#pragma unroll 4
+        for (int p = 0; p < 16; ++p) {
+            int lr = p * 8 + rr, r = r0 + lr, c = c0 + cc * 4;
+            float4 f = (r < rows && c < cols) ? *reinterpret_cast<const float4*>(in + static_cast<long long>(r) * cols + c) : make_float4(0, 0, 0, 0);
+            alignas(4) Q q[4] = {from_float<Q>(f.x * mul), from_float<Q>(f.y * mul), from_float<Q>(f.z * mul), from_float<Q>(f.w * mul)};
+            uint32_t w = *reinterpret_cast<uint32_t*>(q);
+            if (out_rows && r < rows && c < cols) *reinterpret_cast<uint32_t*>(out_rows + static_cast<long long>(r) * cols + c) = w;
+            tile[lr * 32 + (cc ^ (((lr >> 4) & 7) << 2))] = w;
+        }
+    } else {
+        // 1-byte input: 8 threads per row (16 bytes each), 32 rows per pass
+        const int cc = t & 7, rr = t >> 3;
+        uint4 v[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            int r = r0 + p * 32 + rr, c = c0 + cc * 16;
+            v[p] = (r < rows && c < cols) ? __ldcs(reinterpret_cast<const uint4*>(in + static_cast<long long>(r) * cols + c)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            int lr = p * 32 + rr;
+            *reinterpret_cast<uint4*>(&tile[lr * 32 + ((cc * 4) ^ (((lr >> 4) & 7) << 2))]) = v[p];
+        }
+    }
+    __syncthreads();
+    // thread = (16-row chunk rc, word column cw): 8 lanes of equal cw write 128 contiguous bytes of one output row
+    const int lane = t & 31, warp = t >> 5;
+    const int rc = lane & 7, cw = warp * 4 + (lane >> 3);
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = tile[(rc * 16 + j) * 32 + (cw ^ (rc << 2))];
+    uint32_t o[4][4];            // o[g][k]: rows 4g..4g+3 of column k
+#pragma unroll
+    for (int g = 0; g < 4; ++g) transpose_4x4_bytes(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3], o[g]);
+    const int r = r0 + rc * 16;
+    if (r < rows) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int c = c0 + cw * 4 + k;
+            if (c < cols)
+                *reinterpret_cast<uint4*>(out_t + static_cast<long long>(c) * rows + r) = make_uint4(o[0][k], o[1][k], o[2][k], o[3][k]);
+        }
+    }
+}
+
 template <typename S, typename D>
 __global__ void __launch_bounds__(512) convert_kernel(D* __restrict__ out, const S* __restrict__ in, long long n) {
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -168,6 +276,30 @@ extern "C" int llmq_transpose(void* out, float* scale_out, const void* in, const
     T_CASE(bf16, 0, e5m2, 2, true)
     T_CASE(float, 3, e4m3, 1, true)
 #undef T_CASE
+    return -10;
+}
+
+// out_rows (optional, [rows][cols]) and out_t ([cols][rows]) are 1-byte copies of in[rows][cols]; with a 2- or 4-byte
+// input the values are quantised with *absmax first.  rows % 16 == 0 and cols % 16 == 0.
+extern "C" int llmq_quantize_transpose(void* out_rows, void* out_t, float* scale_out, const void* in, const float* absmax, int rows,
+                                       int cols, int in_dtype, int out_dtype, cudaStream_t s) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (rows % 16 != 0 || cols % 16 != 0 || out_t == nullptr) return -11;
+    dim3 grid(ceil_div_i(cols, 128), ceil_div_i(rows, 128));
+#define QT_CASE(T, TC, Q, QC)                                                                                         \
+    if (in_dtype == TC && out_dtype == QC) {                                                                          \
+        if (sizeof(T) > 1 && absmax == nullptr) return -12;                                                           \
+        tile_transpose_kernel<T, Q><<<grid, 256, 0, s>>>(static_cast<Q*>(out_rows), static_cast<Q*>(out_t), scale_out, \
+                                                         static_cast<const T*>(in), absmax, rows, cols);              \
+        return LLMQ_LAUNCH_CHECK();                                                                                   \
+    }
+    QT_CASE(bf16, 0, e4m3, 1)
+    QT_CASE(bf16, 0, e5m2, 2)
+    QT_CASE(float, 3, e4m3, 1)
+    QT_CASE(float, 3, e5m2, 2)
+    QT_CASE(e4m3, 1, e4m3, 1)
+    QT_CASE(e5m2, 2, e5m2, 2)
+#undef QT_CASE
     return -10;
 }
 

@@ -211,6 +211,17 @@ class LlamaModel:
             t.d_res_q = z(BT, C, dtype=self.gdtype)
             t.d_up_q = z(BT, 2 * D, dtype=self.gdtype)
             t.d_qkv_q = z(BT, QC, dtype=self.gdtype)
+        # fp8 backward with every GEMM operand K-major: transposed copies of the output gradients (written by the pass that
+        # quantises them), of the layer inputs and of the weights (small fp8 -> fp8 transposes next to the GEMM that reads them)
+        self._kmajor = bool(q and o.kmajor_backward and dev.type == "cuda" and self.qdtype in F8_TYPES and self.gdtype in F8_TYPES
+                            and all(v % 16 == 0 for v in (BT, C, 2 * D, QC)))
+        t.d_res_qT = t.d_up_qT = t.d_qkv_qT = None
+        if self._kmajor:
+            t.d_res_qT = z(C, BT, dtype=self.gdtype)
+            t.d_up_qT = z(2 * D, BT, dtype=self.gdtype)
+            t.d_qkv_qT = z(QC, BT, dtype=self.gdtype)
+            t.inp_qT = torch.zeros(max(C, D) * BT, dtype=self.qdtype, device=dev)
+            t.w_T = torch.zeros(max(2 * D, QC, C) * max(C, D), dtype=self.qdtype, device=dev)
         chunks = max(1, o.lmhead_chunks)
         if BT % chunks:
             raise ValueError("lmhead_chunks must divide batch * seq_len")
@@ -316,7 +327,7 @@ class LlamaModel:
         K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale, ready=ready)
 
     def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None, dw_rs=None,
-                swiglu_inout=None, swiglu_absmax=None):
+                swiglu_inout=None, swiglu_absmax=None, dout_qT=None):
         """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
         W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second.
         ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside.
@@ -361,13 +372,32 @@ class LlamaModel:
                 K.bias_backward(dbias, dout, self.tmp.bias_scratch, accumulate=True)
             return
         am, sc = slot
-        K.quantize(dout_q, sc, dout, am)
+        t = self.tmp
+        kmajor = self._kmajor and dout_qT is not None and ready is None
+        if kmajor and dw_rs is None:
+            K.quantize_transpose(dout_q, dout_qT, sc, dout, am)
+        else:
+            K.quantize(dout_q, sc, dout, am)
         if swiglu_inout is not None:
             K.gemm_swiglu_backward(swiglu_inout, dout_q, W, scale_a=sc, scale_b=w_scale, absmax=swiglu_absmax)
         elif dinp is not None:
-            K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
+            if kmajor:
+                WT = t.w_T[:W.numel()].view(W.shape[1], W.shape[0])
+                K.transpose(WT, W)
+                K.gemm(dinp, dout_q, WT, scale_a=sc, scale_b=w_scale)
+            else:
+                K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
         if dw_rs is not None:
             self._launch_dw(lambda: dw_rs(dout_q, inp_q, sc, inp_scale))
+        elif kmajor:
+            i2 = inp_q.reshape(-1, inp_q.shape[-1])
+            iT = t.inp_qT[:i2.numel()].view(i2.shape[1], i2.shape[0])
+
+            def dw():
+                # the side stream runs these two in order, so one transposed-input buffer serves every GEMM of the block
+                K.transpose(iT, i2)
+                K.gemm(dW, dout_qT, iT, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
+            self._launch_dw(dw)
         else:
             self._launch_dw(lambda: K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate))
         if dbias is not None:
@@ -672,21 +702,23 @@ class LlamaModel:
         fuse_sw = self._fuse_swiglu and bool(int(self.opts.fuse_swiglu) & 2) and p.ready["down_w"] is None
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
                      a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"),
-                     swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0])
+                     swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0], dout_qT=t.d_res_qT)
         ev_down = self._dw_events[-1] if self._dw_events else None      # dW(down) reads d_res / its fp8 copy
         # ---- SwiGLU backward, in place over the saved up-projection (unless the GEMM epilogue above already did it)
         if not fuse_sw:
             K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
         # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
-                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"))
+                     a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"),
+                     dout_qT=t.d_up_qT)
         # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
         self._wait_dw(ev_down)                                          # the next two kernels overwrite d_res and its fp8 copy
         K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],
                            absmax=self._slot(l, S_DRESATT)[0], accumulate_dweight=True)
         # ---- attention out projection
         self._bwd_mm(t.d_ln, dw["o_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESATT),
-                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc, ready=p.ready["o_w"], dw_rs=rs("o_w"))
+                     a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc, ready=p.ready["o_w"], dw_rs=rs("o_w"),
+                     dout_qT=t.d_res_qT)
         # ---- attention core
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
         K.attention_backward(t.d_qkv, t.att_scratch, t.d_ln.view(self.B, self.T, Hq, cfg.head_size), att4, a.lse[l], a.qkv[l], Hq, Hkv)
@@ -694,7 +726,8 @@ class LlamaModel:
         # ---- QKV projection
         dqkv2d = t.d_qkv.view(BT, cfg.qkv_channels)
         self._bwd_mm(t.d_ln, dw["qkv_w"], dw.get("qkv_b"), dqkv2d, t.d_qkv_q if q else None, self._slot(l, S_DQKV),
-                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc, ready=p.ready["qkv_w"], dw_rs=rs("qkv_w"))
+                     a.ln1[l], a.ln1_q[l] if q else None, sc_of(S_LN1), p.qkv_w, p.scales["qkv_w"], acc, ready=p.ready["qkv_w"], dw_rs=rs("qkv_w"),
+                     dout_qT=t.d_qkv_qT)
         self._join_dw()                                                 # the caller reuses d_res, d_ln and the gradient buffers
 
     # ================================================================================== optimizer

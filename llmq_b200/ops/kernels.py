@@ -495,10 +495,35 @@ def quantize(out: torch.Tensor, scale_out: Optional[torch.Tensor], x: torch.Tens
             scale_out.fill_(1.0)
 
 
+def quantize_transpose(out_rows: Optional[torch.Tensor], out_t: torch.Tensor, scale_out: Optional[torch.Tensor], x: torch.Tensor,
+                       absmax: Optional[torch.Tensor]) -> None:
+    """One pass over ``x[rows, cols]``: ``out_rows`` (optional) = the fp8 copy, ``out_t[cols, rows]`` = its transpose.
+    With a 1-byte ``x`` (and ``absmax`` None) the values are copied.  The transposed copy lets the weight-gradient GEMM
+    read both operands K-major (reference: quantize_and_transpose_with_abs_max, src/kernels/quant.cu:100-193)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, cols = x2.shape
+    if x.is_cuda and rows % 16 == 0 and cols % 16 == 0:
+        L.check(L.kernels().llmq_quantize_transpose(L.ptr(out_rows), L.ptr(out_t), L.ptr(scale_out), L.ptr(x2), L.ptr(absmax), rows, cols,
+                                                    L.dtype_code(x.dtype), L.dtype_code(out_t.dtype), L.stream_ptr()), "quantize_transpose")
+        return
+    if x2.element_size() == 1:
+        if out_rows is not None:
+            out_rows.reshape(rows, cols).copy_(x2)
+        transpose(out_t, x2)
+        return
+    rows_q = out_rows.reshape(rows, cols) if out_rows is not None else torch.empty(rows, cols, dtype=out_t.dtype, device=x.device)
+    quantize(rows_q, scale_out, x2, absmax)
+    transpose(out_t, rows_q)
+
+
 def transpose(out: torch.Tensor, x: torch.Tensor, *, absmax: Optional[torch.Tensor] = None,
               scale_out: Optional[torch.Tensor] = None) -> None:
     """out[c, r] = x[r, c]; with ``absmax`` the values are quantised to ``out.dtype`` on the way."""
     rows, cols = x.shape
+    if x.is_cuda and out.element_size() == 1 and rows % 16 == 0 and cols % 16 == 0 and (absmax is not None or x.element_size() == 1):
+        L.check(L.kernels().llmq_quantize_transpose(None, L.ptr(out), L.ptr(scale_out), L.ptr(x), L.ptr(absmax), rows, cols,
+                                                    L.dtype_code(x.dtype), L.dtype_code(out.dtype), L.stream_ptr()), "transpose")
+        return
     if x.is_cuda:
         L.check(L.kernels().llmq_transpose(L.ptr(out), L.ptr(scale_out), L.ptr(x), L.ptr(absmax), rows, cols, L.dtype_code(x.dtype),
                                            L.dtype_code(out.dtype), L.stream_ptr()), "transpose")

@@ -35,6 +35,7 @@ class LLamaOptions:
     # per 32 elements of the contraction axis (tcgen05 kind::mxf8f6f4.block_scale); activations and weights stay bf16.
     # Also selected by matmul_type = "mxe4m3" / "mxfp8".
     block_scaled: bool = False
+    kmajor_backward: bool = True              # fp8 backward GEMMs read transposed fp8 copies (all operands K-major) instead of MN-major tiles
     lmhead_transposed_operands: bool = True   # LM-head backward reads W^T / lnf^T copies (K-major GEMM operands)
     trigger_timing_events: bool = False
     # placement of state

@@ -228,6 +228,82 @@ def test_quant_transpose_convert_fill():
         assert not torch.equal(other, n[:1024])
 
 
+@pytest.mark.parametrize("rows,cols", [(128, 128), (400, 208), (1024, 3584), (16, 4864)])
+@pytest.mark.parametrize("src", ["bf16", "fp32", "e4m3", "e5m2"])
+def test_quantize_transpose_tiles(rows, cols, src):
+    """The 128 x 128 tile kernel: row-major fp8 copy equals the plain quantiser bit for bit, the transposed copy is its
+    exact transpose; 1-byte inputs are copied.  Shapes cover full tiles, ragged tiles and a single 16-row strip."""
+    torch.manual_seed(rows + cols)
+    x = torch.randn(rows, cols) * 2.5
+    for qdt in ((F8, torch.float8_e5m2) if src in ("bf16", "fp32") else ((F8,) if src == "e4m3" else (torch.float8_e5m2,))):
+        if src in ("bf16", "fp32"):
+            xd = x.to(BF if src == "bf16" else torch.float32).to(DEV)
+            am = torch.zeros(1, device=DEV)
+            K.abs_max(am, xd)
+            ref_rows = torch.zeros(rows, cols, dtype=qdt, device=DEV)
+            sc_ref = torch.zeros(1, device=DEV)
+            K.quantize(ref_rows, sc_ref, xd, am)
+            out_rows = torch.zeros(rows, cols, dtype=qdt, device=DEV)
+            out_t = torch.zeros(cols, rows, dtype=qdt, device=DEV)
+            sc = torch.zeros(1, device=DEV)
+            K.quantize_transpose(out_rows, out_t, sc, xd, am)
+            assert sc.item() == sc_ref.item()
+            assert torch.equal(out_rows.view(torch.uint8), ref_rows.view(torch.uint8))
+            assert torch.equal(out_t.view(torch.uint8), ref_rows.view(torch.uint8).t())
+            only_t = torch.zeros(cols, rows, dtype=qdt, device=DEV)
+            K.quantize_transpose(None, only_t, None, xd, am)
+            assert torch.equal(only_t.view(torch.uint8), out_t.view(torch.uint8))
+        else:
+            xq = x.to(qdt).to(DEV)
+            out_t = torch.zeros(cols, rows, dtype=qdt, device=DEV)
+            K.transpose(out_t, xq)
+            assert torch.equal(out_t.view(torch.uint8), xq.view(torch.uint8).t())
+
+
+# Shapes with M >= 256 and M * N >= 2 Mi select the CTA-pair kernel (256 x 256 tiles, cta_group::2), the kernel that carries
+# the training step; the smaller shapes above all run the one-CTA kernel.
+PAIR_SHAPES = [(2048, 1536, 512), (1104, 2000, 208), (2304, 4608, 3584)]      # every extent a multiple of 16 bytes in fp8 (TMA rows)
+
+
+@pytest.mark.parametrize("M,N,Kd", PAIR_SHAPES)
+@pytest.mark.parametrize("dt", ["bf16", "e4m3", "e5m2"])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+def test_gemm_pair_kernel(M, N, Kd, dt, a_mn, b_mn):
+    """Plain product on the CTA-pair kernel against fp32 A @ B^T, every operand layout, ragged M / N / K edges."""
+    torch.manual_seed(11)
+    tdt = {"bf16": BF, "e4m3": F8, "e5m2": torch.float8_e5m2}[dt]
+    A, B = (torch.randn(M, Kd) * 0.5).to(tdt), (torch.randn(N, Kd) * 0.5).to(tdt)
+    As = A.float().t().contiguous().to(tdt) if a_mn else A
+    Bs = B.float().t().contiguous().to(tdt) if b_mn else B
+    out = torch.zeros(M, N, dtype=BF, device=DEV)
+    K.gemm(out, As.to(DEV), Bs.to(DEV), a_mn=bool(a_mn), b_mn=bool(b_mn))
+    ref = A.float().to(DEV) @ B.float().to(DEV).t()
+    close(out, ref.cpu(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,Kd", PAIR_SHAPES)
+@pytest.mark.parametrize("dt", ["bf16", "e4m3"])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (1, 1)])
+@pytest.mark.parametrize("out_dt", [BF, torch.float32])
+def test_gemm_pair_kernel_epilogue(M, N, Kd, dt, a_mn, b_mn, out_dt):
+    """Bias, accumulation into the existing output (the gradient-accumulation path), per-tensor scales, alpha and the
+    abs-max output of the CTA-pair kernel against fp32 arithmetic."""
+    torch.manual_seed(12)
+    tdt = BF if dt == "bf16" else F8
+    A, B = (torch.randn(M, Kd) * 0.5).to(tdt), (torch.randn(N, Kd) * 0.5).to(tdt)
+    As = A.float().t().contiguous().to(tdt) if a_mn else A
+    Bs = B.float().t().contiguous().to(tdt) if b_mn else B
+    bias, C0 = torch.randn(N).to(BF), torch.randn(M, N).to(out_dt)
+    sa, sb = torch.tensor([0.5]), torch.tensor([0.25])
+    ref = (A.float().to(DEV) @ B.float().to(DEV).t()).cpu() * (0.5 * 0.25 * 2.0) + bias.float() + C0.float()
+    out = C0.to(DEV)
+    am = torch.zeros(1, device=DEV)
+    K.gemm(out, As.to(DEV), Bs.to(DEV), a_mn=bool(a_mn), b_mn=bool(b_mn), bias=bias.to(DEV), accumulate=True, scale_a=sa.to(DEV),
+           scale_b=sb.to(DEV), alpha=2.0, absmax=am)
+    close(out, ref, rtol=1e-2, atol=5e-2)
+    assert abs(am.item() - ref.abs().max().item()) <= 1e-2 * ref.abs().max().item() + 5e-2
+
+
 @pytest.mark.parametrize("V", [512, 1000, 151936])
 def test_fused_classifier(V):
     torch.manual_seed(8)
