@@ -78,6 +78,7 @@ Args parse(int argc, char** argv) {
         else if (flag(s, "--offload-opt-v")) o.OffloadOptV = true;
         else if (flag(s, "--persistent-quants")) o.PersistentQuants = true;
         else if (flag(s, "--custom-matmul")) o.UseCustomMatmul = true;
+        else if (flag(s, "--debug-time-breakdown")) o.TriggerTimingEvents = true;
         else { fprintf(stderr, "unknown argument %s\n", s); std::exit(2); }
     }
     // the same implications as the reference's command line (train.cpp:229-254)
@@ -170,6 +171,22 @@ void run_rank(const Args& args, NCCLCommunicator& comm, Result* out) {
     float e2e_ms = std::chrono::duration<float, std::milli>(t1 - t0).count();
     comm.barrier();
     if (comm.rank() == 0) { printf("TIMED_END\n"); fflush(stdout); }
+    if (options.TriggerTimingEvents && comm.rank() == 0) {
+        // phase times of the last step, read from the reference's own timing events (as logging.cpp:367-396 does)
+        auto& rs = model.run_state();
+        for (size_t i = 0; i < rs.TimingForwardStart.size() && i < (size_t)GA; ++i) {
+            float fwd = 0.f, head = 0.f, bwd = 0.f;
+            CK(cudaEventSynchronize(rs.TimingBackwardEnd.at(i)));
+            CK(cudaEventElapsedTime(&fwd, rs.TimingForwardStart.at(i), rs.TimingForwardEnd.at(i)));
+            CK(cudaEventElapsedTime(&head, rs.TimingHeadStart.at(i), rs.TimingHeadEnd.at(i)));
+            CK(cudaEventElapsedTime(&bwd, rs.TimingBackwardStart.at(i), rs.TimingBackwardEnd.at(i)));
+            fprintf(stderr, "breakdown micro-step %zu: fwd %.2f ms, head %.2f ms, bwd %.2f ms\n", i, fwd, head, bwd - head);
+        }
+        float opt = 0.f;
+        CK(cudaEventSynchronize(rs.TimingOptimizerEnd));
+        CK(cudaEventElapsedTime(&opt, rs.TimingOptimizerStart, rs.TimingOptimizerEnd));
+        fprintf(stderr, "breakdown optimizer: %.2f ms\n", opt);
+    }
 
     out[comm.rank()] = Result{dev_ms, e2e_ms, loss, norm};
 }

@@ -38,7 +38,8 @@ constexpr int B_STAGE_BYTES = BN_HALF * ROW_BYTES;   // 16 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_WARPS = 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_WARPS * EPI_STAGE_BYTES_PER_WARP;
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int rot, int& tm, int& tn) {
     constexpr int G = 8;             // 8 pair-rows (2048 rows of A) share each B tile while it is hot in L2
@@ -198,6 +199,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     } else {
         // ------------------------------------------------------------------ epilogue (4 warps, both CTAs)
         const int q = warp & 3;
+        uint8_t* stage = smem + STAGES * STAGE_BYTES + 256 + q * EPI_STAGE_BYTES_PER_WARP;      // coalescing buffer of this warp
         float alpha = p.alpha;
         if (p.scale_a) alpha *= *p.scale_a;
         if (p.scale_b) alpha *= *p.scale_b;
@@ -220,7 +222,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
             if (p.ep_mode == 1)      epilogue_rows_swiglu_fwd(p, t_row, row, tn * BN_HALF, alpha, tmax);
             else if (p.ep_mode == 2) epilogue_rows_swiglu_bwd(p, t_row, row, tn * BN, BN, alpha, tmax);
-            else                     epilogue_rows(p, t_row, row, tn * BN, BN, alpha, tmax, dst_row);
+            else                     epilogue_rows(p, t_row, row, tn * BN, BN, alpha, tmax, dst_row, stage);
             tc_fence_before_sync();
             mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));            // 2 x 128 arrivals at the leader
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
