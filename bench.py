@@ -280,6 +280,7 @@ def main():
             "gpu_launches": launches, "loss": loss_host, "sol_pct_of_spec_sheet_peak": sol_pct, "impl": "ours",
         }
         print(json.dumps(out))
+    trainer.close()
     trainer.comm.shutdown()
     return 0
 

@@ -220,6 +220,10 @@ class LLMQTrainer:
         return allocator_report(self.model)
 
     def close(self) -> None:
+        """Collective over the ranks: releases the peer-memory segments of the in-kernel collectives in a fixed order
+        (call it on every rank, with no step in flight), and stops the worker processes of the multi-GPU front end."""
         if self._pool:
             self._pool.close()
             self._pool = None
+        elif getattr(self, "model", None) is not None:
+            self.model.close()

@@ -128,6 +128,12 @@ def run_training(cfg: TrainingConfig, argv=None) -> dict:
             eval_loader = DataLoader(cfg.eval_file, T, cfg.eval_seed, rank, world)
         except FileNotFoundError:
             eval_loader = None
+    # The tokenizer's vocabulary may be smaller than the model's (implicit padding), never larger: ids beyond the embedding
+    # table would be out-of-bounds reads and writes on the device (train.cpp:429-439 refuses the same way).
+    for what, loader in (("training", train_loader), ("validation", eval_loader)):
+        lv = int(getattr(loader, "vocab_size", 0) or 0) if loader is not None else 0
+        if lv > mcfg.vocab_size:
+            raise ValueError(f"model vocab size {mcfg.vocab_size} does not match {what} data vocab size {lv}")
     step_tokens = B * T * GA * world
     steps = cfg.steps if cfg.steps > 0 else max(1, cfg.epochs * (train_loader.num_tokens // step_tokens))
 

@@ -1,8 +1,10 @@
 // Token embedding gather, its deterministic backward, and the bias gradient reduction.
 // Behavioural counterparts of src/kernels/encoder.cu:23-249 and src/kernels/bias.cu:14-195 of the reference.
-// The embedding backward works on token positions sorted by token id (sorted on the device by the
-// caller): one CTA owns one distinct token, walks its positions in ascending order and adds the fp32
-// sum to that embedding row, so the result is bitwise reproducible and needs no host-side bucketing.
+// The embedding backward needs no sort and no host work (the reference bucket-sorts the tokens on the CPU,
+// encoder.cu:187-221): a first kernel counts, for every position, how many earlier positions hold the same token
+// (its rank) and how many positions hold it at all; in the second kernel the rank-0 position of every distinct
+// token gathers the other positions of that token in ascending order and adds the fp32 sum to the embedding row.
+// Launch sizes depend only on B*T, nothing is read back by the host, the result is bitwise reproducible.
 #include "api.h"
 #include "common.cuh"
 
@@ -24,27 +26,90 @@ encoder_fwd_kernel(T* __restrict__ out, const int* __restrict__ tokens, const T*
     }
 }
 
-// sorted_pos: positions (b*T + t) ordered by token id (stable);  seg_start[s] .. seg_start[s+1]: segment s;
-// seg_token[s]: token id of the segment.
+// rank[p] = #{q < p : tok[q] == tok[p]},  count[p] = #{q : tok[q] == tok[p]}.  grid (ceil(BT/256), splits): every CTA
+// compares its 256 positions with one slice of all positions (staged through shared memory, read as broadcasts) and
+// adds its partial counts with integer atomics (exact, so the result does not depend on the order).  BT^2 compares:
+// 2.7e8 for 16384 tokens, a few microseconds.
+__global__ void __launch_bounds__(256)
+token_rank_kernel(int* __restrict__ rank, int* __restrict__ count, const int* __restrict__ tokens, int BT) {
+    __shared__ int chunk[2048];
+    const int p = blockIdx.x * 256 + threadIdx.x;
+    const int tok = p < BT ? tokens[p] : -1;
+    const int per_split = (BT + gridDim.y - 1) / gridDim.y;
+    const int q_begin = blockIdx.y * per_split, q_end = min(BT, q_begin + per_split);
+    int r = 0, c = 0;
+    for (int q0 = q_begin; q0 < q_end; q0 += 2048) {
+        const int n = min(2048, q_end - q0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += 256) chunk[i] = tokens[q0 + i];
+        __syncthreads();
+        const int before = min(n, max(0, p - q0));            // entries of this chunk with q < p
+        int i = 0;
+        for (; i < before; ++i) { const int m = chunk[i] == tok; r += m; c += m; }
+        for (; i < n; ++i) c += chunk[i] == tok;
+    }
+    if (p < BT) {
+        if (r) atomicAdd(rank + p, r);
+        if (c) atomicAdd(count + p, c);
+    }
+}
+
+// grid (BT, channel slices of 256 * vector width).  The CTA of position p works only if p is the first position of
+// its token: it lists the later positions with the same token in ascending order (skipped when the token occurs once)
+// and adds dout[p] + dout[those] to the token's embedding gradient row.
 template <typename T>
 __global__ void __launch_bounds__(256)
-encoder_bwd_kernel(T* __restrict__ dwte, const T* __restrict__ dout, const int* __restrict__ sorted_pos,
-                   const int* __restrict__ seg_start, const int* __restrict__ seg_token, int n_segments, int C) {
+encoder_bwd_kernel(T* __restrict__ dwte, const T* __restrict__ dout, const int* __restrict__ tokens, const int* __restrict__ rank,
+                   const int* __restrict__ count, int BT, int C, int V) {
     using Vt = Vec16<T>;
-    const int s = blockIdx.x;
-    if (s >= n_segments) return;
-    const int beg = seg_start[s], end = seg_start[s + 1];
-    const long long tok = seg_token[s];
-    for (int c = threadIdx.x * Vt::N; c < C; c += blockDim.x * Vt::N) {
-        float acc[Vt::N];
-        Vt cur = Vt::load(dwte + tok * C + c);
+    constexpr int LIST = 1024;
+    __shared__ int list[LIST];
+    __shared__ int warp_cnt[8];
+    const int p = blockIdx.x;
+    if (rank[p] != 0) return;
+    const long long tok = tokens[p];
+    if (tok < 0 || tok >= V) return;                           // ids outside the vocabulary never index memory
+    const int c = (blockIdx.y * 256 + threadIdx.x) * Vt::N;
+    const bool active = c < C;
+    float acc[Vt::N];
+    Vt cur;
+    if (active) {
+        cur = Vt::load(dwte + tok * C + c);
+        Vt g = Vt::load_stream(dout + static_cast<long long>(p) * C + c);
 #pragma unroll
-        for (int k = 0; k < Vt::N; ++k) acc[k] = to_float(cur.v[k]);
-        for (int j = beg; j < end; ++j) {
-            Vt g = Vt::load_stream(dout + static_cast<long long>(sorted_pos[j]) * C + c);
+        for (int k = 0; k < Vt::N; ++k) acc[k] = to_float(cur.v[k]) + to_float(g.v[k]);
+    }
+    int remaining = count[p] - 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int q0 = p + 1;
+    while (remaining > 0 && q0 < BT) {                          // uniform across the CTA
+        // fill the list with up to LIST later positions of this token, in ascending order
+        int filled = 0;
+        while (filled + 256 <= LIST && q0 < BT && filled < remaining) {
+            const int q = q0 + threadIdx.x;
+            const bool m = q < BT && tokens[q] == static_cast<int>(tok);
+            const unsigned ballot = __ballot_sync(0xffffffffu, m);
+            if (lane == 0) warp_cnt[warp] = __popc(ballot);
+            __syncthreads();
+            int base = filled, total = 0;
 #pragma unroll
-            for (int k = 0; k < Vt::N; ++k) acc[k] += to_float(g.v[k]);
+            for (int w = 0; w < 8; ++w) { if (w < warp) base += warp_cnt[w]; total += warp_cnt[w]; }
+            if (m) list[base + __popc(ballot & ((1u << lane) - 1u))] = q;
+            filled += total;
+            q0 += 256;
+            __syncthreads();
         }
+        if (active) {
+            for (int j = 0; j < filled; ++j) {
+                Vt g = Vt::load_stream(dout + static_cast<long long>(list[j]) * C + c);
+#pragma unroll
+                for (int k = 0; k < Vt::N; ++k) acc[k] += to_float(g.v[k]);
+            }
+        }
+        remaining -= filled;
+        __syncthreads();                                        // the list is rewritten in the next round
+    }
+    if (active) {
 #pragma unroll
         for (int k = 0; k < Vt::N; ++k) cur.v[k] = from_float<T>(acc[k]);
         cur.store(dwte + tok * C + c);
@@ -105,16 +170,26 @@ extern "C" int llmq_encoder_forward(void* out, const int* tokens, const void* wt
     return LLMQ_LAUNCH_CHECK();
 }
 
-extern "C" int llmq_encoder_backward(void* dwte, const void* dout, const int* sorted_pos, const int* seg_start,
-                                     const int* seg_token, int n_segments, int C, int dtype, cudaStream_t s) {
-    if (n_segments <= 0) return 0;
+// dwte[tokens[p]] += dout[p] for all p, summed per token in ascending position order.  `scratch` holds 2 * BT ints
+// (rank, count) and is cleared here.  Three launches on the stream, nothing comes back to the host.
+extern "C" int llmq_encoder_backward(void* dwte, const void* dout, const int* tokens, int* scratch, int BT, int C, int V,
+                                     int dtype, cudaStream_t s) {
+    if (BT <= 0) return 0;
+    if ((dtype == 0 && C % 8) || (dtype == 3 && C % 4)) return -1;
+    if (dtype != 0 && dtype != 3) return -10;
+    int* rank = scratch;
+    int* count = scratch + BT;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int) * 2 * static_cast<size_t>(BT), s);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    const int pblocks = ceil_div_i(BT, 256);
+    int splits = 1;
+    while (splits < 8 && pblocks * splits < 256 && BT / (splits * 2) >= 2048) splits *= 2;
+    token_rank_kernel<<<dim3(pblocks, splits), 256, 0, s>>>(rank, count, tokens, BT);
     if (dtype == 0) {
-        if (C % 8) return -1;
-        encoder_bwd_kernel<bf16><<<n_segments, 256, 0, s>>>(static_cast<bf16*>(dwte), static_cast<const bf16*>(dout), sorted_pos, seg_start, seg_token, n_segments, C);
-    } else if (dtype == 3) {
-        if (C % 4) return -1;
-        encoder_bwd_kernel<float><<<n_segments, 256, 0, s>>>(static_cast<float*>(dwte), static_cast<const float*>(dout), sorted_pos, seg_start, seg_token, n_segments, C);
-    } else return -10;
+        encoder_bwd_kernel<bf16><<<dim3(BT, ceil_div_i(C, 256 * 8)), 256, 0, s>>>(static_cast<bf16*>(dwte), static_cast<const bf16*>(dout), tokens, rank, count, BT, C, V);
+    } else {
+        encoder_bwd_kernel<float><<<dim3(BT, ceil_div_i(C, 256 * 4)), 256, 0, s>>>(static_cast<float*>(dwte), static_cast<const float*>(dout), tokens, rank, count, BT, C, V);
+    }
     return LLMQ_LAUNCH_CHECK();
 }
 

@@ -2,7 +2,8 @@
 // statistics kernels that go with it (per-position loss groups, log-sum-exp monitoring).
 // Behavioural counterpart of src/kernels/fused_classifier.cu:20-342 and fused_classifier_tma.cu:40-273:
 //   loss[row] += lse - logit[target];   dlogit = p * (dloss + z_reg * lse) - 1[target] * dloss;
-//   rows whose target is -100 get zero loss and zero gradient.
+//   rows whose target is -100 - or any other id outside [0, V), e.g. from a token file of a larger tokenizer - get
+//   zero loss and zero gradient; the id never indexes memory.
 // One CTA of 1024 threads owns a row.  Pass 1 streams the row once and keeps an online (max, sum);
 // pass 2 re-reads the row (still L2 resident: a bf16 row of 152k logits is 300 KB) and overwrites it
 // with the gradient using streaming stores, so HBM sees one read and one write per logit.
@@ -23,7 +24,7 @@ fused_ce_kernel(T* logits, float* __restrict__ losses, float* __restrict__ lse_o
     T* x = logits + row * ld;
     const int tgt = targets[row];
     const int nvec = V / Vt::N;
-    if (tgt == -100) {
+    if (tgt < 0 || tgt >= V) {                  // -100 = masked; other out-of-range ids are treated the same way
         if (write_dlogits) {
             Vt z;
 #pragma unroll

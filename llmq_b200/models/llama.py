@@ -141,6 +141,11 @@ class LlamaModel:
                 raise
             return None
 
+    def close(self) -> None:
+        """Collective: ordered release of the in-kernel collectives' peer-memory segments (see FusedCollectives.close)."""
+        if self.fused is not None:
+            self.fused.close()
+
     def _all_reduce_small(self, t: torch.Tensor, op: str) -> None:
         if self.fused is not None and t.dtype == torch.float32 and t.is_contiguous() and t.numel() * self.comm.world <= 4096:
             self.fused.all_reduce_small(t, op)
@@ -579,7 +584,8 @@ class LlamaModel:
         self._join_dw()
         if write_grads and not cfg.tie_word_embeddings:
             self.grads.notify_non_block(head_name)
-        K.lse_stats(self.lse_stats, self.lse_tok.view(-1), accumulate=False)
+        # max and sum of the per-token log-sum-exp over ALL micro-steps of the optimizer step (llama_model.cpp accumulates them too)
+        K.lse_stats(self.lse_stats, self.lse_tok.view(-1), accumulate=accumulate_dw)
 
     def _head_transposed(self, W: torch.Tensor) -> torch.Tensor:
         """W^T (C, V) of the LM-head weight, refreshed when the weights changed (once per optimizer step)."""
@@ -796,7 +802,7 @@ class LlamaModel:
         g.end_step()
         self.rng_state = (self.rng_state * 48271) % 2147483647
         loss, loss1k = self._reduce_loss(self.B * self.T * grad_accum)
-        ntok = float(self.B * self.T)
+        ntok = float(self.B * self.T * grad_accum)
         hs = self.host_scalars
         hs[0:2].copy_(self.norm_io, non_blocking=True)
         hs[2:4].copy_(self.lse_stats, non_blocking=True)

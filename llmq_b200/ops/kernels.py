@@ -578,9 +578,9 @@ def fused_classifier(logits: torch.Tensor, losses: torch.Tensor, lse: Optional[t
         return
     x = logits.float()
     tg = targets.reshape(rows).long()
-    valid = tg != -100
+    valid = (tg >= 0) & (tg < V)                # -100 and any other id outside the vocabulary: no loss, no gradient
     l = torch.logsumexp(x, -1)
-    safe = tg.clamp_min(0)
+    safe = tg.clamp(0, V - 1)
     picked = x.gather(1, safe[:, None])[:, 0]
     losses.reshape(rows).add_(torch.where(valid, l - picked, torch.zeros_like(l)))
     if lse is not None:
@@ -744,19 +744,20 @@ def encoder_forward(out: torch.Tensor, tokens: torch.Tensor, wte: torch.Tensor) 
 
 
 def encoder_backward(dwte: torch.Tensor, dout: torch.Tensor, tokens: torch.Tensor) -> None:
-    """dwte[tok] += sum of dout rows with that token; deterministic (positions are summed in ascending order)."""
+    """dwte[tok] += sum of dout rows with that token; deterministic (positions are summed in ascending order).
+    On the GPU everything happens in kernels on the current stream (no sort, no host synchronisation); token ids outside
+    the vocabulary are skipped."""
     V, C = dwte.shape
     flat = tokens.reshape(-1)
     if dwte.is_cuda:
-        sorted_tok, sorted_pos = torch.sort(flat, stable=True)
-        uniq, counts = torch.unique_consecutive(sorted_tok, return_counts=True)
-        seg_start = torch.zeros(uniq.numel() + 1, dtype=torch.int32, device=dwte.device)
-        seg_start[1:] = torch.cumsum(counts, 0)
-        L.check(L.kernels().llmq_encoder_backward(L.ptr(dwte), L.ptr(dout), L.ptr(sorted_pos.int()), L.ptr(seg_start), L.ptr(uniq.int()),
-                                                  int(uniq.numel()), C, L.dtype_code(dwte.dtype), L.stream_ptr()), "encoder_backward")
+        BT = flat.numel()
+        scratch = _scratch("encoder_bwd_rank", dwte.device, (2 * BT,), torch.int32)
+        L.check(L.kernels().llmq_encoder_backward(L.ptr(dwte), L.ptr(dout), L.ptr(flat), L.ptr(scratch), BT, C, V,
+                                                  L.dtype_code(dwte.dtype), L.stream_ptr()), "encoder_backward")
         return
+    ok = (flat >= 0) & (flat < V)
     acc = dwte.float()
-    acc.index_add_(0, flat.long(), dout.float().reshape(-1, C))
+    acc.index_add_(0, flat[ok].long(), dout.float().reshape(-1, C)[ok])
     dwte.copy_(acc.to(dwte.dtype))
 
 

@@ -86,7 +86,7 @@ class KernelError(RuntimeError):
 
 
 # Number of device kernels launched through this module (each entry point knows how many it launches).
-_EXTRA_LAUNCHES = {"rmsnorm_backward": 1, "bias_backward": 1, "attention_backward": 2}
+_EXTRA_LAUNCHES = {"rmsnorm_backward": 1, "bias_backward": 1, "attention_backward": 2, "encoder_backward": 1}
 launch_count = 0
 
 

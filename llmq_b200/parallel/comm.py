@@ -113,6 +113,10 @@ class TorchDistComm(Communicator):
             kwargs = {}
             if backend == "nccl":
                 kwargs["device_id"] = device
+                # NCCL is plumbing here (rendez-vous, barriers, the library-collectives mode); the in-kernel collectives map
+                # their own NVSwitch multicast objects over the same GPUs.  Keep NCCL off NVLS so that two owners never bind
+                # memory to multicast objects of one device at the same time (set NCCL_NVLS_ENABLE yourself to override).
+                os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
         self.group = group
         self.rank = dist.get_rank(group)

@@ -1,7 +1,9 @@
 """In-kernel collectives over NVLink peer memory: the symmetric heap and the calls into ``csrc/p2p_collectives.cu``.
 
 ``torch.distributed`` (NCCL) is used only as plumbing here: the rendez-vous that maps every rank's heap segments into
-every peer (``torch.distributed._symmetric_memory``) and a host barrier at set-up.  After that all traffic is
+every peer (``torch.distributed._symmetric_memory``) and a host barrier at set-up.  NCCL's own NVLink-SHARP (NVLS)
+algorithms are switched off by the communicator (``parallel/comm.py``), so that only this module binds device memory to
+NVSwitch multicast objects, and ``close()`` releases the segments in a fixed order on all ranks.  After that all traffic is
 issued by our own kernels with loads / stores on peer addresses, or with ``multimem`` loads on the NVSwitch
 multicast address when the platform offers one (``LLMQ_P2P_MULTIMEM=0`` forces plain peer loads; the failure
 tests use that).
@@ -100,6 +102,20 @@ class FusedCollectives:
         self.use_multimem = self.ctrl.multicast != 0
         torch.cuda.synchronize(device)
         comm.barrier()
+
+    def close(self) -> None:
+        """Ordered teardown, collective over the ranks: every rank finishes its device work, all ranks meet on the host,
+        and only then are the symmetric segments (and with them the multicast bindings) released.  Without it a rank that
+        leaves early unbinds memory that a slower peer's kernel may still be reading through the multicast address."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        torch.cuda.synchronize(self.device)
+        self.comm.barrier()
+        self.heap.segments.clear()
+        self.ctrl = None
+        torch.cuda.synchronize(self.device)
+        self.comm.barrier()
 
     # ---- flags
     def _flag_offset(self, channel: int) -> int:

@@ -35,6 +35,10 @@ def _worker(rank: int, world: int, port: int, conn, cfg, opts, B: int, T: int, G
             break
         name, args = msg
         if name == "close":
+            try:                                                 # all workers got "close": an orderly, collective release
+                tr.close()
+            except Exception:
+                pass
             break
         try:
             if name == "get_gradients":

@@ -116,10 +116,10 @@ class WeightsManager:
         def work_dtype(s):
             return self.matmul_dtype if (s.matrix and s.name in MATRICES) else self.model_dtype
 
-        # fused gathers need bf16 masters on the device and bf16 / e4m3 work copies
-        if self.fused is not None and not (self.master_dtype == torch.bfloat16 and self.model_dtype == torch.bfloat16 and not host_master
-                                           and self.matmul_dtype in (torch.bfloat16, torch.float8_e4m3fn)
-                                           and not (opts.persistent_quants and self.sharded)):
+        # fused gathers need bf16 masters and bf16 / e4m3 work copies; masters in pinned host memory are staged to the
+        # device first, kept e4m3 shards (--persistent-quants) are pushed as they are
+        if self.fused is not None and not (self.master_dtype == torch.bfloat16 and self.model_dtype == torch.bfloat16
+                                           and self.matmul_dtype in (torch.bfloat16, torch.float8_e4m3fn)):
             self.fused = None
         walloc = (lambda shape, dt: self.fused.heap.empty(shape, dt)) if self.fused is not None else (lambda shape, dt: _alloc(shape, dt, device))
         # ---- work buffers
@@ -242,7 +242,7 @@ class WeightsManager:
             # flags are polled by the consuming GEMMs themselves, tile by tile
             for s in self.block_specs:
                 if s.name not in MATRICES:
-                    f.quant_allgather(buf.t[s.name], self.master_blocks[l][s.name])
+                    f.quant_allgather(buf.t[s.name], self._to_device(self.master_blocks[l][s.name], "m_" + s.name))
             gen_vec = f.signal(ch_vec)
             for s in self.block_specs:
                 if s.name in MATRICES:
@@ -252,13 +252,14 @@ class WeightsManager:
                         st = self._stat(l, s.name)
                         q = self.quant_shards[l][s.name] if self.quant_shards is not None else None
                         if q is not None and self.quant_version[l] == self.version:
-                            f.push_allgather(full, q)                    # kept e4m3 shard: the master is not read again
+                            # kept e4m3 shard: the master is not read again (a shard in pinned host memory is staged first)
+                            f.push_allgather(full, self._to_device(q, "q_" + s.name))
                         else:
-                            f.quant_allgather(full, master, st[0:1], st[1:2])
+                            f.quant_allgather(full, self._to_device(master, "m_" + s.name), st[0:1], st[1:2])
                             if q is not None:
                                 q.copy_(self.comm.local_shard(full), non_blocking=True)      # own slot, as just pushed
                     else:
-                        f.quant_allgather(full, master)
+                        f.quant_allgather(full, self._to_device(master, "m_" + s.name))
             if self.quant_shards is not None:
                 self.quant_version[l] = self.version
             gen_mat = f.signal(ch_mat)
@@ -307,7 +308,7 @@ class WeightsManager:
             f = self.fused
             ch = CH_NONBLOCK + 2 * list(self.nb_work).index(slot)
             f.wait(ch, f.signal(ch))                     # every rank is done with the slot's previous content
-            f.quant_allgather(full, master)
+            f.quant_allgather(full, self._to_device(master, "nb_" + name))
             f.wait(ch + 1, f.signal(ch + 1))
         else:
             if master.data_ptr() != local.data_ptr():

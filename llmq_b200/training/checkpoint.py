@@ -48,12 +48,16 @@ def find_latest_checkpoint(directory: str) -> int:
 
 
 def clean_old_checkpoints(directory: str, keep_n: int, major_every: int = -1) -> List[int]:
-    """Keeps the newest ``keep_n`` checkpoints plus every step divisible by ``major_every``; returns what was removed."""
+    """Removes old checkpoints like the reference (src/training/checkpoint.cpp:170-189): nothing happens while at most
+    ``keep_n`` checkpoints exist; otherwise the steps divisible by ``major_every`` are set aside (never removed) and of the
+    remaining ones only the newest ``keep_n`` survive.  Returns the removed steps."""
     steps = get_all_checkpoints(directory)
+    if keep_n <= 0 or len(steps) <= keep_n:
+        return []
+    if major_every > 0:
+        steps = [s for s in steps if s % major_every != 0]
     removed = []
-    for s in steps[:-keep_n] if keep_n > 0 else []:
-        if major_every > 0 and s % major_every == 0:
-            continue
+    for s in sorted(steps)[:max(0, len(steps) - keep_n)]:
         shutil.rmtree(get_checkpoint_path(directory, s), ignore_errors=True)
         removed.append(s)
     return removed

@@ -14,7 +14,7 @@ import torch
 
 # dense TFLOP/s by dtype family
 GPU_SPECS: Dict[str, Dict[str, float]] = {
-    "NVIDIA B200": {"bf16": 2250.0, "fp8": 4500.0, "fp4": 9000.0, "fp32": 1100.0},
+    "NVIDIA B200": {"bf16": 2200.0, "fp8": 4500.0, "fp4": 9000.0, "fp32": 1100.0},
     "NVIDIA B100": {"bf16": 1800.0, "fp8": 3500.0, "fp4": 7000.0, "fp32": 900.0},
     "NVIDIA H100 80GB HBM3": {"bf16": 989.0, "fp8": 1979.0, "fp32": 494.0},
     "NVIDIA H100 PCIe": {"bf16": 756.0, "fp8": 1513.0, "fp32": 378.0},

@@ -1,5 +1,6 @@
 """The ``train`` and ``export-checkpoint`` entry points end to end on CPU with a tiny model and token files."""
 import json
+import math
 import os
 
 import pytest
@@ -42,13 +43,37 @@ def test_flag_surface_and_implications():
 
 
 def test_schedules():
+    """Values computed by hand from the reference's formulas (schedule.h:17-53, train.cpp:563-570)."""
     s = make_schedule("cosine", 1.0, 100, warmup=10, final_lr_fraction=0.1)
-    assert s.eval(0) == pytest.approx(0.1) and s.eval(9) == pytest.approx(1.0) and s.eval(100) == pytest.approx(0.1)
-    assert s.eval(55) == pytest.approx(0.55, abs=0.01)
+    assert s.eval(0) == pytest.approx(0.1) and s.eval(9) == pytest.approx(1.0)
+    # pos = (55 - 10) / 100 = 0.45 -> 0.5 cos(0.45 pi) + 0.5 = 0.578217 -> 0.9 * 0.578217 + 0.1
+    assert s.eval(55) == pytest.approx(0.620396, abs=1e-5)
+    # the warm-up is not subtracted from the denominator: at the last step pos = 0.9, not 1
+    assert s.eval(100) == pytest.approx(0.122025, abs=1e-5)
     l = make_schedule("linear", 1.0, 100, 0, 0.0)
-    assert l.eval(50) == pytest.approx(0.5)
+    assert l.eval(50) == pytest.approx(0.5) and l.eval(150) == pytest.approx(0.0)
+    lw = make_schedule("linear", 2.0, 50, 10, 0.5)
+    assert lw.eval(30) == pytest.approx(2.0 + (1.0 - 2.0) * 20 / 50)
+    # cool-down: end_steps = 80, applies for step > 80 with f = (step - 80) / 20
     w = make_schedule("wsd", 1.0, 100, 5, 1.0, cooldown=20)
-    assert w.eval(50) == 1.0 and w.eval(79) == 1.0 and 0 < w.eval(90) < 1 and w.eval(99) == pytest.approx(0.0)
+    assert w.eval(50) == 1.0 and w.eval(80) == 1.0
+    assert w.eval(90) == pytest.approx(1.0 - 0.5 ** 0.5) and w.eval(99) == pytest.approx(1.0 - (19 / 20) ** 0.5) and w.eval(100) == pytest.approx(0.0)
+    c = make_schedule("cosine", 1.0, 100, warmup=0, final_lr_fraction=0.0, cooldown=20)
+    at_end = 0.5 * math.cos(math.pi * 80 / 80) + 0.5
+    assert c.eval(80) == pytest.approx(at_end) and c.eval(40) == pytest.approx(0.5)
+    assert c.eval(90) == pytest.approx(at_end * (1 - 0.5 ** 0.5))
+    # the Python front end's schedule divides by (max_steps - warmup)
+    from llmq_b200.training.schedule import CosineLRSchedule
+    py = CosineLRSchedule(1.0, 100, 10, 0.1)
+    assert py.get_lr(55) == pytest.approx(0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * 0.5))) and py.get_lr(100) == pytest.approx(0.1)
+
+
+def test_token_file_with_larger_vocabulary_is_refused(tmp_path):
+    """Ids beyond the embedding table must never reach the kernels: the run stops before the first step."""
+    args = _args(tmp_path)
+    write_synthetic_token_file(str(tmp_path / "train-0.bin"), 40_000, 600, seed=0)        # tiny-qwen2 has 512 entries
+    with pytest.raises(ValueError, match="vocab size"):
+        train.main(args)
 
 
 def test_train_resume_and_export(tmp_path):

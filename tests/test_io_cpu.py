@@ -161,8 +161,10 @@ def test_checkpoint_resume_is_exact(tmp_path):
     # retention
     for s in (4, 5, 6, 8):
         ck.save_checkpoint(d, s, b)
-    assert ck.clean_old_checkpoints(d, 2, major_every=4) == [3, 5]
-    assert ck.get_all_checkpoints(d) == [4, 6, 8]
+    # like the reference: the major steps (4, 8) are set aside first, then the newest two of the others (5, 6) are kept
+    assert ck.clean_old_checkpoints(d, 2, major_every=4) == [3]
+    assert ck.get_all_checkpoints(d) == [4, 5, 6, 8]
+    assert ck.clean_old_checkpoints(d, 4) == []               # at most keep_n checkpoints exist: nothing to do
     # damaged checkpoints are refused
     shard = os.path.join(ck.get_checkpoint_path(d, 8), "adam.v.shard_000_of_001.safetensors")
     raw = open(shard, "rb").read()

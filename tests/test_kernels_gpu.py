@@ -405,6 +405,52 @@ def test_encoder_and_bias():
     close(res[1][2], res[0][2], rtol=1e-2, atol=5e-2)
 
 
+@pytest.mark.parametrize("BT,n_distinct,C,dt", [(4096, 3, 128, BF), (1000, 700, 64, torch.float32), (16384, 5000, 896, BF)])
+def test_encoder_backward_device_side(BT, n_distinct, C, dt):
+    """Sort-free embedding backward: heavy duplicates (more than one list round per token), mostly distinct tokens, ids
+    outside the vocabulary skipped; fp32 reference = ordered sum per token.  Run twice: bitwise reproducible."""
+    torch.manual_seed(BT)
+    V = 6000
+    tok = torch.randint(0, n_distinct, (BT,), dtype=torch.int32)
+    tok[5] = -100
+    tok[17] = V + 3                                           # from a larger tokenizer: must not touch memory
+    dout = torch.randn(BT, C).to(dt)
+    prev = torch.randn(V, C).to(dt)
+    ok = (tok >= 0) & (tok < V)
+    ref = prev.float().clone()
+    ref.index_add_(0, tok[ok].long(), dout.float()[ok])
+    outs = []
+    for _ in range(2):
+        dw = prev.clone().to(DEV)
+        K.encoder_backward(dw, dout.to(DEV), tok.to(DEV))
+        outs.append(dw.cpu())
+    assert torch.equal(outs[0], outs[1])
+    close(outs[0], ref, rtol=1e-2 if dt == BF else 1e-5, atol=0.5 if dt == BF else 1e-3)
+    untouched = torch.ones(V, dtype=torch.bool)
+    untouched[tok[ok].long()] = False
+    assert torch.equal(outs[0][untouched], prev[untouched])
+
+
+def test_fused_classifier_ignores_out_of_range_targets():
+    """Targets outside [0, V) behave like -100: zero loss, zero gradient row; rows with valid targets are unchanged."""
+    torch.manual_seed(3)
+    rows, V = 8, 1000
+    logits = torch.randn(rows, V).to(BF)
+    tg_ok = torch.randint(0, V, (rows,), dtype=torch.int32)
+    tg_bad = tg_ok.clone()
+    tg_bad[2], tg_bad[5] = V + 7, -3
+    res = []
+    for tg in (tg_ok, tg_bad):
+        lg = logits.clone().to(DEV)
+        losses = torch.zeros(rows, device=DEV)
+        lse = torch.zeros(rows, device=DEV)
+        K.fused_classifier(lg, losses, lse, tg.to(DEV), 1.0 / rows, write_dlogits=True)
+        res.append((lg.cpu(), losses.cpu()))
+    good = [i for i in range(rows) if i not in (2, 5)]
+    assert torch.equal(res[0][0][good], res[1][0][good]) and torch.equal(res[0][1][good], res[1][1][good])
+    assert (res[1][0][[2, 5]] == 0).all() and (res[1][1][[2, 5]] == 0).all()
+
+
 @pytest.mark.parametrize("HS,Hq,Hkv,T", [(64, 4, 2, 256), (128, 4, 1, 384), (64, 14, 2, 128), (128, 7, 1, 200)])
 def test_attention(HS, Hq, Hkv, T):
     torch.manual_seed(12)

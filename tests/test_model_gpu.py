@@ -41,9 +41,12 @@ def run(opts, tied=True, hs=64, steps=2, ga=2, lr=1e-3):
     return cfg, m, out, grads
 
 
-@pytest.mark.parametrize("mm,hs,tied", [(None, 64, True), ("e4m3", 64, True), ("e4m3", 128, False), (None, 128, False)])
-def test_step_matches_oracle(mm, hs, tied):
-    opts = LLamaOptions(matmul_type=mm)
+@pytest.mark.parametrize("mm,hs,tied,gdt", [(None, 64, True, None), ("e4m3", 64, True, None), ("e4m3", 128, False, None), (None, 128, False, None),
+                                            ("e4m3", 64, True, "e5m2"), ("e4m3", 128, False, "e5m2")])
+def test_step_matches_oracle(mm, hs, tied, gdt):
+    """bf16, e4m3 and e4m3 with e5m2 activation gradients (--matmul-dtype e4m3 --gradient-dtype e5m2, the reference's third
+    pinned configuration) against the fp32 autograd model."""
+    opts = LLamaOptions(matmul_type=mm, gradient_type=gdt)
     cfg = cfg_small(tied, hs)
     m = LlamaModel(cfg, opts, device="cuda:0", batch_size=B, seq_len=T)
     m.init_weights(0)

@@ -212,3 +212,32 @@ def test_nvtx_ranges(monkeypatch):
     with nvtx.range("update", torch.device("cuda", 0)):
         pass
     assert nvtx._state["on"] is False and nvtx.push("x") is False
+
+
+def test_api_level_training_script(tmp_path):
+    """scripts/train.py drives the whole run through the Python API: steps, evaluation cadence, checkpoints with
+    retention, resume from the latest checkpoint, final export."""
+    import json
+
+    from llmq_b200.scripts import train as api_train
+    from llmq_b200.training import checkpoint as ck
+    from llmq_b200.training.dataloader import write_synthetic_token_file
+
+    write_synthetic_token_file(str(tmp_path / "train-0.bin"), 30_000, 512, seed=0)
+    write_synthetic_token_file(str(tmp_path / "eval-0.bin"), 3_000, 512, seed=1)
+    base = ["--model", "tiny-qwen2", "--from-scratch", "--model-dtype", "fp32", "--batch", "2", "--seq-len", "32", "--grad-accumulation", "2",
+            "--lr", "1e-3", "--train-file", str(tmp_path / "train-*.bin"), "--eval-file", str(tmp_path / "eval-*.bin"),
+            "--eval-every-n-steps", "2", "--eval-num-steps", "2", "--ckpt-interval", "2", "--ckpt-keep-n", "1", "--name", "api",
+            "--out-dir", str(tmp_path / "out"), "--checkpoint-dir", str(tmp_path / "ckpt"), "--log-file", str(tmp_path / "log.json"),
+            "--gpus", "1", "--verbosity", "-2", "--log-gpu-util", "0"]
+    assert api_train.main(base + ["--steps", "5"]) == 0
+    log = json.load(open(tmp_path / "log.json"))
+    steps = [e for e in log if e["log"] == "step"]
+    assert [e["step"] for e in steps] == [0, 1, 2, 3, 4] and all(e["loss"] == e["loss"] for e in steps)
+    assert sum(e["log"] == "eval" for e in log) >= 3                       # steps 2 and 4 and the final one
+    assert ck.get_all_checkpoints(str(tmp_path / "ckpt")) == [4, 5]        # keep-n 1 removed step 2; the final state is step 5
+    assert os.path.exists(tmp_path / "out" / "model.safetensors") and os.path.exists(tmp_path / "out" / "config.json")
+    # resume: continues at step 5 and runs two more
+    assert api_train.main(base + ["--steps", "7", "--continue"]) == 0
+    log2 = json.load(open(tmp_path / "log.json"))
+    assert [e["step"] for e in log2 if e["log"] == "step"] == [5, 6]

@@ -20,8 +20,7 @@ def _worker(rank, world, port, multimem, q):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
                           LLMQ_P2P_MULTIMEM="1" if multimem else "0")
-        if not multimem:
-            os.environ["NCCL_NVLS_ENABLE"] = "0"
+        os.environ["NCCL_NVLS_ENABLE"] = "0"                 # NCCL is only the comparison here; our kernels own the multicast objects
         import torch.distributed as dist
         from llmq_b200.ops import kernels as K
         from llmq_b200.parallel.comm import TorchDistComm
@@ -121,8 +120,9 @@ def _worker(rank, world, port, multimem, q):
         except Exception as e:
             assert "timed out" in str(e)
         assert torch.ones(4, device=dev).sum().item() == 4
-        comm.barrier()
-        q.put((rank, "ok", bool(fc.use_multimem)))
+        used_multimem = bool(fc.use_multimem)
+        fc.close()                                          # every rank is done with the peers' memory before anything is unmapped
+        q.put((rank, "ok", used_multimem))
         comm.shutdown()
     except Exception as e:
         q.put((rank, "error", repr(e) + "\n" + traceback.format_exc()))

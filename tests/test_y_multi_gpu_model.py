@@ -49,6 +49,9 @@ def _worker(rank, world, port, q):
                     opts.persistent_quants, opts.offload_quants, opts.offload_master = True, mode.startswith("pqhost"), mode.startswith("pqhost")
                 m = LlamaModel(cfg, opts, comm, dev, B, T)
                 assert (m.fused is not None) == (coll == "fused") and m.mx == mx
+                # the managers decide for themselves whether they use the in-kernel collectives: check what really runs
+                assert (m.weights.fused is not None) == (coll == "fused"), (mode, zero)
+                assert (m.grads.fused is not None) == (coll == "fused"), (mode, zero)
                 assert m.grads.gemm_rs == mode.endswith("gemm_rs")
                 m.init_weights(3)
                 out = []
@@ -61,6 +64,7 @@ def _worker(rank, world, port, q):
                 torch.cuda.synchronize()
                 K.check_status(dev)
                 results[(zero, ga, mode)] = out
+                m.close()
                 del m
                 comm.barrier()
         q.put((rank, "ok", results))
