@@ -160,7 +160,7 @@ def main():
     ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--kmajor-backward", type=int, default=None, help="0 = backward GEMMs read MN-major operands in place, 1 = transposed fp8 copies (default)")
     ap.add_argument("--cuda-graphs", type=int, default=-1,
-                    help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs), 0 = plain launches, -1 = on for one GPU")
+                    help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs; default), 0 = plain launches")
     ap.add_argument("--zero-level", type=int, default=0, help="0 = pick from --gpus (1 GPU: unsharded, else 3)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -181,7 +181,7 @@ def main():
         cfg = cfg.replace(num_hidden_layers=args.layers)
     opts = LLamaOptions(recompute_swiglu=args.recompute == "swiglu", recompute_block=args.recompute == "block",
                         offload_master=args.offload_master, matmul_type=args.matmul_dtype, momentum_type="bf16", variance_type="bf16",
-                        lmhead_chunks=args.lmhead_chunks, collectives=args.collectives, use_cuda_graphs=(args.cuda_graphs == 1 or (args.cuda_graphs < 0 and args.gpus == 1)))
+                        lmhead_chunks=args.lmhead_chunks, collectives=args.collectives, use_cuda_graphs=(args.cuda_graphs != 0))
     if args.fuse_swiglu is not None:
         opts.fuse_swiglu = args.fuse_swiglu
     if args.overlap_dw is not None:

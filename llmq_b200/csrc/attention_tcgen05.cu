@@ -22,6 +22,7 @@
 //   * dQ   : one CTA per (batch, kv head, 128 queries) walks over the query heads of the group and their key
 //     blocks; dQ accumulates in TMEM and is drained once per head.
 // A small pre-pass computes delta = rowsum(dO * O).  Blocks with the longest walks are scheduled first.
+#include <cstdlib>
 #include "ptx_sm100.cuh"
 #include "api.h"
 #include "common.cuh"
@@ -996,6 +997,9 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
 
 }  // namespace
 
+int llmq_attention_forward_pingpong(void* out, float* lse, const void* qkv, int B, int T, int Hq, int Hkv, float* absmax,
+                                    unsigned int* status, cudaStream_t s);
+
 // qkv (B,T,Hq+2Hkv,HS) bf16 -> out (B,T,Hq,HS) bf16, lse (B,Hq,T) fp32.  HS in {64, 128}.
 // absmax (optional): atomic maximum of |out|, for the fp8 quantisation of the output.
 extern "C" int llmq_attention_forward(void* out, float* lse, const void* qkv, int B, int T, int Hq, int Hkv, int HS,
@@ -1003,7 +1007,13 @@ extern "C" int llmq_attention_forward(void* out, float* lse, const void* qkv, in
     if (B <= 0 || T <= 0) return 0;
     if (Hq % Hkv) return -1;
     if (HS == 64) return fwd_impl<64>(out, lse, qkv, B, T, Hq, Hkv, absmax, status, s);
-    if (HS == 128) return fwd_impl<128>(out, lse, qkv, B, T, Hq, Hkv, absmax, status, s);
+    if (HS == 128) {
+        // two query tiles per CTA, processed alternately (attention_fwd_pingpong.cu); LLMQ_ATTN_FWD_SINGLE=1 keeps the
+        // one-tile kernel of this file for comparisons
+        static const bool single = [] { const char* e = getenv("LLMQ_ATTN_FWD_SINGLE"); return e && e[0] == '1'; }();
+        if (!single) return llmq_attention_forward_pingpong(out, lse, qkv, B, T, Hq, Hkv, absmax, status, s);
+        return fwd_impl<128>(out, lse, qkv, B, T, Hq, Hkv, absmax, status, s);
+    }
     return -2;
 }
 

@@ -55,6 +55,9 @@ struct GemmParams {
     // the normal epilogue.  For outputs with fewer tiles than SMs and a long K (weight gradients of small models).
     int k_splits;
     float* partial;
+    // CTA-pair kernel: 1 when the kernel's third tensor map describes C (bf16, plain store) and the epilogue may write
+    // its staged 32 x 64 blocks with TMA stores instead of per-lane global stores
+    int c_tma;
 };
 
 // Adds bias[col0 .. col0+31] to the 32 values of one accumulator chunk (every lane needs the same 32 bias values:
@@ -100,7 +103,8 @@ constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * 128;
 // those scattered writes, not the tensor core, set the tile time (16384 x 37888 x 3584 e4m3: 1.62 ms against 1.46 ms
 // with the stores removed).
 __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_row, int row, int col_base, int ncols,
-                                              float alpha, float& tmax, __nv_bfloat16* dst_row = nullptr, uint8_t* stage = nullptr) {
+                                              float alpha, float& tmax, __nv_bfloat16* dst_row = nullptr, uint8_t* stage = nullptr,
+                                              const CUtensorMap* tmap_c = nullptr, int* stage_sel = nullptr) {
     using namespace sm100;
     const bool row_ok = row < p.M;
     if (stage != nullptr && p.c_dtype == 0 && !p.accumulate && dst_row == nullptr && (p.N & 7) == 0 && (p.ldc & 7) == 0 &&
@@ -108,7 +112,11 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
         const int lane = threadIdx.x & 31;
         const int sub = lane >> 3, ch = lane & 7;
         const int row_base = row - lane;
-        const uint32_t stage_addr = smem_u32(stage);
+        // With a tensor map for C the staged block leaves through one TMA store (box 64 columns x 32 rows, clipped at the
+        // matrix edges) issued by lane 0; two staging buffers alternate, a buffer is rewritten once the store that read it
+        // two blocks ago has finished reading (bulk-group accounting of lane 0).
+        const bool use_tma = tmap_c != nullptr && p.c_tma != 0 && stage_sel != nullptr;
+        uint32_t stage_addr = smem_u32(stage);
 #pragma unroll 1
         for (int c = 0; c < ncols; c += 64) {
             const int col0 = col_base + c;
@@ -136,11 +144,23 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
                     packed[16 * h + j] = *reinterpret_cast<uint32_t*>(&b);
                 }
             }
+            if (use_tma) {
+                stage_addr = smem_u32(stage) + static_cast<uint32_t>(*stage_sel) * EPI_STAGE_BYTES_PER_WARP;
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t a = stage_addr + lane * 128 + ((i ^ (lane & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(packed[4 * i]), "r"(packed[4 * i + 1]),
                              "r"(packed[4 * i + 2]), "r"(packed[4 * i + 3]) : "memory");
+            }
+            if (use_tma) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) { tma_store_2d(tmap_c, stage_addr, col0, row_base); tma_store_commit(); }
+                *stage_sel ^= 1;
+                continue;
             }
             __syncwarp();
             const int gcol = col0 + ch * 8;

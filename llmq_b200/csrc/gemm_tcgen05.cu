@@ -271,10 +271,12 @@ int llmq_encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, long
     return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
-int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream);
+int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int num_sms, cudaStream_t stream);
 
 // Tile-shape selection: 0 = automatic, 1 = force the one-CTA kernel, 2 = force the CTA-pair kernel.
 static int g_gemm_mode = 0;
+static int g_gemm_tma_store = 1;
+extern "C" void llmq_gemm_set_tma_store(int on) { g_gemm_tma_store = on; }
 extern "C" void llmq_gemm_set_mode(int mode) { g_gemm_mode = mode; }
 // Split-K workspace of the calling thread's next GEMMs: `floats` fp32 elements at `ws` (0 switches split-K off).
 // A GEMM uses it when its output has fewer than num_sms / 2 tiles of the one-CTA kernel and K is long enough.
@@ -399,7 +401,15 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias,
         p.rs_limit_ns = rs->rs_limit_ns;
     }
 
-    if (pair_kernel) return llmq_gemm_2cta_launch(ta, tb, p, num_sms, stream);
+    if (pair_kernel) {
+        // plain bf16 outputs leave the epilogue through TMA stores: a tensor map of C with 64-column x 32-row boxes
+        CUtensorMap tc = ta;
+        if (c_dtype == 0 && !accumulate && p.rs_world == 0 && p.ep_mode == 0 && (N % 8) == 0 && (ldc % 8) == 0 &&
+            (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && g_gemm_tma_store) {
+            if (llmq_encode_tmap_2d(&tc, C, 2, M, N, ldc, 32) == 0) p.c_tma = 1;
+        }
+        return llmq_gemm_2cta_launch(ta, tb, tc, p, num_sms, stream);
+    }
 
     static bool attr_set[64] = {};          // the attribute is per device
     int dev = 0;

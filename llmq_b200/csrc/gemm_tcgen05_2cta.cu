@@ -39,7 +39,9 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_WARPS = 4;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + EPI_WARPS * EPI_STAGE_BYTES_PER_WARP;
+// stages | 1 KiB for barriers and flags | two 1024-byte aligned staging buffers per epilogue warp | alignment slack
+constexpr int EPI_STAGE_OFFSET = STAGES * STAGE_BYTES + 1024;
+constexpr int SMEM_BYTES = EPI_STAGE_OFFSET + 2 * EPI_WARPS * EPI_STAGE_BYTES_PER_WARP + 1024;
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int rot, int& tm, int& tn) {
     constexpr int G = 8;             // 8 pair-rows (2048 rows of A) share each B tile while it is hot in L2
@@ -56,7 +58,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <bool F8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -199,7 +201,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     } else {
         // ------------------------------------------------------------------ epilogue (4 warps, both CTAs)
         const int q = warp & 3;
-        uint8_t* stage = smem + STAGES * STAGE_BYTES + 256 + q * EPI_STAGE_BYTES_PER_WARP;      // coalescing buffer of this warp
+        uint8_t* stage = smem + EPI_STAGE_OFFSET + q * 2 * EPI_STAGE_BYTES_PER_WARP;            // coalescing buffers of this warp
+        int stage_sel = 0;
+        if (p.c_tma && lane == 0) tma_prefetch_desc(&tmap_c);
         float alpha = p.alpha;
         if (p.scale_a) alpha *= *p.scale_a;
         if (p.scale_b) alpha *= *p.scale_b;
@@ -222,7 +226,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
             if (p.ep_mode == 1)      epilogue_rows_swiglu_fwd(p, t_row, row, tn * BN_HALF, alpha, tmax);
             else if (p.ep_mode == 2) epilogue_rows_swiglu_bwd(p, t_row, row, tn * BN, BN, alpha, tmax);
-            else                     epilogue_rows(p, t_row, row, tn * BN, BN, alpha, tmax, dst_row, stage);
+            else                     epilogue_rows(p, t_row, row, tn * BN, BN, alpha, tmax, dst_row, stage, &tmap_c, &stage_sel);
             tc_fence_before_sync();
             mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));            // 2 x 128 arrivals at the leader
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -292,6 +296,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             tmax = warp_reduce_max(tmax);
             if (lane == 0 && tmax > 0.f) atomic_max_float(p.absmax_out, tmax);
         }
+        if (p.c_tma && lane == 0) tma_store_wait<0>();          // the staged blocks have left shared memory and are written
     }
 
     // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
@@ -307,7 +312,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 }  // namespace
 
 // Same contract as llmq_gemm (which dispatches here for problems with at least one full 256-row tile).
-int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int num_sms, cudaStream_t stream) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -320,7 +325,7 @@ int llmq_gemm_2cta_launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
     const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * (p.ep_mode == 1 ? (p.ep_D + BN_HALF - 1) / BN_HALF : (p.N + BN - 1) / BN);
     int pairs = num_sms / 2;
     if (tiles < pairs) pairs = tiles;
-    if (p.elem_bytes == 1) gemm_tcgen05_2cta_kernel<true><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
-    else                   gemm_tcgen05_2cta_kernel<false><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (p.elem_bytes == 1) gemm_tcgen05_2cta_kernel<true><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
+    else                   gemm_tcgen05_2cta_kernel<false><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tc, p);
     return static_cast<int>(cudaGetLastError());
 }

@@ -451,7 +451,8 @@ def test_fused_classifier_ignores_out_of_range_targets():
     assert (res[1][0][[2, 5]] == 0).all() and (res[1][1][[2, 5]] == 0).all()
 
 
-@pytest.mark.parametrize("HS,Hq,Hkv,T", [(64, 4, 2, 256), (128, 4, 1, 384), (64, 14, 2, 128), (128, 7, 1, 200)])
+@pytest.mark.parametrize("HS,Hq,Hkv,T", [(64, 4, 2, 256), (128, 4, 1, 384), (64, 14, 2, 128), (128, 7, 1, 200), (128, 8, 2, 1024), (128, 4, 4, 640),
+                                         (128, 2, 1, 96)])
 def test_attention(HS, Hq, Hkv, T):
     torch.manual_seed(12)
     B = 2
