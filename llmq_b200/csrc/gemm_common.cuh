@@ -107,15 +107,20 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
                                               const CUtensorMap* tmap_c = nullptr, int* stage_sel = nullptr) {
     using namespace sm100;
     const bool row_ok = row < p.M;
-    if (stage != nullptr && p.c_dtype == 0 && !p.accumulate && dst_row == nullptr && (p.N & 7) == 0 && (p.ldc & 7) == 0 &&
-        (reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) {
-        const int lane = threadIdx.x & 31;
+    // (`dst_row` redirection: the rows of one warp are consecutive rows of the same landing slot, N elements apart)
+    const int lane_id = threadIdx.x & 31;
+    __nv_bfloat16* const out_base = dst_row ? dst_row - static_cast<long long>(lane_id) * p.N
+                                            : static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row - lane_id) * p.ldc;
+    const long long out_ld = dst_row ? p.N : p.ldc;
+    if (stage != nullptr && p.c_dtype == 0 && !p.accumulate && (p.N & 7) == 0 && (out_ld & 7) == 0 &&
+        (reinterpret_cast<uintptr_t>(out_base) & 15u) == 0) {
+        const int lane = lane_id;
         const int sub = lane >> 3, ch = lane & 7;
         const int row_base = row - lane;
         // With a tensor map for C the staged block leaves through one TMA store (box 64 columns x 32 rows, clipped at the
         // matrix edges) issued by lane 0; two staging buffers alternate, a buffer is rewritten once the store that read it
         // two blocks ago has finished reading (bulk-group accounting of lane 0).
-        const bool use_tma = tmap_c != nullptr && p.c_tma != 0 && stage_sel != nullptr;
+        const bool use_tma = tmap_c != nullptr && p.c_tma != 0 && stage_sel != nullptr && dst_row == nullptr;
         uint32_t stage_addr = smem_u32(stage);
 #pragma unroll 1
         for (int c = 0; c < ncols; c += 64) {
@@ -171,8 +176,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
                 const uint32_t a = stage_addr + rr * 128 + ((ch ^ (rr & 7)) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w) : "r"(a) : "memory");
                 const int grow = row_base + rr;
-                if (grow < p.M && gcol < p.N)
-                    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(grow) * p.ldc + gcol) = o;
+                if (grow < p.M && gcol < p.N) *reinterpret_cast<uint4*>(out_base + rr * out_ld + gcol) = o;
             }
             __syncwarp();
         }

@@ -238,8 +238,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
             }
         }
-        if (p.rs_world > 0) {
-            // ---- tail: sum the slots of this rank's rows once every source delivered
+        if (p.rs_world > 0 && p.rs_dst != nullptr) {
+            // ---- tail (only when the caller asked for it; otherwise a separate kernel on the collectives stream finishes):
+            // sum the slots of this rank's rows once every source delivered
             volatile uint32_t* s_ok = abort_flag + 1;
             float* s_red = reinterpret_cast<float*>(const_cast<uint32_t*>(abort_flag + 2));
             if (warp == 2 && lane == 0) {

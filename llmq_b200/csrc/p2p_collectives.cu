@@ -149,6 +149,65 @@ reduce_scatter_kernel(PeerTable peers, const void* mc_base, long long src_offset
 }
 
 // ------------------------------------------------------------------------------------------------
+// Owner side of the reduce-scatter that weight-gradient GEMMs start in their epilogue (gemm_tcgen05_2cta.cu pushes every
+// output row into the owning rank's landing buffer and bumps its arrival counter per tile).  This kernel runs on the
+// collectives stream: it waits (bounded) until the local counter shows all sources, then sums the `world` LOCAL slots,
+// applies 1/world, adds into the gradient shard with stochastic rounding and collects the squared norm - the work of the
+// reference's ncclReduceScatter + vector_add_sr + global-norm pass (llama_gradients.cpp:50-77) without holding the SMs of
+// the GEMM while the peers are still sending.
+__global__ void __launch_bounds__(512)
+rs_finish_kernel(const bf16* __restrict__ landing, const unsigned int* counter, unsigned int target, long long n_shard, int rank, int world,
+                 bf16* dst, int accumulate, float scale, float* __restrict__ norm_partials, unsigned int seed, unsigned int* status,
+                 unsigned long long limit_ns) {
+    __shared__ float scratch[32];
+    __shared__ int arrived;
+    if (threadIdx.x == 0) {
+        const bool got = wait_flag(counter, target, limit_ns);
+        if (!got) atomicOr(status, sm100::kErrPeerFlag);
+        arrived = got ? 1 : 0;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (!arrived) return;
+    const long long nvec = n_shard / 8;
+    float ss = 0.f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+        for (int s = 0; s < world; ++s) {
+            const int src = (rank + s) % world;
+            Vec16<bf16> v = Vec16<bf16>::load_stream(landing + src * n_shard + i * 8);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += __bfloat162float(v.v[k]);
+        }
+        Vec16<bf16> o;
+        if (accumulate) {
+            Vec16<bf16> old = Vec16<bf16>::load(dst + i * 8);
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                const uint32_t r = rng_u32(static_cast<uint64_t>(i) * 4 + k / 2, seed);
+                o.v[k] = sr_bf16(acc[k] * scale + __bfloat162float(old.v[k]), r);
+                o.v[k + 1] = sr_bf16(acc[k + 1] * scale + __bfloat162float(old.v[k + 1]), r >> 16);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o.v[k] = __float2bfloat16_rn(acc[k] * scale);
+        }
+        if (norm_partials) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { float f = __bfloat162float(o.v[k]); ss += f * f; }
+        }
+        o.store(dst + i * 8);
+    }
+    if (norm_partials) {
+        ss = block_reduce_sum(ss, scratch);
+        if (threadIdx.x == 0) norm_partials[blockIdx.x] += ss;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // small all-reduce: push my n floats into slot [rank] of every peer, flag, wait, reduce locally.  One CTA.
 __global__ void __launch_bounds__(256)
 allreduce_small_kernel(PeerTable peers, long long slots_offset_bytes, long long flag_offset_bytes, float* data, int n, int rank, int world,
@@ -243,5 +302,17 @@ extern "C" int llmq_p2p_allreduce_small(void* const* peer_bases, long long slots
     if (world > MAX_PEERS || n <= 0) return -1;
     allreduce_small_kernel<<<1, 256, 0, s>>>(make_table(peer_bases, world), slots_offset_bytes, flag_offset_bytes, data, n, rank, world, op,
                                              gen, status, static_cast<unsigned long long>(limit_seconds * 1e9));
+    return LLMQ_LAUNCH_CHECK();
+}
+
+// landing: this rank's landing buffer [world][n_shard] bf16 (local memory); counter: its local arrival counter.
+extern "C" int llmq_p2p_rs_finish(const void* landing, const unsigned int* counter, unsigned int target, long long n_shard, int rank,
+                                  int world, void* dst, int accumulate, float scale, float* norm_partials, int num_partials,
+                                  unsigned int seed, unsigned int* status, double limit_seconds, int num_sms, cudaStream_t s) {
+    if (n_shard <= 0) return 0;
+    if (n_shard % 8 || world > MAX_PEERS) return -1;
+    int g = norm_partials ? num_partials : grid_for(n_shard / 8, 512, num_sms, 2);
+    rs_finish_kernel<<<g, 512, 0, s>>>(static_cast<const bf16*>(landing), counter, target, n_shard, rank, world, static_cast<bf16*>(dst),
+                                       accumulate, scale, norm_partials, seed, status, static_cast<unsigned long long>(limit_seconds * 1e9));
     return LLMQ_LAUNCH_CHECK();
 }

@@ -110,7 +110,7 @@ class LlamaModel:
         # per-block CUDA graphs: only where a block body contains nothing but kernels on fixed buffers
         self.graphs = None
         if (opts.use_cuda_graphs and self.device.type == "cuda" and not opts.offload_residual
-                and os.environ.get("LLMQ_GEMM_RS", "0") != "1" and os.environ.get("LLMQ_GEMM_POLL", "0") != "1"):
+                and os.environ.get("LLMQ_GEMM_POLL", "0") != "1"):
             self.graphs = _BlockGraphs(self.device)
         self.weights = WeightsManager(cfg, opts, self.comm, self.device, self.fused)
         self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
@@ -379,7 +379,7 @@ class LlamaModel:
         am, sc = slot
         t = self.tmp
         kmajor = self._kmajor and dout_qT is not None and ready is None
-        if kmajor and dw_rs is None:
+        if kmajor:
             K.quantize_transpose(dout_q, dout_qT, sc, dout, am)
         else:
             K.quantize(dout_q, sc, dout, am)
@@ -392,17 +392,20 @@ class LlamaModel:
                 K.gemm(dinp, dout_q, WT, scale_a=sc, scale_b=w_scale)
             else:
                 K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
-        if dw_rs is not None:
-            self._launch_dw(lambda: dw_rs(dout_q, inp_q, sc, inp_scale))
-        elif kmajor:
+        if kmajor:
             i2 = inp_q.reshape(-1, inp_q.shape[-1])
             iT = t.inp_qT[:i2.numel()].view(i2.shape[1], i2.shape[0])
 
             def dw():
                 # the side stream runs these two in order, so one transposed-input buffer serves every GEMM of the block
                 K.transpose(iT, i2)
-                K.gemm(dW, dout_qT, iT, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
+                if dw_rs is not None:
+                    dw_rs(dout_qT, iT, sc, inp_scale, a_mn=False, b_mn=False)
+                else:
+                    K.gemm(dW, dout_qT, iT, scale_a=sc, scale_b=inp_scale, accumulate=accumulate)
             self._launch_dw(dw)
+        elif dw_rs is not None:
+            self._launch_dw(lambda: dw_rs(dout_q, inp_q, sc, inp_scale))
         else:
             self._launch_dw(lambda: K.gemm(dW, dout_q, inp_q, a_mn=True, b_mn=True, scale_a=sc, scale_b=inp_scale, accumulate=accumulate))
         if dbias is not None:

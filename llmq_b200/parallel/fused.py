@@ -179,7 +179,7 @@ class FusedCollectives:
     def gemm_rs_supported(self, M: int, N: int) -> bool:
         return M % self.world == 0 and (M // self.world) % 32 == 0 and M >= 256 and N % 8 == 0
 
-    def gemm_rs(self, landing: torch.Tensor, counter_id: int, dst: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False,
+    def gemm_rs(self, landing: torch.Tensor, counter_id: int, dst: Optional[torch.Tensor], a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False,
                 scale_a=None, scale_b=None, alpha: float = 1.0, prev: Optional[torch.Tensor] = None, shard_accumulate: bool = False,
                 shard_scale: float = 1.0, norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
         """dst (+)= shard_scale * (rows of this rank of the sum over ranks of (prev +) alpha * A @ B^T).
@@ -187,18 +187,18 @@ class FusedCollectives:
         One kernel: tcgen05 GEMM whose epilogue stores each output row into the owner rank's ``landing`` buffer
         ([world, M/world, N] bf16 in the heap, same allocation on every rank) and whose tail sums the slots.
         ``counter_id`` names the arrival counter of this landing buffer (one per buffer).  Callers make sure that every
-        rank finished reading the previous content of its landing buffer (signal / wait) before the next call."""
+        rank finished reading the previous content of its landing buffer (signal / wait) before the next call.
+
+        ``dst=None``: the kernel only pushes (no waiting, no summing tail, nothing that changes from call to call, so it
+        can sit in a CUDA graph); ``rs_finish`` on the collectives stream completes the reduce-scatter."""
         seg, off = self.heap.locate(landing)
         w = self.world
         M = landing.shape[0] * landing.shape[1]
         N = landing.shape[2]
         Kd = a.shape[0] if a_mn else a.shape[1]
-        if not self.gemm_rs_supported(M, N) or landing.dtype != torch.bfloat16 or dst.dtype != torch.bfloat16:
+        if not self.gemm_rs_supported(M, N) or landing.dtype != torch.bfloat16 or (dst is not None and dst.dtype != torch.bfloat16):
             raise ValueError("fused GEMM + reduce-scatter: unsupported shape or dtype")
-        key = ("rs", counter_id)
-        arrivals = int(L.kernels().llmq_gemm_rs_arrivals(M, N, w))
-        target = (self.gen.get(key, 0) + arrivals) & 0xFFFFFFFF
-        self.gen[key] = target
+        target = self._rs_next_target(counter_id, M, N) if dst is not None else 0
         ptrs = list(seg.hdl.buffer_ptrs)
         landing_arr = (ctypes.c_void_p * 8)(*([p + off for p in ptrs] + [0] * (8 - len(ptrs))))
         cptrs = list(self.ctrl.hdl.buffer_ptrs)
@@ -212,6 +212,28 @@ class FusedCollectives:
             int(shard_accumulate), ctypes.c_float(shard_scale), L.ptr(norm_partials), 0 if norm_partials is None else norm_partials.numel(),
             ctypes.c_uint(seed & 0xFFFFFFFF), ctypes.c_double(self.wait_limit_s), L.stream_ptr())
         L.check(rc, "gemm_rs")
+
+    def _rs_next_target(self, counter_id: int, M: int, N: int) -> int:
+        """The value the local arrival counter reaches once every rank delivered all tiles of one more [M, N] product."""
+        key = ("rs", counter_id)
+        arrivals = int(L.kernels().llmq_gemm_rs_arrivals(M, N, self.world))
+        target = (self.gen.get(key, 0) + arrivals) & 0xFFFFFFFF
+        self.gen[key] = target
+        return target
+
+    def rs_finish(self, landing: torch.Tensor, counter_id: int, dst: torch.Tensor, *, accumulate: bool, scale: float,
+                  norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
+        """Owner side of a push-only ``gemm_rs``: waits (bounded, on the device) for all sources' tiles of the landing buffer,
+        then dst (+)= scale * sum of the local slots, with stochastic rounding and the squared-norm partials.  One call per
+        ``gemm_rs(..., dst=None)`` on the same landing buffer, on the collectives stream."""
+        M = landing.shape[0] * landing.shape[1]
+        N = landing.shape[2]
+        target = self._rs_next_target(counter_id, M, N)
+        counter = ctypes.c_void_p(self.ctrl.base + self.RS_COUNTER_BASE + 4 * counter_id)
+        L.check(L.kernels().llmq_p2p_rs_finish(L.ptr(landing), counter, ctypes.c_uint(target), ctypes.c_longlong(dst.numel()), self.rank,
+                                               self.world, L.ptr(dst), int(accumulate), ctypes.c_float(scale), L.ptr(norm_partials),
+                                               0 if norm_partials is None else norm_partials.numel(), ctypes.c_uint(seed & 0xFFFFFFFF),
+                                               L.ptr(self.status), ctypes.c_double(self.wait_limit_s), self.sms, L.stream_ptr()), "p2p_rs_finish")
 
     def all_reduce_small(self, t: torch.Tensor, op: str = "sum") -> None:
         """In-place sum / max / avg of a few fp32 values across ranks, one kernel, no library call."""

@@ -393,11 +393,13 @@ class GradientManager:
         # squared-norm partials: first half written by the side-stream reductions, second half by GEMMs with the
         # reduce-scatter inside (main stream), so the two streams never touch the same word
         self.norm_partials = torch.zeros(2 * K.NORM_PARTIALS, dtype=torch.float32, device=device) if self.fused is not None else None
-        # Weight-gradient GEMMs with the reduce-scatter inside the kernel.  Off unless LLMQ_GEMM_RS=1: the kernel's tail
-        # has to wait for the peers while it holds every SM, which measured 521 ms against 497 ms per step (Qwen2.5-7B,
-        # 2 GPUs) for the plain GEMM followed by the pull reduce-scatter kernel on the collectives stream.
-        self.gemm_rs = self.fused is not None and os.environ.get("LLMQ_GEMM_RS", "0") == "1"
-        self._rs_names: set = set()
+        # Weight-gradient GEMMs start their reduce-scatter in the epilogue: every output tile is pushed into the owner
+        # rank's landing buffer over NVLink while the tensor core works on the next tile; the owner-side sum (1/world,
+        # stochastic-rounding accumulation, norm partials) is one small kernel per matrix on the collectives stream that waits
+        # for its arrival counter (`_rs_finishers`).  Default; LLMQ_GEMM_RS=0 selects the plain GEMM followed by the pull
+        # reduce-scatter kernel.  Qwen2.5-7B, 2 GPUs, same box, alternating runs: 473.9 / 474.1 ms against 477.6 / 478.3 ms.
+        # (An earlier form that summed inside the GEMM kernel's tail held all SMs while it waited for the peers and lost.)
+        self.gemm_rs = self.fused is not None and os.environ.get("LLMQ_GEMM_RS", "1") == "1"
         self._fdone: Dict[int, tuple] = {}           # channel -> (generation, event) of the last reduction reading a buffer
         self._fevents: List = []
         _heap = self.fused.heap if self.fused is not None else None
@@ -454,14 +456,17 @@ class GradientManager:
             torch.cuda.current_stream(self.device).wait_event(ev)
             self.fused.wait(ch_ready + 1, gen)
 
-    def _reduce_fused(self, ch_ready: int, pairs, accumulate: bool, seed: int) -> None:
+    def _reduce_fused(self, ch_ready: int, pairs, accumulate: bool, seed: int, finishers=()) -> None:
         """pairs: [(full tensor in the heap, destination shard)].  Main stream: flag "my gradients are complete".
-        Side stream: wait for every rank's flag, pull-and-reduce this rank's rows, flag "done reading"."""
+        Side stream: the owner-side halves of the in-GEMM reduce-scatters (``finishers``: each waits for its own arrival
+        counter), then wait for every rank's flag, pull-and-reduce this rank's rows, flag "done reading"."""
         f = self.fused
         main = torch.cuda.current_stream(self.device)
         gen = f.signal(ch_ready)
         f.stream.wait_stream(main)
         with torch.cuda.stream(f.stream):
+            for fin in finishers:
+                fin()
             f.wait(ch_ready, gen)
             for k, (full, dst) in enumerate(pairs):
                 f.reduce_scatter(full, dst, accumulate=accumulate, scale=1.0 / self.comm.world,
@@ -475,11 +480,10 @@ class GradientManager:
     def _block_seed(self, l: int) -> int:
         return (self.seed * 7919 + self.step * 104729 + l * 131 + self._acc_count[l] * 7) & 0x7FFFFFFF
 
-    def fused_dw(self, l: int, name: str):
-        """A callable ``run(a, b, scale_a, scale_b)`` that computes this rank's weight gradient ``a^T-stored @ b`` and
-        reduce-scatters it inside the same kernel (the result lands in the shard), or ``None`` when the plain GEMM
-        followed by ``notify_block`` has to be used: no peer-memory path, the reduction does not follow this
-        micro-step, or the shape does not split into row shards of a multiple of 32 rows."""
+    def _rs_plan(self, l: int, name: str):
+        """(landing buffer, counter id, destination shard, accumulate) when the weight gradient ``name`` of layer ``l`` is
+        reduce-scattered from inside its GEMM in the current micro-step, else None.  Depends only on the step state, not
+        on whether the block body was executed by Python or replayed from a CUDA graph."""
         if not self.gemm_rs or not (self.sharded or (self.last and self.micro_step == 0)):
             return None
         k = next(i for i, s in enumerate(self.block_specs) if s.name == name)
@@ -490,31 +494,52 @@ class GradientManager:
         M, N = spec.shape
         if self.sharded:
             i = l % 2
-            landing, dst, acc, counter = self.bufs[i][name].view(w, M // w, N), self.shards[l][name], self._acc_count[l] > 0, i * 16 + k
-        else:
-            full = self.full[l][name]                       # the own slot of the landing buffer is the shard itself
-            landing, dst, acc, counter = full.view(w, M // w, N), self.comm.local_shard(full), False, 64 + l * 16 + k
-        seed = self._block_seed(l) + 17 * k
-        parts = self.norm_partials[K.NORM_PARTIALS:] if self.last else None
-        self._rs_names.add(name)
+            return self.bufs[i][name].view(w, M // w, N), i * 16 + k, self.shards[l][name], self._acc_count[l] > 0, k
+        full = self.full[l][name]                           # the own slot of the landing buffer is the shard itself
+        return full.view(w, M // w, N), 64 + l * 16 + k, self.comm.local_shard(full), False, k
 
-        def run(a, b, scale_a=None, scale_b=None):
-            self.fused.gemm_rs(landing, counter, dst, a, b, a_mn=True, b_mn=True, scale_a=scale_a, scale_b=scale_b, shard_accumulate=acc,
-                               shard_scale=1.0 / w, norm_partials=parts, seed=seed)
+    def fused_dw(self, l: int, name: str):
+        """A callable ``run(a, b, scale_a, scale_b)`` that computes this rank's weight gradient ``a^T-stored @ b`` with a
+        GEMM whose epilogue pushes every output row into the owner rank's landing buffer over NVLink (the reduce-scatter
+        starts tile by tile inside the GEMM; ``notify_block`` finishes it on the collectives stream), or ``None`` when the
+        plain GEMM has to be used: no peer-memory path, the reduction does not follow this micro-step, or the shape does
+        not split into row shards of a multiple of 32 rows."""
+        plan = self._rs_plan(l, name)
+        if plan is None:
+            return None
+        landing, counter = plan[0], plan[1]
+
+        def run(a, b, scale_a=None, scale_b=None, a_mn=True, b_mn=True):
+            self.fused.gemm_rs(landing, counter, None, a, b, a_mn=a_mn, b_mn=b_mn, scale_a=scale_a, scale_b=scale_b)
         return run
+
+    def _rs_finishers(self, l: int):
+        """The owner-side halves of this block's in-GEMM reduce-scatters: callables for the collectives stream."""
+        out, names = [], set()
+        for s in self.block_specs:
+            plan = self._rs_plan(l, s.name) if s.matrix else None
+            if plan is None:
+                continue
+            landing, counter, dst, acc, k = plan
+            seed = self._block_seed(l) + 17 * k
+            parts = self.norm_partials[:K.NORM_PARTIALS] if self.last else None
+            names.add(s.name)
+            out.append(lambda landing=landing, counter=counter, dst=dst, acc=acc, seed=seed, parts=parts: self.fused.rs_finish(
+                landing, counter, dst, accumulate=acc, scale=1.0 / self.comm.world, norm_partials=parts, seed=seed))
+        return out, names
 
     def notify_block(self, l: int) -> None:
         if self.fused is not None:
             seed = self._block_seed(l)
-            done, self._rs_names = self._rs_names, set()     # matrices already reduced inside their GEMM
+            finishers, done = self._rs_finishers(l)          # matrices whose reduce-scatter started inside their GEMM
             if not self.sharded:
                 if self.last:
                     self._reduce_fused(CH_GRADS + 2 * l, [(t, self.comm.local_shard(t)) for n, t in self.full[l].items() if n not in done],
-                                       False, seed)
+                                       False, seed, finishers)
             else:
                 i = l % 2
                 pairs = [(self.bufs[i][s.name], self.shards[l][s.name]) for s in self.block_specs if s.name not in done]
-                self._reduce_fused(CH_GRADS + 2 * i, pairs, self._acc_count[l] > 0, seed)
+                self._reduce_fused(CH_GRADS + 2 * i, pairs, self._acc_count[l] > 0, seed, finishers)
                 self._acc_count[l] += 1
             return
         if not self.sharded:
