@@ -2,6 +2,7 @@
 // global gradient norm with a deterministic reduction, and the stochastic-rounding vector add / reduce
 // used for sharded gradient accumulation.
 // Behavioural counterparts of src/kernels/{adamw,global_norm,vector_add}.cu of the reference.
+#include <cstring>
 #include "api.h"
 #include "common.cuh"
 
@@ -84,8 +85,17 @@ template <typename P, typename G, typename M, typename Vv>
 __global__ void __launch_bounds__(256)
 adamw_kernel(P* __restrict__ param, const G* __restrict__ grad, M* __restrict__ m_state, Vv* __restrict__ v_state,
              float* __restrict__ m_scales, long long n, float lr, float beta1, float beta2, float bc1, float bc2, float eps,
-             float wd, const float* __restrict__ grad_scale, float* __restrict__ absmax_out, uint32_t seed, long long elem_offset) {
+             float wd, const float* __restrict__ grad_scale, float* __restrict__ absmax_out, uint32_t seed, long long elem_offset,
+             const float* __restrict__ hyper) {
     __shared__ float scratch[32];
+    if (hyper) {
+        // Step-dependent scalars from device memory: {lr, beta1, beta2, 1/(1-beta1^t), 1/(1-beta2^t), eps, weight decay,
+        // seed bits}.  The launch itself is then the same every step and can be replayed from a CUDA graph; `wd` of the
+        // launch selects (non-zero) or masks (zero) the weight decay, `seed` is added to the step's seed.
+        lr = hyper[0]; beta1 = hyper[1]; beta2 = hyper[2]; bc1 = hyper[3]; bc2 = hyper[4]; eps = hyper[5];
+        wd = wd != 0.f ? hyper[6] : 0.f;
+        seed += __float_as_uint(hyper[7]);
+    }
     const float gs = grad_scale ? *grad_scale : 1.f;
     float tmax = 0.f;
     const long long nvec = n / 8;
@@ -247,10 +257,31 @@ vector_reduce_sr_kernel(T* dst, const T* src, float scale, int n_shards, int ski
 }  // namespace
 
 // dtype codes: param/grad: 0 bf16 | 3 fp32;  m: 0 | 3 | 1 (e4m3, needs m_scales and n % 128 == 0);  v: 0 | 3
+extern "C" int llmq_adamw_hyper(void*, const void*, void*, void*, float*, long long, float, float, float, int, float, float, const float*, float*,
+                                unsigned int, long long, int, int, int, int, int, const float*, cudaStream_t);
+
 extern "C" int llmq_adamw(void* param, const void* grad, void* m, void* v, float* m_scales, long long n, float lr, float beta1,
                           float beta2, int step, float eps, float wd, const float* grad_scale, float* absmax_out,
                           unsigned int seed, long long elem_offset, int p_dtype, int g_dtype, int m_dtype, int v_dtype,
                           int num_sms, cudaStream_t s) {
+    return llmq_adamw_hyper(param, grad, m, v, m_scales, n, lr, beta1, beta2, step, eps, wd, grad_scale, absmax_out, seed, elem_offset,
+                            p_dtype, g_dtype, m_dtype, v_dtype, num_sms, nullptr, s);
+}
+
+// Fills the 8 host floats that `hyper` points the kernel at, with the same arithmetic as the by-value launch.
+extern "C" void llmq_adamw_fill_hyper(float* out, float lr, float beta1, float beta2, int step, float eps, float wd, unsigned int seed) {
+    out[0] = lr; out[1] = beta1; out[2] = beta2;
+    out[3] = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
+    out[4] = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
+    out[5] = eps; out[6] = wd;
+    memcpy(out + 7, &seed, sizeof(seed));
+}
+
+// Same, with the step-dependent scalars optionally read from 8 floats in device memory (see adamw_kernel).
+extern "C" int llmq_adamw_hyper(void* param, const void* grad, void* m, void* v, float* m_scales, long long n, float lr, float beta1,
+                                float beta2, int step, float eps, float wd, const float* grad_scale, float* absmax_out,
+                                unsigned int seed, long long elem_offset, int p_dtype, int g_dtype, int m_dtype, int v_dtype,
+                                int num_sms, const float* hyper, cudaStream_t s) {
     if (n <= 0) return 0;
     if (n % 8) return -1;
     if (m_dtype == 1 && (n % 128 || !m_scales)) return -2;
@@ -261,7 +292,7 @@ extern "C" int llmq_adamw(void* param, const void* grad, void* m, void* v, float
     if (p_dtype == PC && g_dtype == GC && m_dtype == MC && v_dtype == VC) {                                         \
         adamw_kernel<P, G, M, V><<<g, 256, 0, s>>>(static_cast<P*>(param), static_cast<const G*>(grad), static_cast<M*>(m), \
                                                    static_cast<V*>(v), m_scales, n, lr, beta1, beta2, bc1, bc2, eps, wd,   \
-                                                   grad_scale, absmax_out, seed, elem_offset);                      \
+                                                   grad_scale, absmax_out, seed, elem_offset, hyper);               \
         return LLMQ_LAUNCH_CHECK();                                                                                 \
     }
     A_CASE(bf16, 0, bf16, 0, bf16, 0, bf16, 0)

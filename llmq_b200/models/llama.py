@@ -750,12 +750,25 @@ class LlamaModel:
         self.norm_partials.zero_()
         shard_of = {}
         norm_fused = getattr(g, "norm_fused", False)       # the reduce-scatter kernels already summed the squares
-        for name, master, spec, l in w.master_items():
-            gs = g.get_block_shard(l)[spec.name] if l is not None else g.get_nb_shard(spec.name)
-            shard_of[name] = gs
-            if not norm_fused:
+        items = list(w.master_items())
+        for name, master, spec, l in items:
+            shard_of[name] = g.get_block_shard(l)[spec.name] if l is not None else g.get_nb_shard(spec.name)
+        # Nothing offloaded: every launch of the norm and AdamW loops has the same arguments each step (the step's scalars
+        # travel through device memory), so with --use-cuda-graphs the ~400 small launches become two graph replays.
+        on_device = self.device.type == "cuda" and all(
+            t.device.type == "cuda" for name, master, spec, l in items for t in (master, shard_of[name], o.m[name], o.v[name]))
+        graph_opt = self.graphs is not None and on_device
+
+        def norms():
+            for name, master, spec, l in items:
+                gs = shard_of[name]
                 gd = gs if gs.device.type == self.device.type else gs.to(self.device, non_blocking=True)
                 K.norm_squared(self.norm_partials, gd)
+        if not norm_fused:
+            if graph_opt:
+                self.graphs.run(("opt-norm",), norms)
+            else:
+                norms()
         K.deterministic_sum(self.norm_io[0:1], g.norm_partials if norm_fused else self.norm_partials)
         if self.comm.world > 1:
             self._all_reduce_small(self.norm_io[0:1], "sum")
@@ -764,7 +777,23 @@ class LlamaModel:
         # ---- AdamW on every shard
         w.zero_absmax()
         seed_base = (self.rng_state * 1000003) & 0x7FFFFFFF
-        items = list(w.master_items())
+        if graph_opt:
+            if getattr(self, "_opt_hyper", None) is None:
+                self._opt_hyper = torch.zeros(8, dtype=torch.float32, device=self.device)
+                self._opt_hyper_host = torch.zeros(8, dtype=torch.float32, pin_memory=True)
+            K.adamw_hyper(self._opt_hyper_host, lr=lr, beta1=beta1, beta2=beta2, step=step, eps=eps, weight_decay=weight_decay, seed=seed_base)
+            self._opt_hyper.copy_(self._opt_hyper_host, non_blocking=True)
+
+            def adam_all():
+                for idx, (name, master, spec, l) in enumerate(items):
+                    am = w._stat(l, spec.name)[0:1] if (l is not None and spec.name in MATRICES and w.quantized) else None
+                    if master.numel() % 8:
+                        raise ValueError(f"parameter shard {name} has {master.numel()} elements; shard sizes must be multiples of 8")
+                    K.adamw(master.view(-1), shard_of[name].view(-1), o.m[name].view(-1), o.v[name].view(-1), lr=0.0, beta1=0.0, beta2=0.0,
+                            step=1, eps=0.0, weight_decay=1.0 if spec.matrix else 0.0, grad_scale=scale, absmax=am,
+                            m_scales=o.m_scales.get(name), seed=idx * 7919, elem_offset=self.comm.rank * master.numel(), hyper=self._opt_hyper)
+            self.graphs.run(("opt-adamw",), adam_all)
+            items = []                                           # the staged loop below has nothing left to do
         stager = self._stager
         staged = [None] * len(items)
 

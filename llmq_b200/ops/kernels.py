@@ -629,15 +629,19 @@ def _sr_cpu(x: torch.Tensor, dtype: torch.dtype, gen: torch.Generator) -> torch.
 def adamw(param: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Tensor, *, lr: float, beta1: float, beta2: float,
           step: int, eps: float, weight_decay: float, grad_scale: Optional[torch.Tensor] = None,
           absmax: Optional[torch.Tensor] = None, m_scales: Optional[torch.Tensor] = None, seed: int = 0,
-          elem_offset: int = 0, stochastic: bool = True) -> None:
-    """In-place AdamW on flat shards; fp32 math, stochastic rounding when storing to bf16 / e4m3."""
+          elem_offset: int = 0, stochastic: bool = True, hyper: Optional[torch.Tensor] = None) -> None:
+    """In-place AdamW on flat shards; fp32 math, stochastic rounding when storing to bf16 / e4m3.
+
+    ``hyper`` (GPU only, 8 fp32 values from ``adamw_hyper``): the step-dependent scalars are read from device memory, so
+    the launch is the same every step (CUDA-graph replay); ``weight_decay`` then only selects (non-zero) or masks the decay
+    and ``seed`` is an offset to the step's seed."""
     n = param.numel()
     if param.is_cuda:
-        L.check(L.kernels().llmq_adamw(L.ptr(param), L.ptr(grad), L.ptr(m), L.ptr(v), L.ptr(m_scales), _ll(n), _f(lr), _f(beta1), _f(beta2),
-                                       int(step), _f(eps), _f(weight_decay), L.ptr(grad_scale), L.ptr(absmax),
-                                       ctypes.c_uint(seed & 0xFFFFFFFF), _ll(elem_offset), L.dtype_code(param.dtype),
-                                       L.dtype_code(grad.dtype), L.dtype_code(m.dtype), L.dtype_code(v.dtype), num_sms(param.device),
-                                       L.stream_ptr()), "adamw")
+        L.check(L.kernels().llmq_adamw_hyper(L.ptr(param), L.ptr(grad), L.ptr(m), L.ptr(v), L.ptr(m_scales), _ll(n), _f(lr), _f(beta1),
+                                             _f(beta2), int(step), _f(eps), _f(weight_decay), L.ptr(grad_scale), L.ptr(absmax),
+                                             ctypes.c_uint(seed & 0xFFFFFFFF), _ll(elem_offset), L.dtype_code(param.dtype),
+                                             L.dtype_code(grad.dtype), L.dtype_code(m.dtype), L.dtype_code(v.dtype), num_sms(param.device),
+                                             L.ptr(hyper), L.stream_ptr()), "adamw")
         return
     gen = torch.Generator().manual_seed((seed * 2654435761 + elem_offset) % (2 ** 63))
     g = grad.float().reshape(-1)
@@ -665,6 +669,13 @@ def adamw(param: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Ten
         m.copy_(rnd(mf, m.dtype).reshape(m.shape))
     if absmax is not None:
         absmax.copy_(torch.maximum(absmax, param.float().abs().max().reshape_as(absmax)))
+
+
+def adamw_hyper(out: torch.Tensor, *, lr: float, beta1: float, beta2: float, step: int, eps: float, weight_decay: float, seed: int) -> None:
+    """Fills the 8 fp32 values that ``adamw(..., hyper=...)`` reads (``out``: pinned host tensor), with the arithmetic of
+    the by-value launch (fp32 bias corrections)."""
+    L.kernels().llmq_adamw_fill_hyper(L.ptr(out), _f(lr), _f(beta1), _f(beta2), int(step), _f(eps), _f(weight_decay),
+                                      ctypes.c_uint(seed & 0xFFFFFFFF))
 
 
 NORM_PARTIALS = 512
