@@ -316,3 +316,10 @@ extern "C" int llmq_p2p_rs_finish(const void* landing, const unsigned int* count
                                        accumulate, scale, norm_partials, seed, status, static_cast<unsigned long long>(limit_seconds * 1e9));
     return LLMQ_LAUNCH_CHECK();
 }
+
+// Copy-engine transfer between two device addresses of this process' address space; a peer GPU's mapped segment counts
+// (--memcpy-all-gather / --memcpy-send-recv: the reference's cudaMemcpyAsync collectives, src/utilities/comm.cpp:570-618).
+extern "C" int llmq_memcpy_d2d_async(void* dst, const void* src, long long bytes, cudaStream_t s) {
+    if (bytes <= 0) return 0;
+    return static_cast<int>(cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, s));
+}

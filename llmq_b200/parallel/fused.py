@@ -162,6 +162,46 @@ class FusedCollectives:
         L.check(L.kernels().llmq_p2p_quant_allgather(seg.peer_array, ctypes.c_longlong(off), L.ptr(shard), ctypes.c_longlong(nbytes // 2),
                                                      self.rank, self.world, None, None, 0, self.sms, L.stream_ptr()), "p2p_quant_allgather")
 
+    # ---- copy-engine forms (--memcpy-all-gather, --memcpy-send-recv + --all-to-all-reduce in process mode)
+    def _memcpy(self, dst_ptr: int, src_ptr: int, nbytes: int) -> None:
+        L.check(L.kernels().llmq_memcpy_d2d_async(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), ctypes.c_longlong(nbytes),
+                                                  L.stream_ptr()), "memcpy_d2d")
+
+    def copy_allgather(self, full: torch.Tensor) -> None:
+        """This rank's slot of ``full`` (already filled locally) goes into the same slot of every peer's ``full`` with
+        copy-engine transfers on the current stream, no SM involved (schedule_all_gather with memcpy in the reference,
+        comm.cpp:570-590)."""
+        seg, off = self.heap.locate(full)
+        nbytes = full.numel() * full.element_size() // self.world
+        ptrs = list(seg.hdl.buffer_ptrs)
+        mine = off + self.rank * nbytes
+        for k in range(1, self.world):
+            p = (self.rank + k) % self.world                      # every rank starts with a different peer
+            self._memcpy(ptrs[p] + mine, ptrs[self.rank] + mine, nbytes)
+
+    def copy_all_to_all(self, full: torch.Tensor, landing: torch.Tensor) -> None:
+        """Slot s of ``full`` goes into slot [this rank] of rank s's ``landing`` (same shape, in the heap) for every peer s,
+        with copy-engine transfers; the own slot is copied locally.  The send half of the all-to-all reduce-scatter
+        (schedule_destructive_all_to_all, comm.cpp:500-549; here the landing buffer is separate, so nothing is destroyed)."""
+        seg, off = self.heap.locate(full)
+        lseg, loff = self.heap.locate(landing)
+        nbytes = full.numel() * full.element_size() // self.world
+        src_base = list(seg.hdl.buffer_ptrs)[self.rank] + off
+        lptrs = list(lseg.hdl.buffer_ptrs)
+        for k in range(self.world):
+            s = (self.rank + k) % self.world
+            self._memcpy(lptrs[s] + loff + self.rank * nbytes, src_base + s * nbytes, nbytes)
+
+    def sum_slots(self, landing: torch.Tensor, dst: torch.Tensor, *, accumulate: bool, scale: float,
+                  norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
+        """dst (+)= scale * sum over the ``world`` local slots of ``landing`` (the receive half of the all-to-all reduction:
+        the kernel of ``rs_finish`` without a counter to wait for; callers order it after the arrival flags)."""
+        zero_counter = ctypes.c_void_p(self.ctrl.base + self.RS_COUNTER_BASE + 4 * 8000)      # a word nobody increments; target 0
+        L.check(L.kernels().llmq_p2p_rs_finish(L.ptr(landing), zero_counter, ctypes.c_uint(0), ctypes.c_longlong(dst.numel()), self.rank,
+                                               self.world, L.ptr(dst), int(accumulate), ctypes.c_float(scale), L.ptr(norm_partials),
+                                               0 if norm_partials is None else norm_partials.numel(), ctypes.c_uint(seed & 0xFFFFFFFF),
+                                               L.ptr(self.status), ctypes.c_double(self.wait_limit_s), self.sms, L.stream_ptr()), "p2p_rs_finish")
+
     def reduce_scatter(self, full: torch.Tensor, dst: torch.Tensor, *, accumulate: bool, scale: float,
                        norm_partials: Optional[torch.Tensor] = None, seed: int = 0) -> None:
         """dst (+)= scale * sum over ranks of rows [rank*n/w, (rank+1)*n/w) of ``full`` (bf16, in the heap)."""

@@ -71,7 +71,7 @@ def _rows(shape, world):
 
 
 # flag channels of the fused collectives (each channel = one word per source rank)
-CH_WEIGHTS, CH_NONBLOCK, CH_GRADS, CH_GRADS_NB = 0, 1024, 1100, 3000
+CH_WEIGHTS, CH_NONBLOCK, CH_GRADS, CH_GRADS_NB, CH_A2A = 0, 1024, 1100, 3000, 3500
 
 
 class _FusedPending:
@@ -240,9 +240,15 @@ class WeightsManager:
             f.wait(ch_free, f.signal(ch_free))
             # the small vectors first: their flag is awaited by a tiny kernel before the layer starts; the matrices'
             # flags are polled by the consuming GEMMs themselves, tile by tile
+            memcpy = bool(getattr(self.opts, "memcpy_all_gather", False))     # copy engines instead of SM stores for the pushes
             for s in self.block_specs:
                 if s.name not in MATRICES:
-                    f.quant_allgather(buf.t[s.name], self._to_device(self.master_blocks[l][s.name], "m_" + s.name))
+                    src = self._to_device(self.master_blocks[l][s.name], "m_" + s.name)
+                    if memcpy:
+                        self.comm.local_shard(buf.t[s.name]).copy_(src)
+                        f.copy_allgather(buf.t[s.name])
+                    else:
+                        f.quant_allgather(buf.t[s.name], src)
             gen_vec = f.signal(ch_vec)
             for s in self.block_specs:
                 if s.name in MATRICES:
@@ -251,13 +257,26 @@ class WeightsManager:
                     if self.quantized:
                         st = self._stat(l, s.name)
                         q = self.quant_shards[l][s.name] if self.quant_shards is not None else None
-                        if q is not None and self.quant_version[l] == self.version:
+                        if memcpy:
+                            # quantise (or fetch the kept shard) into the own slot, then copy-engine transfers to the peers
+                            local = self.comm.local_shard(full)
+                            if q is not None and self.quant_version[l] == self.version:
+                                local.copy_(q, non_blocking=True)
+                            else:
+                                K.quantize(local, st[1:2], self._to_device(master, "m_" + s.name), st[0:1])
+                                if q is not None:
+                                    q.copy_(local, non_blocking=True)
+                            f.copy_allgather(full)
+                        elif q is not None and self.quant_version[l] == self.version:
                             # kept e4m3 shard: the master is not read again (a shard in pinned host memory is staged first)
                             f.push_allgather(full, self._to_device(q, "q_" + s.name))
                         else:
                             f.quant_allgather(full, self._to_device(master, "m_" + s.name), st[0:1], st[1:2])
                             if q is not None:
                                 q.copy_(self.comm.local_shard(full), non_blocking=True)      # own slot, as just pushed
+                    elif memcpy:
+                        self.comm.local_shard(full).copy_(self._to_device(master, "m_" + s.name))
+                        f.copy_allgather(full)
                     else:
                         f.quant_allgather(full, self._to_device(master, "m_" + s.name))
             if self.quant_shards is not None:
@@ -308,7 +327,11 @@ class WeightsManager:
             f = self.fused
             ch = CH_NONBLOCK + 2 * list(self.nb_work).index(slot)
             f.wait(ch, f.signal(ch))                     # every rank is done with the slot's previous content
-            f.quant_allgather(full, self._to_device(master, "nb_" + name))
+            if getattr(self.opts, "memcpy_all_gather", False):
+                local.copy_(self._to_device(master, "nb_" + name))
+                f.copy_allgather(full)
+            else:
+                f.quant_allgather(full, self._to_device(master, "nb_" + name))
             f.wait(ch + 1, f.signal(ch + 1))
         else:
             if master.data_ptr() != local.data_ptr():
@@ -400,6 +423,12 @@ class GradientManager:
         # reduce-scatter kernel.  Qwen2.5-7B, 2 GPUs, same box, alternating runs: 473.9 / 474.1 ms against 477.6 / 478.3 ms.
         # (An earlier form that summed inside the GEMM kernel's tail held all SMs while it waited for the peers and lost.)
         self.gemm_rs = self.fused is not None and os.environ.get("LLMQ_GEMM_RS", "1") == "1"
+        # --all-to-all-reduce with --memcpy-send-recv (LLamaGradientsBlockSharded_AllToAll with memcpy transfers in the
+        # reference, llama_gradients.cpp:81-134): plain GEMMs, then copy-engine transfers of slot s to rank s's landing buffer
+        # and a local sum.  Without --memcpy-send-recv the all-to-all is the GEMM epilogue's push above (SM stores).
+        self.a2a_copy = bool(self.fused is not None and self.sharded and opts.use_all_to_all_reduce and getattr(opts, "memcpy_send_recv", False))
+        if self.a2a_copy:
+            self.gemm_rs = False
         self._fdone: Dict[int, tuple] = {}           # channel -> (generation, event) of the last reduction reading a buffer
         self._fevents: List = []
         _heap = self.fused.heap if self.fused is not None else None
@@ -412,6 +441,8 @@ class GradientManager:
         else:
             self.full = [{s.name: _galloc(s.shape) for s in self.block_specs} for _ in range(L)]
             self.pending: List = [None] * L
+        self.a2a_landing = ([{s.name: _galloc(s.shape) for s in self.block_specs if s.matrix and s.shape[0] % w == 0} for _ in range(2)]
+                            if self.a2a_copy else None)
         self.nb_full = {s.name: _galloc(s.shape) for s in self.nonblock_specs}
         self.nb_pending: Dict[str, object] = {}
         self._stage: Dict[str, torch.Tensor] = {}
@@ -456,7 +487,7 @@ class GradientManager:
             torch.cuda.current_stream(self.device).wait_event(ev)
             self.fused.wait(ch_ready + 1, gen)
 
-    def _reduce_fused(self, ch_ready: int, pairs, accumulate: bool, seed: int, finishers=()) -> None:
+    def _reduce_fused(self, ch_ready: int, pairs, accumulate: bool, seed: int, finishers=(), a2a=(), ch_a2a: int = 0) -> None:
         """pairs: [(full tensor in the heap, destination shard)].  Main stream: flag "my gradients are complete".
         Side stream: the owner-side halves of the in-GEMM reduce-scatters (``finishers``: each waits for its own arrival
         counter), then wait for every rank's flag, pull-and-reduce this rank's rows, flag "done reading"."""
@@ -467,6 +498,16 @@ class GradientManager:
         with torch.cuda.stream(f.stream):
             for fin in finishers:
                 fin()
+            if a2a:
+                # copy-engine all-to-all: every peer finished with its landing buffers before this block's backward began
+                # (get_block_full waited for all ranks' "done reading" flags), so the transfers can start right away
+                for full, landing, dst, sd in a2a:
+                    f.copy_all_to_all(full, landing)
+                f.wait(ch_a2a, f.signal(ch_a2a))             # every rank's slots have landed everywhere
+                w = self.comm.world
+                for full, landing, dst, sd in a2a:
+                    f.sum_slots(landing.view(w, -1), dst, accumulate=accumulate, scale=1.0 / w,
+                                norm_partials=self.norm_partials[:K.NORM_PARTIALS] if self.last else None, seed=sd)
             f.wait(ch_ready, gen)
             for k, (full, dst) in enumerate(pairs):
                 f.reduce_scatter(full, dst, accumulate=accumulate, scale=1.0 / self.comm.world,
@@ -538,8 +579,14 @@ class GradientManager:
                                        False, seed, finishers)
             else:
                 i = l % 2
+                a2a = []
+                if self.a2a_copy:
+                    for k, s in enumerate(self.block_specs):
+                        if s.name in self.a2a_landing[i]:
+                            a2a.append((self.bufs[i][s.name], self.a2a_landing[i][s.name], self.shards[l][s.name], seed + 17 * k))
+                            done.add(s.name)
                 pairs = [(self.bufs[i][s.name], self.shards[l][s.name]) for s in self.block_specs if s.name not in done]
-                self._reduce_fused(CH_GRADS + 2 * i, pairs, self._acc_count[l] > 0, seed, finishers)
+                self._reduce_fused(CH_GRADS + 2 * i, pairs, self._acc_count[l] > 0, seed, finishers, a2a, CH_A2A + i)
                 self._acc_count[l] += 1
             return
         if not self.sharded:

@@ -37,14 +37,18 @@ def _worker(rank, world, port, q):
         runs = [(zero, ga, mode) for zero, ga in CASES for mode in ("nccl", "fused", "fused+gemm_rs")]
         runs += [(3, 2, "mx-nccl"), (3, 2, "mx-fused")]          # block-scaled e4m3 matmuls on sharded bf16 weights
         runs += [(3, 2, "pq-fused"), (3, 2, "pqhost-fused")]     # quantised shards kept for the whole step (device / pinned host)
+        runs += [(2, 2, "copy-fused"), (3, 2, "copy-fused")]     # copy-engine all-gather and all-to-all reduction (the memcpy flags)
         for zero, ga, mode in runs:
             if True:
                 mx = mode.startswith("mx-")
                 pq = mode.startswith("pq")
-                coll = mode.split("-")[1] if (mx or pq) else mode.split("+")[0]
+                cp = mode.startswith("copy")
+                coll = mode.split("-")[1] if (mx or pq or cp) else mode.split("+")[0]
                 os.environ["LLMQ_GEMM_RS"] = "1" if mode.endswith("gemm_rs") else "0"
                 opts = LLamaOptions(matmul_type="mxe4m3" if mx else "e4m3", collectives=coll, momentum_type="bf16", variance_type="bf16")
                 opts.set_zero_level(zero)
+                if cp:
+                    opts.memcpy_all_gather = opts.memcpy_send_recv = opts.use_all_to_all_reduce = True
                 if pq:
                     opts.persistent_quants, opts.offload_quants, opts.offload_master = True, mode.startswith("pqhost"), mode.startswith("pqhost")
                 m = LlamaModel(cfg, opts, comm, dev, B, T)
@@ -53,6 +57,7 @@ def _worker(rank, world, port, q):
                 assert (m.weights.fused is not None) == (coll == "fused"), (mode, zero)
                 assert (m.grads.fused is not None) == (coll == "fused"), (mode, zero)
                 assert m.grads.gemm_rs == mode.endswith("gemm_rs")
+                assert m.grads.a2a_copy == cp
                 m.init_weights(3)
                 out = []
                 for step in range(1, 4):
@@ -113,5 +118,9 @@ def test_fused_training_matches_nccl():
         for (l0, n0), (l1, n1) in zip(r0[(3, 2, "fused")], r0[(3, 2, mode)]):
             assert abs(l0 - l1) < 5e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0), (mode, r0[(3, 2, mode)], r0[(3, 2, "fused")])
         assert r0[(3, 2, mode)][0][0] == r0[(3, 2, "fused")][0][0]          # the first forward pass sees the same weights
+    # copy-engine collectives: same protocol, the bytes travel by DMA instead of SM stores / loads
+    for zero in (2, 3):
+        for (l0, n0), (l1, n1) in zip(r0[(zero, 2, "nccl")], r0[(zero, 2, "copy-fused")]):
+            assert abs(l0 - l1) < 5e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0), (zero, r0[(zero, 2, "copy-fused")], r0[(zero, 2, "nccl")])
     # the block-scaled recipe follows the per-tensor one closely on this model
     assert abs(a[0][0] - r0[(3, 2, "nccl")][0][0]) < 5e-2
