@@ -158,6 +158,7 @@ def main():
                     help="ZeRO-3: keep the quantised weight shards on the device for the whole optimizer step (master weights are read once)")
     ap.add_argument("--fuse-swiglu", type=int, default=None)
     ap.add_argument("--overlap-dw", type=int, default=None)
+    ap.add_argument("--overlap-lmhead", type=int, default=None)
     ap.add_argument("--kmajor-backward", type=int, default=None, help="0 = backward GEMMs read MN-major operands in place, 1 = transposed fp8 copies (default)")
     ap.add_argument("--cuda-graphs", type=int, default=-1,
                     help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs; default), 0 = plain launches")
@@ -186,6 +187,8 @@ def main():
         opts.fuse_swiglu = args.fuse_swiglu
     if args.overlap_dw is not None:
         opts.overlap_dw = bool(args.overlap_dw)
+    if args.overlap_lmhead is not None:
+        opts.overlap_lmhead = bool(args.overlap_lmhead)
     if args.kmajor_backward is not None:
         opts.kmajor_backward = bool(args.kmajor_backward)
     zl = args.zero_level or (1 if args.gpus == 1 else 3)

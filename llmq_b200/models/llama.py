@@ -100,8 +100,11 @@ class LlamaModel:
             raise ValueError("sequence length exceeds max_position_embeddings")
         self.fused = self._make_fused()
         self._marks: List = []
-        self._dw_stream = (torch.cuda.Stream(self.device, priority=-1)
-                           if (opts.overlap_dw and self.device.type == "cuda") else None)
+        # second stream: weight-gradient GEMMs of the blocks (overlap_dw) and the LM-head gradient GEMMs of a chunk beside the
+        # next chunk's logits + classifier (overlap_lmhead)
+        self._side_stream = (torch.cuda.Stream(self.device, priority=-1)
+                             if ((opts.overlap_dw or opts.overlap_lmhead) and self.device.type == "cuda") else None)
+        self._dw_stream = self._side_stream if opts.overlap_dw else None
         self._mx_dw_event = None                  # block-scaled path: last weight-gradient GEMM that reads the shared operand buffers
         self._dw_events: List = []
         # SwiGLU inside the epilogues of the up-projection GEMM and of the down-projection's dX GEMM
@@ -232,7 +235,7 @@ class LlamaModel:
             raise ValueError("lmhead_chunks must divide batch * seq_len")
         t.logits = z(BT // chunks, V)
         # second buffer: the LM-head gradients of a chunk run beside the next chunk's logits + classifier
-        t.logits2 = z(BT // chunks, V) if (dev.type == "cuda" and o.overlap_dw and chunks > 1) else None
+        t.logits2 = z(BT // chunks, V) if (dev.type == "cuda" and o.overlap_lmhead and chunks > 1) else None
         t.lnf_T = z(C, BT // chunks) if dev.type == "cuda" else None      # lnf chunk transposed, B operand of the LM-head dW GEMM
         t.att_scratch = torch.zeros(B * Hq * T, dtype=torch.float32, device=dev)
         t.norm_scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32, device=dev)
@@ -416,8 +419,8 @@ class LlamaModel:
     # length of the backward pass.  On the GPU the dW GEMMs therefore go to a second, higher-priority stream: their
     # CTAs (one per SM, tensor-core bound) share the SMs with the memory-bound element-wise kernels of the main
     # stream.  Every block joins the side stream before it ends, so nothing outlives the buffers it reads.
-    def _launch_dw(self, fn):
-        side = self._dw_stream
+    def _launch_dw(self, fn, stream=None):
+        side = stream if stream is not None else self._dw_stream
         if side is None:
             fn()
             return None
@@ -434,12 +437,12 @@ class LlamaModel:
 
     def _wait_dw(self, ev) -> None:
         """The main stream waits for one weight-gradient GEMM."""
-        if self._dw_stream is not None and ev is not None:
+        if ev is not None:
             torch.cuda.current_stream(self.device).wait_event(ev)
 
     def _join_dw(self) -> None:
         """The main stream waits for every outstanding weight-gradient GEMM."""
-        if self._dw_stream is None:
+        if not self._dw_events:
             return
         main = torch.cuda.current_stream(self.device)
         for e in self._dw_events:
@@ -558,7 +561,7 @@ class LlamaModel:
         WT = self._head_transposed(W) if use_t else None
         # The chain is logits GEMM -> classifier -> next chunk's logits GEMM; dW and dX of a chunk only need its
         # classifier, so with a second logits buffer they run on the side stream under the next chunk's classifier.
-        side = self._dw_stream if (write_grads and t.logits2 is not None) else None
+        side = self._side_stream if (write_grads and t.logits2 is not None and self.opts.overlap_lmhead) else None
         main = torch.cuda.current_stream(self.device) if side is not None else None
         busy = [None, None]                                     # side-stream event of the last reader of each logits buffer
         for c in range(chunks):
@@ -583,7 +586,7 @@ class LlamaModel:
             if side is None:
                 grads_of_chunk()
             else:
-                busy[c % 2] = self._launch_dw(grads_of_chunk)
+                busy[c % 2] = self._launch_dw(grads_of_chunk, side)
         self._join_dw()
         if write_grads and not cfg.tie_word_embeddings:
             self.grads.notify_non_block(head_name)

@@ -26,7 +26,11 @@ class LLamaOptions:
     lmhead_chunks: int = 1
     attn_bwd_chunks: int = 1
     use_cuda_graphs: bool = False
-    overlap_dw: bool = True                   # weight-gradient GEMMs on a second stream, overlapping the element-wise kernels
+    # weight-gradient GEMMs of the blocks on a second stream, beside the element-wise kernels of the dX chain.  It paid while
+    # those GEMMs read MN-major operands and left the tensor pipe half idle (-10 ms per 7B step); with K-major operands they
+    # fill the SMs themselves and sharing costs more than it hides (477.7 ms off against 481-485 ms on, same box), so: off.
+    overlap_dw: bool = False
+    overlap_lmhead: bool = True               # LM-head gradient GEMMs of a chunk on the second stream, beside the next chunk's logits + classifier
     # bit 0 / 1: SwiGLU forward / backward inside GEMM epilogues (GPU, bf16 activations).  Bit-identical to the separate
     # kernels; off by default: with four epilogue warps per CTA the extra math takes as long as the memory pass it saves
     # (Qwen2.5-7B step: 495.6 ms without, 494.3 forward only, 498.9 backward only, 497.8 both).
