@@ -119,7 +119,7 @@ class LlamaModel:
         self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
         self.opt_state = OptimizerStateManager(cfg, opts, self.comm, self.device, self.weights)
         self._alloc_run_state()
-        self._stager = Stager(self.device)
+        self._stager = Stager(self.device, zero_copy=bool(opts.use_zero_copy))
         self.adam_seed = 42
         self.rng_state = 42                       # advanced every optimizer step; saved in checkpoints
 
@@ -208,51 +208,87 @@ class LlamaModel:
         self.acts = a
         self.lnf = z(BT, C)
         self.rstd_f = torch.zeros(BT, dtype=torch.float32, device=dev)
-        # temporaries shared by all layers
-        t = SimpleNamespace()
-        t.proj = z(BT, C)                 # attention-out / mlp-down results, folded into the next residual add
-        t.d_res = z(BT, C)                # gradient of the residual stream
-        t.d_ln = z(BT, C)                 # gradient wrt a norm output / attention output
-        t.d_sw = z(BT, D)
-        t.d_qkv = z(B, T, QC // HS, HS)
-        if q:
-            t.d_res_q = z(BT, C, dtype=self.gdtype)
-            t.d_up_q = z(BT, 2 * D, dtype=self.gdtype)
-            t.d_qkv_q = z(BT, QC, dtype=self.gdtype)
-        # fp8 backward with every GEMM operand K-major: transposed copies of the output gradients (written by the pass that
-        # quantises them), of the layer inputs and of the weights (small fp8 -> fp8 transposes next to the GEMM that reads them)
-        self._kmajor = bool(q and o.kmajor_backward and dev.type == "cuda" and self.qdtype in F8_TYPES and self.gdtype in F8_TYPES
-                            and all(v % 16 == 0 for v in (BT, C, 2 * D, QC)))
-        t.d_res_qT = t.d_up_qT = t.d_qkv_qT = None
-        if self._kmajor:
-            t.d_res_qT = z(C, BT, dtype=self.gdtype)
-            t.d_up_qT = z(2 * D, BT, dtype=self.gdtype)
-            t.d_qkv_qT = z(QC, BT, dtype=self.gdtype)
-            t.inp_qT = torch.zeros(max(C, D) * BT, dtype=self.qdtype, device=dev)
-            t.w_T = torch.zeros(max(2 * D, QC, C) * max(C, D), dtype=self.qdtype, device=dev)
+        # ---- temporaries shared by all layers, carved from ONE stack buffer (utils/memory.py, role of the reference's
+        # DeviceMemoryStack, stack.cpp:13-56 / llama_model.cpp:899-925).  The allocation pattern of a step is replayed twice:
+        # first on a dry-run stack, whose high-water mark sizes the backing buffer, then on the real one.  Buffers of
+        # different phases (LM head: logits chunks; block backward: activation gradients, their fp8 copies and transposes)
+        # are pushed and popped per phase, so they share addresses; the addresses are the same every step (CUDA graphs).
+        from ..utils.memory import DeviceMemoryStack
         chunks = max(1, o.lmhead_chunks)
         if BT % chunks:
             raise ValueError("lmhead_chunks must divide batch * seq_len")
-        t.logits = z(BT // chunks, V)
-        # second buffer: the LM-head gradients of a chunk run beside the next chunk's logits + classifier
-        t.logits2 = z(BT // chunks, V) if (dev.type == "cuda" and o.overlap_lmhead and chunks > 1) else None
-        t.lnf_T = z(C, BT // chunks) if dev.type == "cuda" else None      # lnf chunk transposed, B operand of the LM-head dW GEMM
-        t.att_scratch = torch.zeros(B * Hq * T, dtype=torch.float32, device=dev)
-        t.norm_scratch = torch.zeros(K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32, device=dev)
-        t.bias_scratch = torch.zeros(64 * QC, dtype=torch.float32, device=dev)
-        if self.mx:
-            # one A-role and one B-role operand buffer (values + tiled scales), sized for the largest use
-            feat = max(C, QC, 2 * D)
-            a_uses = [(BT, feat), (feat, BT)]
-            b_uses = [(2 * D, C), (C, 2 * D), (QC, C), (C, QC), (C, D), (D, C), (C, BT), (D, BT)]
-            t.mx_a_q = torch.zeros(BT * feat, dtype=torch.float8_e4m3fn, device=dev)
-            t.mx_a_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_A) for r, k in a_uses), dtype=torch.uint8, device=dev)
-            t.mx_a2_q = torch.zeros(BT * feat, dtype=torch.float8_e4m3fn, device=dev)       # column form of an output gradient
-            t.mx_a2_sf = torch.zeros_like(t.mx_a_sf)
-            t.mx_b2_q = torch.zeros(BT * max(C, D), dtype=torch.float8_e4m3fn, device=dev)  # transposed layer input (second stream)
-            t.mx_b2_sf = torch.zeros(max(K.mx_sf_bytes(r, BT, K.MX_TILE_B) for r in (C, D)), dtype=torch.uint8, device=dev)
-            t.mx_b_q = torch.zeros(max(r * k for r, k in b_uses), dtype=torch.float8_e4m3fn, device=dev)
-            t.mx_b_sf = torch.zeros(max(K.mx_sf_bytes(r, k, K.MX_TILE_B) for r, k in b_uses), dtype=torch.uint8, device=dev)
+        self._kmajor = bool(q and o.kmajor_backward and dev.type == "cuda" and self.qdtype in F8_TYPES and self.gdtype in F8_TYPES
+                            and all(v % 16 == 0 for v in (BT, C, 2 * D, QC)))
+        on_gpu = dev.type == "cuda"
+
+        def plan(stack):
+            t = SimpleNamespace()
+            names = []
+
+            def A(name, *shape, dtype=dt):
+                setattr(t, name, stack.allocate(shape, dtype, name))
+                names.append(name)
+
+            def end_phase(first, last=None):
+                for n in reversed(names[first:last]):
+                    stack.free(getattr(t, n))
+            # whole step
+            A("proj", BT, C)                 # attention-out / mlp-down results, folded into the next residual add
+            A("d_res", BT, C)                # gradient of the residual stream
+            A("d_ln", BT, C)                 # gradient wrt a norm output / attention output
+            A("norm_scratch", K.rmsnorm_backward_scratch_elems(C, dev), dtype=torch.float32)
+            A("bias_scratch", 64 * QC, dtype=torch.float32)
+            base = len(names)
+            # LM-head phase
+            A("logits", BT // chunks, V)
+            t.logits2 = t.lnf_T = None
+            if on_gpu and o.overlap_lmhead and chunks > 1:
+                A("logits2", BT // chunks, V)    # the LM-head gradients of a chunk run beside the next chunk's logits + classifier
+            if on_gpu:
+                A("lnf_T", C, BT // chunks)      # lnf chunk transposed, B operand of the LM-head dW GEMM
+            end_phase(base)
+            first = len(names)
+            # block-backward phase
+            A("d_sw", BT, D)
+            A("d_qkv", B, T, QC // HS, HS)
+            A("att_scratch", B * Hq * T, dtype=torch.float32)
+            if q:
+                A("d_res_q", BT, C, dtype=self.gdtype)
+                A("d_up_q", BT, 2 * D, dtype=self.gdtype)
+                A("d_qkv_q", BT, QC, dtype=self.gdtype)
+            # fp8 backward with every GEMM operand K-major: transposed copies of the output gradients (written by the pass
+            # that quantises them), of the layer inputs and of the weights (fp8 -> fp8 transposes next to their GEMM)
+            t.d_res_qT = t.d_up_qT = t.d_qkv_qT = None
+            if self._kmajor:
+                A("d_res_qT", C, BT, dtype=self.gdtype)
+                A("d_up_qT", 2 * D, BT, dtype=self.gdtype)
+                A("d_qkv_qT", QC, BT, dtype=self.gdtype)
+                A("inp_qT", max(C, D) * BT, dtype=self.qdtype)
+                A("w_T", max(2 * D, QC, C) * max(C, D), dtype=self.qdtype)
+            if self.mx:
+                # one A-role and one B-role operand buffer (values + tiled scales), sized for the largest use
+                feat = max(C, QC, 2 * D)
+                a_uses = [(BT, feat), (feat, BT)]
+                b_uses = [(2 * D, C), (C, 2 * D), (QC, C), (C, QC), (C, D), (D, C), (C, BT), (D, BT)]
+                f8, u8 = torch.float8_e4m3fn, torch.uint8
+                A("mx_a_q", BT * feat, dtype=f8)
+                A("mx_a_sf", max(K.mx_sf_bytes(r, k, K.MX_TILE_A) for r, k in a_uses), dtype=u8)
+                A("mx_a2_q", BT * feat, dtype=f8)                 # column form of an output gradient
+                A("mx_a2_sf", max(K.mx_sf_bytes(r, k, K.MX_TILE_A) for r, k in a_uses), dtype=u8)
+                A("mx_b2_q", BT * max(C, D), dtype=f8)            # transposed layer input (second stream)
+                A("mx_b2_sf", max(K.mx_sf_bytes(r, BT, K.MX_TILE_B) for r in (C, D)), dtype=u8)
+                A("mx_b_q", max(r * k for r, k in b_uses), dtype=f8)
+                A("mx_b_sf", max(K.mx_sf_bytes(r, k, K.MX_TILE_B) for r, k in b_uses), dtype=u8)
+            end_phase(first)
+            end_phase(0, base)
+            return t
+
+        sizing = DeviceMemoryStack(0, dry_run=True)
+        plan(sizing)
+        self.stack = DeviceMemoryStack(sizing.high_water, device=dev)
+        self.stack.backing.zero_()
+        t = plan(self.stack)
+        self.stack_report = {"capacity": self.stack.capacity, "high_water": self.stack.high_water, "breakdown": sizing.high_water_breakdown()}
         self.tmp = t
         self.host_scalars = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
 

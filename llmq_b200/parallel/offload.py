@@ -18,9 +18,13 @@ from ..utils import nvtx
 class Stager:
     """Double-buffered staging for a sequence of work items (parity = item index & 1)."""
 
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, zero_copy: bool = False):
         self.device = device
         self.enabled = device.type == "cuda"
+        # --use-zero-copy: no staging at all, the kernels read and write the pinned host tensors through their device mapping
+        # (the reference's alternative to double-buffered cudaMemcpy for offloaded optimizer state, adamw_optimizer.cpp:36-159)
+        self.zero_copy = zero_copy and self.enabled
+        self._alias: Dict[int, torch.Tensor] = {}
         if self.enabled:
             self.h2d = torch.cuda.Stream(device)
             self.d2h = torch.cuda.Stream(device)
@@ -40,6 +44,12 @@ class Stager:
         """-> (device tensor, event or None).  Device-resident tensors pass through untouched."""
         if not self.enabled or t.device.type == self.device.type:
             return t, None
+        if self.zero_copy:
+            a = self._alias.get(t.data_ptr())
+            if a is None or a.shape != t.shape or a.dtype != t.dtype:
+                from ..utils.memory import device_alias
+                a = self._alias[t.data_ptr()] = device_alias(t, self.device)
+            return a, None
         key = (kind, parity)
         buf = self._buf(key, t)
         with nvtx.range("offload fetch", self.device), torch.cuda.stream(self.h2d):
@@ -61,7 +71,7 @@ class Stager:
 
     def store(self, staged: torch.Tensor, host: torch.Tensor, kind: str, parity: int) -> None:
         """Writes ``staged`` (produced on the current stream) back to pinned ``host`` on the store stream."""
-        if not self.enabled or staged is host:
+        if not self.enabled or staged is host or staged.data_ptr() == host.data_ptr():
             return
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))

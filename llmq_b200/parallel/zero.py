@@ -58,8 +58,14 @@ def nonblock_param_specs(cfg: TransformerConfig) -> List[ParamSpec]:
     return specs
 
 
+_HOST_WRITE_COMBINED = False          # set by the managers from LLamaOptions.use_write_combined before they allocate
+
+
 def _alloc(shape, dtype, device, pinned=False):
     if pinned:
+        if _HOST_WRITE_COMBINED:
+            from ..utils.memory import host_tensor
+            return host_tensor(shape, dtype, write_combined=True)
         return torch.zeros(shape, dtype=dtype, pin_memory=torch.cuda.is_available())
     return torch.zeros(shape, dtype=dtype, device=device)
 
@@ -101,6 +107,8 @@ class _Buf:
 class WeightsManager:
     def __init__(self, cfg: TransformerConfig, opts: LLamaOptions, comm: Communicator, device: torch.device, fused=None):
         self.cfg, self.opts, self.comm, self.device = cfg, opts, comm, device
+        global _HOST_WRITE_COMBINED
+        _HOST_WRITE_COMBINED = bool(getattr(opts, "use_write_combined", False))      # offloaded tensors in write-combined pages
         self.fused = fused                    # FusedCollectives: gathers become in-kernel peer stores
         self.model_dtype = opts.model_type or cfg.dtype
         self.matmul_dtype = opts.matmul_dtype()

@@ -113,6 +113,11 @@ class TrainingRunLogger:
             if k.startswith("_"):
                 continue
             lines.append(f"  {k:<12}: device {v['device'] / 2**20:9.0f} MiB | pinned {v['pinned'] / 2**20:9.0f} MiB | host {v['host'] / 2**20:7.0f} MiB")
+        if "_stack" in rep:
+            st = rep["_stack"]
+            top = sorted(st.get("breakdown", {}).items(), key=lambda kv: -kv[1])[:4]
+            lines.append(f"  Stack high-water {st['high_water'] / 2**20:.0f} MiB of {st['capacity'] / 2**20:.0f} MiB"
+                         + (" (" + ", ".join(f"{k} {v / 2**20:.0f}" for k, v in top) + ")" if top else ""))
         if "_device" in rep:
             d = rep["_device"]
             lines.append(f"  Free {d['free'] / 2**20:.0f} MiB | Reserved {d['reserved'] / 2**20:.0f} MiB | Total {d['total'] / 2**20:.0f} MiB")

@@ -95,6 +95,45 @@ class DeviceMemoryStack:
         return out
 
 
+def host_tensor(shape, dtype: torch.dtype, write_combined: bool = False) -> torch.Tensor:
+    """A zero-filled CPU tensor in page-locked host memory that is mapped into the device address space (offloaded
+    state).  ``write_combined`` asks for write-combined pages (``--write-combined``): fast for the device to read over
+    PCIe and for the CPU to write, slow for the CPU to read - fine for state that only the GPU consumes.  Falls back to
+    torch's pinned allocator when the runtime library cannot allocate (no CUDA device)."""
+    n = 1
+    for s_ in shape:
+        n *= int(s_)
+    nbytes = n * torch.empty(0, dtype=dtype).element_size()
+    ptr = None
+    if nbytes > 0 and torch.cuda.is_available():
+        rt = L.runtime()
+        rt.llmq_host_alloc.restype = ctypes.c_void_p
+        ptr = rt.llmq_host_alloc(ctypes.c_longlong(nbytes), int(write_combined))
+    if not ptr:
+        return torch.zeros(shape, dtype=dtype, pin_memory=torch.cuda.is_available())
+    buf = (ctypes.c_uint8 * nbytes).from_address(ptr)
+    ctypes.memset(ptr, 0, nbytes)
+    t = torch.frombuffer(buf, dtype=torch.uint8).view(dtype).view(*shape)
+    import weakref
+    weakref.finalize(buf, rt.llmq_host_free, ctypes.c_void_p(ptr))      # the tensor keeps `buf` alive; free when both are gone
+    return t
+
+
+class _CudaView:
+    """Object with the CUDA array interface over an address range: lets torch build a device tensor on existing memory."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3, "strides": None}
+
+
+def device_alias(t: torch.Tensor, device: torch.device) -> torch.Tensor:
+    """A CUDA tensor over the memory of a page-locked, device-mapped host tensor (zero copy): kernels read and write the
+    host memory over the bus.  Under unified addressing the device pointer of mapped pinned memory equals the host pointer."""
+    assert t.device.type == "cpu" and t.is_contiguous()
+    raw = torch.as_tensor(_CudaView(t.data_ptr(), (t.numel() * t.element_size(),), "|u1"), device=device)
+    return raw.view(t.dtype).view(t.shape)
+
+
 def _nbytes(t) -> int:
     return t.numel() * t.element_size()
 
@@ -151,6 +190,8 @@ def allocator_report(model) -> Dict[str, Dict[str, int]]:
     for t in vars(model.tmp).values():
         if isinstance(t, torch.Tensor):
             _add(rep, "Stack", t, seen)
+    if getattr(model, "stack_report", None):
+        rep["_stack"] = dict(model.stack_report)             # dry-run sizing of the temporaries' stack: capacity, high-water mark, who was live
     if model.device.type == "cuda":
         free, total = torch.cuda.mem_get_info(model.device)
         rep["_device"] = {"free": free, "total": total, "reserved": torch.cuda.memory_reserved(model.device)}

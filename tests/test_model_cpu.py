@@ -166,3 +166,27 @@ def test_fp32_model_with_bf16_matmuls_tracks_fp32():
         a, b = g32[n].flatten().float(), gx[n].flatten().float()
         if a.norm() > 0:
             assert torch.dot(a, b) / (a.norm() * b.norm() + 1e-12) > 0.999, n
+
+
+def test_temporaries_live_on_the_stack_and_phases_share_addresses():
+    """The step's temporaries are views of one stack buffer sized by a dry run; LM-head buffers and block-backward buffers
+    are pushed and popped per phase, so they overlap, while the buffers that live for the whole step do not."""
+    from llmq_b200.config import create_config_from_name
+    from llmq_b200.models.llama import LlamaModel
+    from llmq_b200.options import LLamaOptions
+    from llmq_b200.utils.memory import allocator_report
+
+    cfg = create_config_from_name("tiny-qwen2", "fp32")
+    m = LlamaModel(cfg, LLamaOptions(lmhead_chunks=2), batch_size=2, seq_len=64)
+    t, back = m.tmp, m.stack.backing
+    lo, hi = back.data_ptr(), back.data_ptr() + back.numel()
+    span = lambda x: (x.data_ptr(), x.data_ptr() + x.numel() * x.element_size())
+    for name in ("proj", "d_res", "d_ln", "logits", "d_sw", "d_qkv", "att_scratch"):
+        a, b = span(getattr(t, name))
+        assert lo <= a and b <= hi, name
+    overlap = lambda x, y: span(x)[0] < span(y)[1] and span(y)[0] < span(x)[1]
+    assert overlap(t.logits, t.d_sw)                                 # different phases: same addresses
+    assert not overlap(t.proj, t.logits) and not overlap(t.d_res, t.d_sw) and not overlap(t.d_sw, t.d_qkv)
+    rep = m.stack_report
+    assert rep["capacity"] == rep["high_water"] == back.numel() and rep["breakdown"]
+    assert allocator_report(m)["_stack"]["high_water"] == rep["high_water"]

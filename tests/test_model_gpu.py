@@ -109,6 +109,8 @@ def test_fp32_model_matches_oracle(mm):
 @pytest.mark.parametrize("kw", [dict(recompute_swiglu=True), dict(recompute_block=True), dict(recompute_att=True, recompute_ffn=True),
                                 dict(recompute_rms_norm=True, recompute_qkv=True), dict(shard_weights=True, shard_gradients=True),
                                 dict(offload_master=True, offload_opt_m=True, offload_opt_v=True),
+                                dict(offload_master=True, offload_opt_m=True, offload_opt_v=True, use_zero_copy=True),
+                                dict(offload_master=True, offload_opt_m=True, offload_opt_v=True, use_write_combined=True),
                                 dict(offload_residual=True, recompute_block=True),
                                 dict(shard_weights=True, persistent_quants=True, offload_quants=True, offload_master=True)],
                          ids=lambda d: "+".join(d))
