@@ -19,3 +19,23 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+# Files whose GPU tests run with guard zones around every CUDA tensor the test creates through torch.zeros / empty / full
+# / *_like (llmq_b200/utils/guards.py): a kernel that writes past its output fails the test instead of silently changing a
+# neighbouring tensor.  (compute-sanitizer is not available for these runs; this is the bounds check that always runs.)
+_GUARDED = ("test_kernels_gpu.py", "test_mx_gpu.py", "test_fused_emulated_gpu.py", "test_zz_no_alloc.py")
+
+
+@pytest.fixture(autouse=True)
+def _guard_device_buffers(request):
+    import torch
+
+    if "gpu" not in request.keywords or not torch.cuda.is_available() or request.node.fspath.basename not in _GUARDED:
+        yield
+        return
+    from llmq_b200.utils.guards import guard_torch_allocations
+
+    with guard_torch_allocations("cuda"):
+        yield
+        torch.cuda.synchronize()

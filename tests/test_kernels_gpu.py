@@ -501,3 +501,20 @@ def test_native_unit_tests():
     exe = build_tests()
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ALL TESTS PASSED" in r.stdout, r.stdout + r.stderr
+
+
+def test_guard_zones_catch_a_write_past_the_end():
+    """The guard tooling itself: a write one element past a guarded tensor is reported, writes inside are not."""
+    from llmq_b200.utils.guards import GuardedAllocator
+
+    ga = GuardedAllocator(DEV)
+    a = ga.empty((33, 7), BF, "a")
+    b = ga.empty((5,), torch.float32, "b", fill=0.0)
+    a.fill_(1.0)
+    b.add_(2.0)
+    assert ga.check() == []
+    # the raw storage continues behind the view: address the first guard byte after `b` through an overlapping view
+    over = torch.as_strided(b, (6,), (1,))
+    over[5] = 3.0
+    msgs = ga.check()
+    assert len(msgs) == 1 and msgs[0].startswith("b ") and "after the buffer" in msgs[0] and "+0" in msgs[0]
