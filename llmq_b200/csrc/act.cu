@@ -2,6 +2,7 @@
 // Behavioural counterparts of src/kernels/swiglu.cu:21-405 and src/kernels/rope.cu:41-153 of the reference.
 #include "api.h"
 #include "common.cuh"
+#include "tile_transpose.cuh"
 
 namespace {
 
@@ -63,6 +64,48 @@ swiglu_fwd_kernel(T* __restrict__ out, e4m3* __restrict__ q_out, const T* __rest
         }
     }
     block_absmax_commit(absmax_out, tmax, scratch);
+}
+
+// SwiGLU recompute for the backward pass of an fp8 model: the only consumer of the recomputed activation is the
+// weight-gradient GEMM of the down projection, which reads it transposed (K-major), so this kernel writes nothing but
+// q_t[D][rows] = e4m3(swiglu(inp)[rows][D]) with the abs-max known from the forward pass.  One 128 x 128 tile per CTA; the
+// values are rounded to T first, exactly like swiglu_fwd_kernel's q_out path, so the bytes are the same.
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_fwd_transposed_kernel(e4m3* __restrict__ q_t, const T* __restrict__ inp, int rows, int D, const float* __restrict__ known_absmax,
+                             float* __restrict__ q_scale_out) {
+    static_assert(sizeof(T) == 2, "16-bit activations");
+    __shared__ __align__(16) uint32_t tile[128 * 32];
+    const int t = threadIdx.x;
+    const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
+    const float am = fmaxf(*known_absmax, 1e-10f);
+    const float qmul = 448.f / am;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0 && q_scale_out) *q_scale_out = am / 448.f;
+    const int cc = t & 15, rr = t >> 4;                    // 16 threads per row (8 elements each), 16 rows per pass
+    uint4 vu[8], vg[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const int r = r0 + p * 16 + rr, c = c0 + cc * 8;
+        const bool ok = r < rows && c < D;
+        const T* up = inp + static_cast<long long>(r) * 2 * D + c;
+        vu[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(up)) : make_uint4(0, 0, 0, 0);
+        vg[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(up + D)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const int lr = p * 16 + rr;
+        const T* u = reinterpret_cast<const T*>(&vu[p]);
+        const T* g = reinterpret_cast<const T*>(&vg[p]);
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float uf = to_float(u[k]), gf = to_float(g[k]);
+            f[k] = to_float(from_float<T>(uf * gf * fast_sigmoid(gf))) * qmul;
+        }
+        *reinterpret_cast<uint2*>(&tile[tile_word_index(lr, cc * 2)]) = pack_e4m3x8(f);
+    }
+    __syncthreads();
+    tile_store_transposed<e4m3>(tile, q_t, r0, c0, rows, D);
 }
 
 // Backward: dinp = [d_up | d_gate]; dinp may alias inp (in-place over the saved up-projection).
@@ -230,5 +273,16 @@ extern "C" int llmq_rope_table(float* freqs, int T, int HS, float theta, cudaStr
     int n = T * (HS / 2);
     if (n <= 0) return 0;
     rope_table_kernel<<<ceil_div_i(n, 256), 256, 0, s>>>(freqs, T, HS / 2, theta);
+    return LLMQ_LAUNCH_CHECK();
+}
+
+// q_t[D][rows] (e4m3) = transpose of the quantised SwiGLU output; rows and D multiples of 16, bf16 input [rows][2D].
+extern "C" int llmq_swiglu_forward_transposed(void* q_t, const void* inp, int rows, int D, const float* known_absmax, float* q_scale_out,
+                                              int dtype, cudaStream_t s) {
+    if (rows <= 0 || D <= 0) return 0;
+    if (rows % 16 || D % 16 || !known_absmax) return -11;
+    if (dtype != 0) return -10;
+    dim3 grid(ceil_div_i(D, 128), ceil_div_i(rows, 128));
+    swiglu_fwd_transposed_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<e4m3*>(q_t), static_cast<const bf16*>(inp), rows, D, known_absmax, q_scale_out);
     return LLMQ_LAUNCH_CHECK();
 }

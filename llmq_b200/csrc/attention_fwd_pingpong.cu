@@ -10,7 +10,7 @@
 //     columns 384..511  O_B
 //
 // Per 128-key tile j and query tile X the chain is  S_X = Q_X K_j^T  ->  softmax warpgroup X: max, exp2, bf16, P_X into
-// tensor memory  ->  O_X += P_X V_j (P is the A operand straight from tensor memory).  The two chains are independent,
+// tensor memory (handed over in two halves of 64 keys)  ->  O_X += P_X V_j (P is the A operand straight from tensor memory).  The two chains are independent,
 // so while one tile's warpgroup computes exponentials the tensor core runs the other tile's MMAs; the single-tile
 // kernel (attention_tcgen05.cu, still used for head size 64) left the tensor pipe idle during that time.
 // K and V tiles stream through two shared-memory stages each (TMA, 128-byte swizzle); Q_A and Q_B stay in shared memory
@@ -163,12 +163,18 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
                 mma_commit(s_full(x));
                 mma_commit(k_empty(st));
                 if (!mbar_wait(v_full(st), par, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(p_ready(x), j & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after_sync();
                 const uint32_t v_base = smem_u32(sV) + st * TILE_BYTES;
+                // P arrives in two halves of 64 keys (two barrier phases per tile): the first half's MMAs run while the
+                // warpgroup still exponentiates the second half
 #pragma unroll
-                for (int k = 0; k < BKV / 16; ++k)
-                    mma_issue_f16_tmem_a(tO, tS + k * 8, DLO(v_base, CHUNK_BYTES, k * (16 * 128)), hi, idesc_o, (j > 0 || k > 0));
+                for (int half = 0; half < 2; ++half) {
+                    if (!mbar_wait(p_ready(x), half, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int k = half * 4; k < half * 4 + 4; ++k)
+                        mma_issue_f16_tmem_a(tO, tS + k * 8, DLO(v_base, CHUNK_BYTES, k * (16 * 128)), hi, idesc_o, (j > 0 || k > 0));
+                }
+                if (!ok) break;
                 mma_commit(o_done(x));
                 mma_commit(v_empty(st));
             }
@@ -254,6 +260,11 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
                     pw[i / 2] = pack2(p0, p1);
                 }
                 tmem_st_32x32b_x16(tS + ch * 16, pw);
+                if (ch == 1) {                                  // first 64 keys of P are complete: hand them over
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                    warp_arrive(p_ready(x));
+                }
             }
             const float sum = sum0 + sum1;
             l_sum += sum;

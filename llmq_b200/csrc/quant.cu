@@ -4,6 +4,7 @@
 // QMAX is 448 for e4m3 and 57344 for e5m2 (the reference uses 448 for both, which wastes the e5m2 range).
 #include "api.h"
 #include "common.cuh"
+#include "tile_transpose.cuh"
 #include <type_traits>
 
 namespace {
@@ -90,16 +91,6 @@ transpose_kernel(Q* __restrict__ out, float* __restrict__ scale_out, const T* __
     }
 }
 
-// 4 x 4 byte transpose: words a..d hold bytes [x0 x1 x2 x3] of four consecutive rows; col[k] = [a_k b_k c_k d_k].
-__device__ __forceinline__ void transpose_4x4_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&col)[4]) {
-    uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
-    uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
-    col[0] = __byte_perm(t0, t1, 0x5410);
-    col[1] = __byte_perm(t0, t1, 0x7632);
-    col[2] = __byte_perm(t2, t3, 0x5410);
-    col[3] = __byte_perm(t2, t3, 0x7632);
-}
-
 // One 128 x 128 tile per CTA: reads in[rows][cols] (bf16/fp32: quantised with the given abs-max; 1-byte types: copied),
 // optionally writes the row-major 1-byte copy, and writes the transposed 1-byte copy out_t[cols][rows] so that the
 // weight-gradient GEMMs can read both operands K-major (the reference's quantize_and_transpose_with_abs_max,
@@ -177,24 +168,7 @@ tile_transpose_kernel(Q* __restrict__ out_rows, Q* __restrict__ out_t, float* __
         }
     }
     __syncthreads();
-    // thread = (16-row chunk rc, word column cw): 8 lanes of equal cw write 128 contiguous bytes of one output row
-    const int lane = t & 31, warp = t >> 5;
-    const int rc = lane & 7, cw = warp * 4 + (lane >> 3);
-    uint32_t w[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = tile[(rc * 16 + j) * 32 + (cw ^ (rc << 2))];
-    uint32_t o[4][4];            // o[g][k]: rows 4g..4g+3 of column k
-#pragma unroll
-    for (int g = 0; g < 4; ++g) transpose_4x4_bytes(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3], o[g]);
-    const int r = r0 + rc * 16;
-    if (r < rows) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            int c = c0 + cw * 4 + k;
-            if (c < cols)
-                *reinterpret_cast<uint4*>(out_t + static_cast<long long>(c) * rows + r) = make_uint4(o[0][k], o[1][k], o[2][k], o[3][k]);
-        }
-    }
+    tile_store_transposed<Q>(tile, out_t, r0, c0, rows, cols);
 }
 
 template <typename S, typename D>

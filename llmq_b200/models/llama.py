@@ -371,7 +371,7 @@ class LlamaModel:
         K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale, ready=ready)
 
     def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None, dw_rs=None,
-                swiglu_inout=None, swiglu_absmax=None, dout_qT=None):
+                swiglu_inout=None, swiglu_absmax=None, dout_qT=None, inp_qT_ready=False):
         """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
         W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second.
         ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside.
@@ -435,9 +435,12 @@ class LlamaModel:
             i2 = inp_q.reshape(-1, inp_q.shape[-1])
             iT = t.inp_qT[:i2.numel()].view(i2.shape[1], i2.shape[0])
 
+            have_T = inp_qT_ready
+
             def dw():
                 # the side stream runs these two in order, so one transposed-input buffer serves every GEMM of the block
-                K.transpose(iT, i2)
+                if not have_T:
+                    K.transpose(iT, i2)
                 if dw_rs is not None:
                     dw_rs(dout_qT, iT, sc, inp_scale, a_mn=False, b_mn=False)
                 else:
@@ -732,12 +735,23 @@ class LlamaModel:
             renorm(a.ln2[l], a.ln2_q[l] if q else None, S_LN2, a.res_att[l], p.ln2_w, a.rstd2[l])
         if re.up:
             self._fwd_mm(a.up[l], None if q else a.ln2[l], a.ln2_q[l] if q else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
+        self._swiglu_T_ready = False
         if re.sw:
             am, sc = self._slot(l, S_SWIGLU)
-            if q:
+            if q and self._kmajor and self.qdtype == torch.float8_e4m3fn and self.dtype == torch.bfloat16 and self.grads_use_kmajor_dw():
+                # the recomputed activation only feeds the down projection's weight-gradient GEMM, which reads it
+                # transposed: write just that copy (into the transposed-input buffer the GEMM reads next)
+                D = cfg.intermediate_size
+                K.swiglu_forward_transposed(t.inp_qT[:D * BT].view(D, BT), a.up[l], known_absmax=am, q_scale=sc)
+                self._swiglu_T_ready = True
+            elif q:
                 K.swiglu_forward(None, a.up[l], q_out=a.swiglu_q[l], known_absmax=am, q_scale=sc)
             else:
                 K.swiglu_forward(a.swiglu[l], a.up[l])
+
+    def grads_use_kmajor_dw(self) -> bool:
+        """True when the weight-gradient GEMMs of the blocks take the K-major path of ``_bwd_mm`` (no in-GEMM flag polling)."""
+        return self._kmajor and os.environ.get("LLMQ_GEMM_POLL", "0") != "1"
 
     def _backward_block(self, l: int, p, dw: Dict[str, torch.Tensor], acc: bool) -> None:
         cfg, a, t = self.cfg, self.acts, self.tmp
@@ -750,7 +764,8 @@ class LlamaModel:
         fuse_sw = self._fuse_swiglu and bool(int(self.opts.fuse_swiglu) & 2) and p.ready["down_w"] is None
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
                      a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"),
-                     swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0], dout_qT=t.d_res_qT)
+                     swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0], dout_qT=t.d_res_qT,
+                     inp_qT_ready=getattr(self, "_swiglu_T_ready", False))
         ev_down = self._dw_events[-1] if self._dw_events else None      # dW(down) reads d_res / its fp8 copy
         # ---- SwiGLU backward, in place over the saved up-projection (unless the GEMM epilogue above already did it)
         if not fuse_sw:

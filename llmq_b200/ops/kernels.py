@@ -401,6 +401,21 @@ def swiglu_forward(out: Optional[torch.Tensor], inp: torch.Tensor, *, absmax: Op
             q_scale.copy_((am / 448.0).reshape_as(q_scale))
 
 
+def swiglu_forward_transposed(q_t: torch.Tensor, inp: torch.Tensor, *, known_absmax: torch.Tensor, q_scale: Optional[torch.Tensor] = None) -> None:
+    """q_t[D, rows] (e4m3) = transpose of quantise(swiglu(inp[rows, 2D])) with an abs-max that is already known: the
+    recompute path of an fp8 model whose weight-gradient GEMM reads the activation K-major.  Same bytes as
+    ``swiglu_forward(q_out=...)`` followed by ``transpose``."""
+    rows, D2 = inp.reshape(-1, inp.shape[-1]).shape
+    D = D2 // 2
+    if inp.is_cuda and inp.dtype == torch.bfloat16 and rows % 16 == 0 and D % 16 == 0:
+        L.check(L.kernels().llmq_swiglu_forward_transposed(L.ptr(q_t), L.ptr(inp), rows, D, L.ptr(known_absmax), L.ptr(q_scale),
+                                                           L.dtype_code(inp.dtype), L.stream_ptr()), "swiglu_forward_transposed")
+        return
+    tmp = torch.empty(rows, D, dtype=q_t.dtype, device=inp.device)
+    swiglu_forward(None, inp.reshape(rows, D2), q_out=tmp, known_absmax=known_absmax, q_scale=q_scale)
+    transpose(q_t, tmp)
+
+
 def swiglu_backward(dinp: torch.Tensor, dout: torch.Tensor, inp: torch.Tensor, *, absmax: Optional[torch.Tensor] = None) -> None:
     """dinp = [d_up | d_gate]; may alias ``inp``."""
     D = inp.shape[-1] // 2

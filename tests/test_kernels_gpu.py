@@ -260,6 +260,24 @@ def test_quantize_transpose_tiles(rows, cols, src):
             assert torch.equal(out_t.view(torch.uint8), xq.view(torch.uint8).t())
 
 
+@pytest.mark.parametrize("rows,D", [(256, 128), (400, 4864), (1024, 176)])
+def test_swiglu_forward_transposed(rows, D):
+    """The recompute kernel that writes only the transposed e4m3 activation: same bytes as quantise-then-transpose."""
+    torch.manual_seed(5)
+    inp = (torch.randn(rows, 2 * D) * 1.5).to(BF).to(DEV)
+    out = torch.zeros(rows, D, dtype=BF, device=DEV)
+    am = torch.zeros(1, device=DEV)
+    K.swiglu_forward(out, inp, absmax=am)
+    q = torch.zeros(rows, D, dtype=F8, device=DEV)
+    sc = torch.zeros(1, device=DEV)
+    K.swiglu_forward(None, inp, q_out=q, known_absmax=am, q_scale=sc)
+    qt = torch.zeros(D, rows, dtype=F8, device=DEV)
+    sc2 = torch.zeros(1, device=DEV)
+    K.swiglu_forward_transposed(qt, inp, known_absmax=am, q_scale=sc2)
+    assert sc.item() == sc2.item()
+    assert torch.equal(qt.view(torch.uint8), q.view(torch.uint8).t())
+
+
 # Shapes with M >= 256 and M * N >= 2 Mi select the CTA-pair kernel (256 x 256 tiles, cta_group::2), the kernel that carries
 # the training step; the smaller shapes above all run the one-CTA kernel.
 PAIR_SHAPES = [(2048, 1536, 512), (1104, 2000, 208), (2304, 4608, 3584)]      # every extent a multiple of 16 bytes in fp8 (TMA rows)
