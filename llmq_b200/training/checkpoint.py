@@ -1,11 +1,17 @@
 """Sharded training checkpoints.
 
-Layout (same as the reference, src/training/checkpoint.cpp:24-189, src/models/llama_optimizer.cpp:55-79):
+Layout (directory structure of the reference, src/training/checkpoint.cpp:24-189, src/models/llama_optimizer.cpp:55-79):
 
     <dir>/step_00000100/weights.shard_000_of_008.safetensors     master-weight shards, fused names
                         adam.m.shard_000_of_008.safetensors      first moments (+ adam.m.scales.* for e4m3)
                         adam.v.shard_000_of_008.safetensors
                         checkpoint.json                          {version, data-loader, run, distributed}
+
+The directory layout, the shard file names and the top-level keys of ``checkpoint.json`` are the reference's; the values
+under ``run`` are not interchangeable with it: the random state is one decimal number here (a byte vector there), the
+outlier windows are flat lists (``past_losses.values / index / size`` there), and the step counter of the gradient manager
+and the stochastic-rounding state are stored in addition.  Checkpoints are therefore portable between runs of this
+framework only; the HF export (``model.safetensors``) is the interchange format.
 
 Every rank writes its own shard files (tmp + rename), then rank 0 writes ``checkpoint.json`` last, so a directory
 with that file is complete.  Restoring needs the same world size; corrupted, truncated or mismatching shards
