@@ -71,7 +71,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
     uint8_t* sK = sQ + 2 * TILE_BYTES;                    // [KV_STAGES][TILE_BYTES]
     uint8_t* sV = sK + KV_STAGES * TILE_BYTES;            // [KV_STAGES][TILE_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + KV_STAGES * TILE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -92,7 +92,9 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
     const int active = nB > 0 ? 2 : 1;
     const int qcol = h * HS, kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
-    // barriers: 0 q_full | 1-2 k_full | 3-4 k_empty | 5-6 v_full | 7-8 v_empty | 9-10 s_full[X] | 11-12 p_ready[X] | 13-14 o_done[X]
+    // barriers: 0 q_full | 1-2 k_full | 3-4 k_empty | 5-6 v_full | 7-8 v_empty | 9-10 s_full[X] | 11-12 p_ready[X] (first 64 keys)
+    //           | 13-14 o_done[X] | 15-16 p_ready2[X] (second 64 keys).  One phase per key tile on every barrier, so a waiter that
+    //           comes late can be at most one completed phase behind and the parity test stays unambiguous.
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0;
     auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
@@ -102,13 +104,14 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
     auto s_full = [&](int x) { return bar0 + 8u * (9 + x); };
     auto p_ready = [&](int x) { return bar0 + 8u * (11 + x); };
     auto o_done = [&](int x) { return bar0 + 8u * (13 + x); };
+    auto p_ready2 = [&](int x) { return bar0 + 8u * (15 + x); };
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(k_full(s), 1); mbar_init(v_full(s), 1);
             mbar_init(k_empty(s), active); mbar_init(v_empty(s), active);      // one arrival per active query tile
         }
-        for (int x = 0; x < 2; ++x) { mbar_init(s_full(x), 1); mbar_init(p_ready(x), 4); mbar_init(o_done(x), 1); }
+        for (int x = 0; x < 2; ++x) { mbar_init(s_full(x), 1); mbar_init(p_ready(x), 4); mbar_init(p_ready2(x), 4); mbar_init(o_done(x), 1); }
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -164,11 +167,11 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
                 mma_commit(k_empty(st));
                 if (!mbar_wait(v_full(st), par, abort_flag)) { ok = false; break; }
                 const uint32_t v_base = smem_u32(sV) + st * TILE_BYTES;
-                // P arrives in two halves of 64 keys (two barrier phases per tile): the first half's MMAs run while the
-                // warpgroup still exponentiates the second half
+                // P arrives in two halves of 64 keys (a barrier each): the first half's MMAs run while the warpgroup still
+                // exponentiates the second half
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    if (!mbar_wait(p_ready(x), half, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(half == 0 ? p_ready(x) : p_ready2(x), j & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
 #pragma unroll
                     for (int k = half * 4; k < half * 4 + 4; ++k)
@@ -270,7 +273,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
             l_sum += sum;
             tmem_st_wait();
             tc_fence_before_sync();
-            warp_arrive(p_ready(x));
+            warp_arrive(p_ready2(x));
         }
         // ---- the walk is over: normalise and store this tile's rows
         if (ok && n > 0) ok = mbar_wait(o_done(x), (n - 1) & 1, abort_flag);

@@ -17,6 +17,8 @@ import torch
 
 GUARD_BYTES = 4096
 PATTERN = 0xA5
+# the allocator itself must keep using the real factories while they are patched
+_torch_full, _torch_empty = torch.full, torch.empty
 
 
 class GuardedAllocator:
@@ -31,10 +33,10 @@ class GuardedAllocator:
         n = 1
         for s in shape:
             n *= int(s)
-        es = torch.empty(0, dtype=dtype).element_size()
+        es = _torch_empty(0, dtype=dtype).element_size()
         payload = n * es
         padded = (payload + 255) // 256 * 256                          # keeps the payload's natural alignment behind the guard
-        raw = torch.full((self.guard + padded + self.guard,), PATTERN, dtype=torch.uint8, device=self.device)
+        raw = _torch_full((self.guard + padded + self.guard,), PATTERN, dtype=torch.uint8, device=self.device)
         view = raw[self.guard:self.guard + payload].view(dtype).view(*shape)
         if fill is not None:
             view.fill_(fill)
