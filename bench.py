@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--fuse-swiglu", type=int, default=None)
     ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--overlap-lmhead", type=int, default=None)
+    ap.add_argument("--lmhead-transpose-dlogits", type=int, default=None)
     ap.add_argument("--kmajor-backward", type=int, default=None, help="0 = backward GEMMs read MN-major operands in place, 1 = transposed fp8 copies (default)")
     ap.add_argument("--cuda-graphs", type=int, default=-1,
                     help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs; default), 0 = plain launches")
@@ -189,6 +190,8 @@ def main():
         opts.overlap_dw = bool(args.overlap_dw)
     if args.overlap_lmhead is not None:
         opts.overlap_lmhead = bool(args.overlap_lmhead)
+    if args.lmhead_transpose_dlogits is not None:
+        opts.lmhead_transpose_dlogits = bool(args.lmhead_transpose_dlogits)
     if args.kmajor_backward is not None:
         opts.kmajor_backward = bool(args.kmajor_backward)
     zl = args.zero_level or (1 if args.gpus == 1 else 3)

@@ -171,6 +171,38 @@ tile_transpose_kernel(Q* __restrict__ out_rows, Q* __restrict__ out_t, float* __
     tile_store_transposed<Q>(tile, out_t, r0, c0, rows, cols);
 }
 
+// out[c][r] = in[r][c] for 2-byte elements, 64 x 64 tiles, 16-byte global accesses on both sides (rows and cols multiples
+// of 8).  The row pitch of 66 halves (33 words) spreads a column walk over the banks.
+__global__ void __launch_bounds__(256)
+transpose16_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ in, int rows, int cols) {
+    __shared__ __align__(16) uint16_t tile[64 * 66];
+    const int t = threadIdx.x;
+    const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+    const int sub = t >> 3, ch = t & 7;
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const int lr = p * 32 + sub, r = r0 + lr, c = c0 + ch * 8;
+        const uint4 v = (r < rows && c < cols) ? __ldcs(reinterpret_cast<const uint4*>(in + static_cast<long long>(r) * cols + c)) : make_uint4(0, 0, 0, 0);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[lr * 66 + ch * 8]);
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const int lc = p * 32 + sub;                            // column of the input tile = row of the output
+        const int c = c0 + lc, r = r0 + ch * 8;
+        uint16_t h[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) h[k] = tile[(ch * 8 + k) * 66 + lc];
+        if (c < cols && r < rows) {
+            uint4 o;
+            o.x = h[0] | (static_cast<uint32_t>(h[1]) << 16); o.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
+            o.z = h[4] | (static_cast<uint32_t>(h[5]) << 16); o.w = h[6] | (static_cast<uint32_t>(h[7]) << 16);
+            *reinterpret_cast<uint4*>(out + static_cast<long long>(c) * rows + r) = o;
+        }
+    }
+}
+
 template <typename S, typename D>
 __global__ void __launch_bounds__(512) convert_kernel(D* __restrict__ out, const S* __restrict__ in, long long n) {
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -236,6 +268,11 @@ extern "C" int llmq_quantize(void* out, float* scale_out, const void* x, const f
 extern "C" int llmq_transpose(void* out, float* scale_out, const void* in, const float* absmax, int rows, int cols,
                               int in_dtype, int out_dtype, cudaStream_t s) {
     if (rows <= 0 || cols <= 0) return 0;
+    if (in_dtype == 0 && out_dtype == 0 && absmax == nullptr && rows % 8 == 0 && cols % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
+        transpose16_kernel<<<dim3(ceil_div_i(cols, 64), ceil_div_i(rows, 64)), 256, 0, s>>>(static_cast<uint16_t*>(out), static_cast<const uint16_t*>(in), rows, cols);
+        return LLMQ_LAUNCH_CHECK();
+    }
     dim3 grid(ceil_div_i(cols, 32), ceil_div_i(rows, 32)), block(32, 8);
 #define T_CASE(T, TC, Q, QC, QUANT)                                                                                \
     if (in_dtype == TC && out_dtype == QC && (absmax != nullptr) == QUANT) {                                       \

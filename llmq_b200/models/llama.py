@@ -244,8 +244,11 @@ class LlamaModel:
             t.logits2 = t.lnf_T = None
             if on_gpu and o.overlap_lmhead and chunks > 1:
                 A("logits2", BT // chunks, V)    # the LM-head gradients of a chunk run beside the next chunk's logits + classifier
+            t.dlogits_T = None
             if on_gpu:
                 A("lnf_T", C, BT // chunks)      # lnf chunk transposed, B operand of the LM-head dW GEMM
+                if o.lmhead_transposed_operands and o.lmhead_transpose_dlogits and V % 8 == 0 and (BT // chunks) % 8 == 0:
+                    A("dlogits_T", V, BT // chunks)      # d(logits) chunk transposed, A operand of the LM-head dW GEMM
             end_phase(base)
             first = len(names)
             # block-backward phase
@@ -616,8 +619,12 @@ class LlamaModel:
             def grads_of_chunk(logits=logits, sl=sl, c=c):
                 if use_t:
                     K.transpose(t.lnf_T, self.lnf[sl])
-                    K.gemm(dW, logits, t.lnf_T, a_mn=True, accumulate=accumulate_dw or c > 0)
                     K.gemm(t.d_ln[sl], logits, WT)
+                    if t.dlogits_T is not None:
+                        K.transpose(t.dlogits_T, logits)            # both operands of dW K-major
+                        K.gemm(dW, t.dlogits_T, t.lnf_T, accumulate=accumulate_dw or c > 0)
+                    else:
+                        K.gemm(dW, logits, t.lnf_T, a_mn=True, accumulate=accumulate_dw or c > 0)
                 else:
                     K.gemm(dW, logits, self.lnf[sl], a_mn=True, b_mn=True, accumulate=accumulate_dw or c > 0)
                     K.gemm(t.d_ln[sl], logits, W, b_mn=True)

@@ -260,6 +260,16 @@ def test_quantize_transpose_tiles(rows, cols, src):
             assert torch.equal(out_t.view(torch.uint8), xq.view(torch.uint8).t())
 
 
+@pytest.mark.parametrize("rows,cols", [(64, 8), (256, 136), (1000, 3584), (72, 4104)])
+def test_transpose_bf16_tiles(rows, cols):
+    """The 64 x 64 tile transpose of 2-byte elements (full and ragged tiles) is exact."""
+    torch.manual_seed(rows)
+    x = torch.randn(rows, cols).to(BF).to(DEV)
+    out = torch.zeros(cols, rows, dtype=BF, device=DEV)
+    K.transpose(out, x)
+    assert torch.equal(out, x.t())
+
+
 @pytest.mark.parametrize("rows,D", [(256, 128), (400, 4864), (1024, 176)])
 def test_swiglu_forward_transposed(rows, D):
     """The recompute kernel that writes only the transposed e4m3 activation: same bytes as quantise-then-transpose."""
