@@ -60,6 +60,12 @@ class SymmetricHeap:
         if seg is None:
             seg = _Segment(max(self.segment_bytes, nbytes), self.device, self.group)
             seg.buf.zero_()
+            # The clearing memset runs on this rank's stream; a faster peer could already store into the new segment (its
+            # first push after the allocation) and this rank's memset would then wipe that data.  So: finish the memset,
+            # then meet all ranks on the host before anybody uses the segment.
+            torch.cuda.synchronize(self.device)
+            import torch.distributed as dist
+            dist.barrier(group=self.group, device_ids=[self.device.index])
             self.segments.append(seg)
         off = seg.used
         seg.used += nbytes

@@ -27,7 +27,7 @@ def _worker(rank, world, port, multimem, q):
         from llmq_b200.parallel.fused import FusedCollectives
         dev = torch.device("cuda", rank)
         torch.cuda.set_device(dev)
-        comm = TorchDistComm(dev, timeout_s=60)
+        comm = TorchDistComm(dev, timeout_s=30)
         fc = FusedCollectives(comm, dev, wait_limit_s=5.0)
         g = torch.Generator(device="cpu").manual_seed(100 + rank)
         rows, cols = 512, 384
@@ -51,7 +51,7 @@ def _worker(rank, world, port, multimem, q):
             dist.all_gather_into_tensor(ref.view(-1), q_local.view(torch.uint8).view(-1))
             torch.cuda.synchronize()
             assert torch.equal(full.view(torch.uint8), ref), f"all-gather mismatch it={it}"
-            assert abs(scale.item() - am.item() / 448.0) < 1e-9
+            assert abs(scale.item() - am.item() / 448.0) <= 2e-7 * scale.item()            # fp32 division on the device
             g2 = fc.signal(2)                                   # everybody finished checking before the next overwrite
             fc.wait(2, g2)
             shard.mul_(0.5)
@@ -142,11 +142,11 @@ def test_fused_collectives_match_nccl(multimem):
     res = []
     try:
         for _ in range(world):
-            res.append(q.get(timeout=240))
+            res.append(q.get(timeout=100))
     except Exception:                                   # a rank that never answered: report what the others said
         pass
     for p in procs:
-        p.join(timeout=60)
+        p.join(timeout=20)
         if p.is_alive():
             p.kill()
     assert len(res) == world and all(r[1] == "ok" for r in res), res
