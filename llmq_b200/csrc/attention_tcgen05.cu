@@ -105,26 +105,33 @@ struct AttnParams {
 };
 
 // ------------------------------------------------------------------------------------------------
-// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per row
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; HS / 8 lanes per row (one 16-byte load of each tensor per lane), so a
+// warp covers 2 (HS = 128) or 4 (HS = 64) rows and every lane has work
 template <int HS>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(float* __restrict__ delta, const bf16* __restrict__ o, const bf16* __restrict__ d_o, int B, int T, int Hq) {
-    const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
+    constexpr int LANES = HS / 8;                       // lanes per row
+    static_assert(LANES == 8 || LANES == 16, "head sizes 64 and 128");
+    const long long gid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long w = gid / LANES;                    // row index over (b, t, h)
+    const int sub = static_cast<int>(gid % LANES);
     const long long total = static_cast<long long>(B) * T * Hq;
-    if (w >= total) return;
-    const int h = static_cast<int>(w % Hq);
-    const long long bt = w / Hq;
-    const int t = static_cast<int>(bt % T);
-    const long long b = bt / T;
+    const bool active = w < total;
     float s = 0.f;
-    for (int c = lane * 8; c < HS; c += 256) {
-        Vec16<bf16> a = Vec16<bf16>::load(o + w * HS + c), g = Vec16<bf16>::load(d_o + w * HS + c);
+    if (active) {
+        Vec16<bf16> a = Vec16<bf16>::load(o + w * HS + sub * 8), g = Vec16<bf16>::load(d_o + w * HS + sub * 8);
 #pragma unroll
         for (int k = 0; k < 8; ++k) s += __bfloat162float(a.v[k]) * __bfloat162float(g.v[k]);
     }
-    s = warp_reduce_sum(s);
-    if (lane == 0) delta[(b * Hq + h) * T + t] = s;
+#pragma unroll
+    for (int off = LANES / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (active && sub == 0) {
+        const int h = static_cast<int>(w % Hq);
+        const long long bt = w / Hq;
+        const int t = static_cast<int>(bt % T);
+        const long long b = bt / T;
+        delta[(b * Hq + h) * T + t] = s;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -960,7 +967,7 @@ int bwd_impl(void* dqkv, float* delta, const void* d_out, const void* out, const
     const int H = Hq + 2 * Hkv;
     {
         long long rows = static_cast<long long>(B) * T * Hq;
-        long long blocks = (rows * 32 + 255) / 256;
+        long long blocks = (rows * (HS / 8) + 255) / 256;
         attn_delta_kernel<HS><<<static_cast<unsigned int>(blocks), 256, 0, s>>>(delta, static_cast<const bf16*>(out), static_cast<const bf16*>(d_out), B, T, Hq);
         int rc = LLMQ_LAUNCH_CHECK();
         if (rc) return rc;
