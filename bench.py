@@ -160,6 +160,7 @@ def main():
     ap.add_argument("--overlap-dw", type=int, default=None)
     ap.add_argument("--overlap-lmhead", type=int, default=None)
     ap.add_argument("--lmhead-transpose-dlogits", type=int, default=None)
+    ap.add_argument("--swiglu-two-pass", type=int, default=None, help="0 = SwiGLU backward writes bf16 then quantises, 1 = abs-max pass + quantising pass (default)")
     ap.add_argument("--kmajor-backward", type=int, default=None, help="0 = backward GEMMs read MN-major operands in place, 1 = transposed fp8 copies (default)")
     ap.add_argument("--cuda-graphs", type=int, default=-1,
                     help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs; default), 0 = plain launches")
@@ -194,6 +195,8 @@ def main():
         opts.lmhead_transpose_dlogits = bool(args.lmhead_transpose_dlogits)
     if args.kmajor_backward is not None:
         opts.kmajor_backward = bool(args.kmajor_backward)
+    if args.swiglu_two_pass is not None:
+        opts.swiglu_backward_two_pass = bool(args.swiglu_two_pass)
     zl = args.zero_level or (1 if args.gpus == 1 else 3)
     opts.set_zero_level(zl)
     opts.offload_opt_m = opts.offload_opt_v = args.offload_opt

@@ -139,6 +139,132 @@ swiglu_bwd_kernel(T* dinp, const T* __restrict__ dout, const T* inp, long long r
     block_absmax_commit(absmax_out, tmax, scratch);
 }
 
+// SwiGLU backward of an fp8 model whose GEMMs read K-major operands, in two passes that never write the 16-bit gradient:
+// the only consumers of [d_up | d_gate] are the two GEMMs of the up projection, which read its e4m3 copy and the
+// transpose of that copy.  The first pass finds the abs-max of the gradient (rounded to T, as swiglu_bwd_kernel would
+// store it) and, while the up projection is in registers anyway, can emit the transposed e4m3 SwiGLU output that the
+// weight-gradient GEMM of the down projection needs (the recompute of swiglu_fwd_transposed_kernel); the second pass
+// recomputes the gradient and writes q_rows[rows][2D] and q_t[2D][rows].  Both passes work on 128 x 128 tiles of the D
+// columns: one CTA reads the matching up, gate and dout tiles and owns both halves of the output.
+template <typename T>
+__device__ __forceinline__ void swiglu_bwd_values(const uint4& vu, const uint4& vg, const uint4& vd, float (&du)[8], float (&dg)[8]) {
+    const T* u = reinterpret_cast<const T*>(&vu);
+    const T* g = reinterpret_cast<const T*>(&vg);
+    const T* d = reinterpret_cast<const T*>(&vd);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float uf = to_float(u[k]), gf = to_float(g[k]), df = to_float(d[k]);
+        const float s = fast_sigmoid(gf);
+        du[k] = to_float(from_float<T>(df * gf * s));
+        dg[k] = to_float(from_float<T>(df * uf * s * (1.f + gf * (1.f - s))));
+    }
+}
+
+template <typename T, bool WriteAct>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_stats_kernel(float* __restrict__ absmax_out, e4m3* __restrict__ act_t, const T* __restrict__ dout, const T* __restrict__ inp,
+                        int rows, int D, const float* __restrict__ act_absmax, float* __restrict__ act_scale_out) {
+    static_assert(sizeof(T) == 2, "16-bit activations");
+    __shared__ __align__(16) uint32_t tile[WriteAct ? 128 * 32 : 4];
+    __shared__ float scratch[32];
+    const int t = threadIdx.x;
+    const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
+    float qmul = 0.f;
+    if constexpr (WriteAct) {
+        const float am = fmaxf(*act_absmax, 1e-10f);
+        qmul = 448.f / am;
+        if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0 && act_scale_out) *act_scale_out = am / 448.f;
+    }
+    const int cc = t & 15, rr = t >> 4;                    // 16 threads per row (8 elements each), 16 rows per pass
+    float tmax = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint4 vu[4], vg[4], vd[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int r = r0 + (h * 4 + p) * 16 + rr, c = c0 + cc * 8;
+            const bool ok = r < rows && c < D;
+            const T* up = inp + static_cast<long long>(r) * 2 * D + c;
+            vu[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(up)) : make_uint4(0, 0, 0, 0);
+            vg[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(up + D)) : make_uint4(0, 0, 0, 0);
+            vd[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(dout + static_cast<long long>(r) * D + c)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            float du[8], dg[8];
+            swiglu_bwd_values<T>(vu[p], vg[p], vd[p], du, dg);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) tmax = fmaxf(tmax, fmaxf(fabsf(du[k]), fabsf(dg[k])));
+            if constexpr (WriteAct) {
+                const int lr = (h * 4 + p) * 16 + rr;
+                const T* u = reinterpret_cast<const T*>(&vu[p]);
+                const T* g = reinterpret_cast<const T*>(&vg[p]);
+                float f[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float uf = to_float(u[k]), gf = to_float(g[k]);
+                    f[k] = to_float(from_float<T>(uf * gf * fast_sigmoid(gf))) * qmul;
+                }
+                *reinterpret_cast<uint2*>(&tile[tile_word_index(lr, cc * 2)]) = pack_e4m3x8(f);
+            }
+        }
+    }
+    if constexpr (WriteAct) {
+        __syncthreads();
+        tile_store_transposed<e4m3>(tile, act_t, r0, c0, rows, D);
+    }
+    block_absmax_commit(absmax_out, tmax, scratch);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_quant_kernel(e4m3* __restrict__ q_rows, e4m3* __restrict__ q_t, float* __restrict__ scale_out, const T* __restrict__ dout,
+                        const T* __restrict__ inp, int rows, int D, const float* __restrict__ absmax) {
+    static_assert(sizeof(T) == 2, "16-bit activations");
+    __shared__ __align__(16) uint32_t tile_u[128 * 32];
+    __shared__ __align__(16) uint32_t tile_g[128 * 32];
+    const int t = threadIdx.x;
+    const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 128;
+    const float am = fmaxf(*absmax, 1e-10f);
+    const float mul = 448.f / am;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && t == 0 && scale_out) *scale_out = am / 448.f;
+    const int cc = t & 15, rr = t >> 4;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint4 vu[4], vg[4], vd[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int r = r0 + (h * 4 + p) * 16 + rr, c = c0 + cc * 8;
+            const bool ok = r < rows && c < D;
+            const T* up = inp + static_cast<long long>(r) * 2 * D + c;
+            vu[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(up)) : make_uint4(0, 0, 0, 0);
+            vg[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(up + D)) : make_uint4(0, 0, 0, 0);
+            vd[p] = ok ? __ldcs(reinterpret_cast<const uint4*>(dout + static_cast<long long>(r) * D + c)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int lr = (h * 4 + p) * 16 + rr, r = r0 + lr, c = c0 + cc * 8;
+            float du[8], dg[8];
+            swiglu_bwd_values<T>(vu[p], vg[p], vd[p], du, dg);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { du[k] *= mul; dg[k] *= mul; }
+            const uint2 wu = pack_e4m3x8(du), wg = pack_e4m3x8(dg);
+            if (r < rows && c < D) {
+                e4m3* o = q_rows + static_cast<long long>(r) * 2 * D + c;
+                *reinterpret_cast<uint2*>(o) = wu;
+                *reinterpret_cast<uint2*>(o + D) = wg;
+            }
+            *reinterpret_cast<uint2*>(&tile_u[tile_word_index(lr, cc * 2)]) = wu;
+            *reinterpret_cast<uint2*>(&tile_g[tile_word_index(lr, cc * 2)]) = wg;
+        }
+    }
+    __syncthreads();
+    // q_t is [2D][rows]: the d_up tile lands at rows c0.. of q_t, the d_gate tile at rows D + c0..; the column bound of each
+    // call is the end of its half
+    tile_store_transposed<e4m3>(tile_u, q_t, r0, c0, rows, D);
+    tile_store_transposed<e4m3>(tile_g, q_t, r0, D + c0, rows, 2 * D);
+}
+
 // ------------------------------------------------------------------------------------------------
 // RoPE on the packed (B, T, Hq + 2*Hkv, HS) tensor; query and key heads are rotated with the half-split
 // pairing (d, d + HS/2), value heads are copied (or left alone when in place).  freqs is (T, HS/2, 2)
@@ -284,5 +410,35 @@ extern "C" int llmq_swiglu_forward_transposed(void* q_t, const void* inp, int ro
     if (dtype != 0) return -10;
     dim3 grid(ceil_div_i(D, 128), ceil_div_i(rows, 128));
     swiglu_fwd_transposed_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<e4m3*>(q_t), static_cast<const bf16*>(inp), rows, D, known_absmax, q_scale_out);
+    return LLMQ_LAUNCH_CHECK();
+}
+
+// Pass 1 of the fp8 SwiGLU backward: *absmax_out = max(*absmax_out, abs-max of [d_up | d_gate] rounded to the activation
+// type); with act_t also act_t[D][rows] = transposed e4m3 SwiGLU output under the known abs-max *act_absmax.
+// dout is [rows][D], inp [rows][2D] (bf16); rows and D multiples of 16.
+extern "C" int llmq_swiglu_backward_stats(float* absmax_out, void* act_t, const void* dout, const void* inp, int rows, int D,
+                                          const float* act_absmax, float* act_scale_out, int dtype, cudaStream_t s) {
+    if (rows <= 0 || D <= 0) return 0;
+    if (rows % 16 || D % 16 || !absmax_out || (act_t && !act_absmax)) return -11;
+    if (dtype != 0) return -10;
+    dim3 grid(ceil_div_i(D, 128), ceil_div_i(rows, 128));
+    if (act_t)
+        swiglu_bwd_stats_kernel<bf16, true><<<grid, 256, 0, s>>>(absmax_out, static_cast<e4m3*>(act_t), static_cast<const bf16*>(dout),
+                                                                 static_cast<const bf16*>(inp), rows, D, act_absmax, act_scale_out);
+    else
+        swiglu_bwd_stats_kernel<bf16, false><<<grid, 256, 0, s>>>(absmax_out, nullptr, static_cast<const bf16*>(dout),
+                                                                  static_cast<const bf16*>(inp), rows, D, nullptr, nullptr);
+    return LLMQ_LAUNCH_CHECK();
+}
+
+// Pass 2: q_rows[rows][2D] and q_t[2D][rows] = e4m3([d_up | d_gate] * 448 / *absmax), *scale_out = *absmax / 448.
+extern "C" int llmq_swiglu_backward_quant(void* q_rows, void* q_t, float* scale_out, const void* dout, const void* inp, int rows, int D,
+                                          const float* absmax, int dtype, cudaStream_t s) {
+    if (rows <= 0 || D <= 0) return 0;
+    if (rows % 16 || D % 16 || !absmax || !q_rows || !q_t) return -11;
+    if (dtype != 0) return -10;
+    dim3 grid(ceil_div_i(D, 128), ceil_div_i(rows, 128));
+    swiglu_bwd_quant_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<e4m3*>(q_rows), static_cast<e4m3*>(q_t), scale_out,
+                                                       static_cast<const bf16*>(dout), static_cast<const bf16*>(inp), rows, D, absmax);
     return LLMQ_LAUNCH_CHECK();
 }

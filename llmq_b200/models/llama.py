@@ -374,12 +374,14 @@ class LlamaModel:
         K.gemm(out, act_q, W, bias=bias, scale_a=sc, scale_b=w_scale, ready=ready)
 
     def _bwd_mm(self, dinp, dW, dbias, dout, dout_q, slot, inp, inp_q, inp_scale, W, w_scale, accumulate, ready=None, dw_rs=None,
-                swiglu_inout=None, swiglu_absmax=None, dout_qT=None, inp_qT_ready=False):
+                swiglu_inout=None, swiglu_absmax=None, dout_qT=None, inp_qT_ready=False, dout_ready=False, before_dw=None):
         """dinp = dout @ W;  dW (+)= dout^T @ inp;  dbias += colsum(dout).  Operands are read in place:
         W is the MN-major B operand of the first product, dout and inp the MN-major operands of the second.
         ``dw_rs`` (from ``GradientManager.fused_dw``) runs the weight-gradient GEMM with its reduce-scatter inside.
         ``swiglu_inout`` ([up | gate] -> [d_up | d_gate], in place): the input-gradient GEMM applies the SwiGLU backward
-        in its epilogue instead of writing ``dinp``."""
+        in its epilogue instead of writing ``dinp``.  ``dout_ready``: ``dout_q`` / ``dout_qT`` and the scale already hold the
+        quantised gradient (``dout`` itself is not read).  ``before_dw`` runs on the main stream between the input-gradient
+        GEMM and the launch of the weight-gradient GEMM (K-major fp8 path only)."""
         if self.mx:
             # dout feeds two GEMMs with different contraction axes: its row form and its column form come from one pass
             t = self.tmp
@@ -421,7 +423,10 @@ class LlamaModel:
         am, sc = slot
         t = self.tmp
         kmajor = self._kmajor and dout_qT is not None and ready is None
-        if kmajor:
+        assert kmajor or (not dout_ready and before_dw is None)
+        if dout_ready:
+            pass
+        elif kmajor:
             K.quantize_transpose(dout_q, dout_qT, sc, dout, am)
         else:
             K.quantize(dout_q, sc, dout, am)
@@ -435,6 +440,8 @@ class LlamaModel:
             else:
                 K.gemm(dinp, dout_q, W, b_mn=True, scale_a=sc, scale_b=w_scale, ready=ready)
         if kmajor:
+            if before_dw is not None:
+                before_dw()
             i2 = inp_q.reshape(-1, inp_q.shape[-1])
             iT = t.inp_qT[:i2.numel()].view(i2.shape[1], i2.shape[0])
 
@@ -745,7 +752,9 @@ class LlamaModel:
         self._swiglu_T_ready = False
         if re.sw:
             am, sc = self._slot(l, S_SWIGLU)
-            if q and self._kmajor and self.qdtype == torch.float8_e4m3fn and self.dtype == torch.bfloat16 and self.grads_use_kmajor_dw():
+            if self._swiglu_two_pass(p):
+                pass        # the first pass of the SwiGLU backward writes the transposed activation (see _backward_block)
+            elif q and self._kmajor and self.qdtype == torch.float8_e4m3fn and self.dtype == torch.bfloat16 and self.grads_use_kmajor_dw():
                 # the recomputed activation only feeds the down projection's weight-gradient GEMM, which reads it
                 # transposed: write just that copy (into the transposed-input buffer the GEMM reads next)
                 D = cfg.intermediate_size
@@ -760,6 +769,16 @@ class LlamaModel:
         """True when the weight-gradient GEMMs of the blocks take the K-major path of ``_bwd_mm`` (no in-GEMM flag polling)."""
         return self._kmajor and os.environ.get("LLMQ_GEMM_POLL", "0") != "1"
 
+    def _swiglu_two_pass(self, p) -> bool:
+        """True when the SwiGLU backward runs as abs-max pass + quantising pass (``K.swiglu_backward_stats`` /
+        ``K.swiglu_backward_quant``): e4m3 GEMMs on K-major operands are the only readers of [d_up | d_gate], so its bf16
+        form is never written, and the first pass doubles as the SwiGLU recompute for the down projection's dW GEMM."""
+        e4 = torch.float8_e4m3fn
+        return bool(self.quant and self._kmajor and self.opts.swiglu_backward_two_pass and self.qdtype == e4 and self.gdtype == e4
+                    and self.dtype == torch.bfloat16 and self.grads_use_kmajor_dw()
+                    and p.ready["down_w"] is None and p.ready["up_w"] is None
+                    and not (self._fuse_swiglu and int(self.opts.fuse_swiglu) & 2))
+
     def _backward_block(self, l: int, p, dw: Dict[str, torch.Tensor], acc: bool) -> None:
         cfg, a, t = self.cfg, self.acts, self.tmp
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
@@ -769,18 +788,33 @@ class LlamaModel:
         rs = (lambda name: fused_dw(l, name)) if (fused_dw is not None and not self.mx) else (lambda name: None)
         # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
         fuse_sw = self._fuse_swiglu and bool(int(self.opts.fuse_swiglu) & 2) and p.ready["down_w"] is None
+        two_pass = self._swiglu_two_pass(p)
+        sw_T_ready = getattr(self, "_swiglu_T_ready", False)
+        before_dw = None
+        if two_pass:
+            D = cfg.intermediate_size
+            # the transposed SwiGLU output for dW(down) comes out of the first pass when the recompute left it to us
+            need_act = self.re.sw and not sw_T_ready
+            am_sw, sc_sw = self._slot(l, S_SWIGLU)
+
+            def before_dw():
+                K.swiglu_backward_stats(self._slot(l, S_DMLPUP)[0], t.d_sw, a.up[l], act_t=t.inp_qT[:D * BT].view(D, BT) if need_act else None,
+                                        act_absmax=am_sw if need_act else None, act_scale=sc_sw if need_act else None)
+            sw_T_ready = sw_T_ready or need_act
         self._bwd_mm(t.d_sw, dw["down_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESFFN),
                      a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"),
                      swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0], dout_qT=t.d_res_qT,
-                     inp_qT_ready=getattr(self, "_swiglu_T_ready", False))
+                     inp_qT_ready=sw_T_ready, before_dw=before_dw)
         ev_down = self._dw_events[-1] if self._dw_events else None      # dW(down) reads d_res / its fp8 copy
         # ---- SwiGLU backward, in place over the saved up-projection (unless the GEMM epilogue above already did it)
-        if not fuse_sw:
+        if two_pass:
+            K.swiglu_backward_quant(t.d_up_q, t.d_up_qT, self._slot(l, S_DMLPUP)[1], t.d_sw, a.up[l], self._slot(l, S_DMLPUP)[0])
+        elif not fuse_sw:
             K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
         # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
                      a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"),
-                     dout_qT=t.d_up_qT)
+                     dout_qT=t.d_up_qT, dout_ready=two_pass)
         # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
         self._wait_dw(ev_down)                                          # the next two kernels overwrite d_res and its fp8 copy
         K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],

@@ -437,6 +437,39 @@ def swiglu_backward(dinp: torch.Tensor, dout: torch.Tensor, inp: torch.Tensor, *
         absmax.copy_(torch.maximum(absmax, r.float().abs().max().reshape_as(absmax)))
 
 
+def swiglu_backward_stats(absmax: torch.Tensor, dout: torch.Tensor, inp: torch.Tensor, *, act_t: Optional[torch.Tensor] = None,
+                          act_absmax: Optional[torch.Tensor] = None, act_scale: Optional[torch.Tensor] = None) -> None:
+    """First pass of the SwiGLU backward of an fp8 model that never stores the 16-bit gradient: ``absmax`` is raised to the
+    abs-max of [d_up | d_gate] (rounded to the activation type, as ``swiglu_backward`` would store it).  With ``act_t`` the
+    same pass also writes ``act_t[D, rows]``, the transposed e4m3 SwiGLU output under the known ``act_absmax`` (what
+    ``swiglu_forward_transposed`` computes), because it holds the up projection in registers anyway."""
+    D = inp.shape[-1] // 2
+    rows = inp.numel() // (2 * D)
+    if inp.is_cuda and inp.dtype == torch.bfloat16 and rows % 16 == 0 and D % 16 == 0:
+        L.check(L.kernels().llmq_swiglu_backward_stats(L.ptr(absmax), L.ptr(act_t), L.ptr(dout), L.ptr(inp), rows, D, L.ptr(act_absmax),
+                                                       L.ptr(act_scale), L.dtype_code(inp.dtype), L.stream_ptr()), "swiglu_backward_stats")
+        return
+    tmp = torch.empty(rows, 2 * D, dtype=inp.dtype, device=inp.device)
+    swiglu_backward(tmp, dout, inp, absmax=absmax)
+    if act_t is not None:
+        swiglu_forward_transposed(act_t, inp, known_absmax=act_absmax, q_scale=act_scale)
+
+
+def swiglu_backward_quant(q_rows: torch.Tensor, q_t: torch.Tensor, scale_out: Optional[torch.Tensor], dout: torch.Tensor, inp: torch.Tensor,
+                          absmax: torch.Tensor) -> None:
+    """Second pass: ``q_rows[rows, 2D]`` = e4m3 copy of [d_up | d_gate] under ``absmax`` and ``q_t[2D, rows]`` its transpose; same
+    bytes as ``swiglu_backward`` followed by ``quantize_transpose``."""
+    D = inp.shape[-1] // 2
+    rows = inp.numel() // (2 * D)
+    if inp.is_cuda and inp.dtype == torch.bfloat16 and rows % 16 == 0 and D % 16 == 0 and q_rows.dtype == torch.float8_e4m3fn:
+        L.check(L.kernels().llmq_swiglu_backward_quant(L.ptr(q_rows), L.ptr(q_t), L.ptr(scale_out), L.ptr(dout), L.ptr(inp), rows, D,
+                                                       L.ptr(absmax), L.dtype_code(inp.dtype), L.stream_ptr()), "swiglu_backward_quant")
+        return
+    tmp = torch.empty(rows, 2 * D, dtype=inp.dtype, device=inp.device)
+    swiglu_backward(tmp, dout, inp)
+    quantize_transpose(q_rows, q_t, scale_out, tmp, absmax)
+
+
 # =====================================================================================================
 # RoPE
 def rope_table(T: int, HS: int, theta: float, device) -> torch.Tensor:

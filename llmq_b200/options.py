@@ -39,6 +39,7 @@ class LLamaOptions:
     # per 32 elements of the contraction axis (tcgen05 kind::mxf8f6f4.block_scale); activations and weights stay bf16.
     # Also selected by matmul_type = "mxe4m3" / "mxfp8".
     block_scaled: bool = False
+    swiglu_backward_two_pass: bool = True     # fp8 K-major backward: SwiGLU gradient as abs-max pass + quantise/transpose pass, its bf16 form never stored
     kmajor_backward: bool = True              # fp8 backward GEMMs read transposed fp8 copies (all operands K-major) instead of MN-major tiles
     lmhead_transposed_operands: bool = True   # LM-head backward reads W^T / lnf^T copies (K-major GEMM operands)
     # ... and a transposed copy of each d(logits) chunk for the dW GEMM: no measurable gain (469.3 / 472.4 ms with, 472.1 / 470.7 ms

@@ -288,6 +288,52 @@ def test_swiglu_forward_transposed(rows, D):
     assert torch.equal(qt.view(torch.uint8), q.view(torch.uint8).t())
 
 
+@pytest.mark.parametrize("rows,D", [(256, 384), (272, 208), (1040, 1168)])
+@pytest.mark.parametrize("with_act", [False, True])
+def test_swiglu_backward_two_pass(rows, D, with_act):
+    """Abs-max pass + quantising pass against swiglu_backward followed by quantize_transpose: same abs-max, same scale, same
+    bytes in both copies; the first pass's optional transposed activation equals swiglu_forward_transposed's."""
+    torch.manual_seed(6)
+    inp = (torch.randn(rows, 2 * D) * 1.5).to(BF).to(DEV)
+    dout = (torch.randn(rows, D) * 0.7).to(BF).to(DEV)
+    # the separate kernels
+    d_ref = torch.zeros(rows, 2 * D, dtype=BF, device=DEV)
+    am_ref = torch.zeros(1, device=DEV)
+    K.swiglu_backward(d_ref, dout, inp, absmax=am_ref)
+    q_ref = torch.zeros(rows, 2 * D, dtype=F8, device=DEV)
+    qt_ref = torch.zeros(2 * D, rows, dtype=F8, device=DEV)
+    sc_ref = torch.zeros(1, device=DEV)
+    K.quantize_transpose(q_ref, qt_ref, sc_ref, d_ref, am_ref)
+    # fp32 oracle of the gradient itself
+    x = inp.float()
+    up, gate = x[:, :D], x[:, D:]
+    s_ = torch.sigmoid(gate)
+    want = torch.cat([dout.float() * gate * s_, dout.float() * up * s_ * (1 + gate * (1 - s_))], -1)
+    assert (d_ref.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    # the two passes
+    am = torch.zeros(1, device=DEV)
+    act_am = torch.zeros(1, device=DEV)
+    act_t = act_t_ref = None
+    if with_act:
+        K.swiglu_forward(torch.zeros(rows, D, dtype=BF, device=DEV), inp, absmax=act_am)
+        act_t_ref = torch.zeros(D, rows, dtype=F8, device=DEV)
+        K.swiglu_forward_transposed(act_t_ref, inp, known_absmax=act_am)
+        act_t = torch.zeros(D, rows, dtype=F8, device=DEV)
+    act_sc = torch.zeros(1, device=DEV)
+    K.swiglu_backward_stats(am, dout, inp, act_t=act_t, act_absmax=act_am if with_act else None, act_scale=act_sc if with_act else None)
+    assert am.item() == am_ref.item()
+    q = torch.zeros(rows, 2 * D, dtype=F8, device=DEV)
+    qt = torch.zeros(2 * D, rows, dtype=F8, device=DEV)
+    sc = torch.zeros(1, device=DEV)
+    K.swiglu_backward_quant(q, qt, sc, dout, inp, am)
+    assert sc.item() == sc_ref.item()
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    assert torch.equal(qt.view(torch.uint8), qt_ref.view(torch.uint8))
+    if with_act:
+        assert act_sc.item() == pytest.approx(act_am.item() / 448.0, rel=1e-6)
+        assert torch.equal(act_t.view(torch.uint8), act_t_ref.view(torch.uint8))
+
+
 # Shapes with M >= 256 and M * N >= 2 Mi select the CTA-pair kernel (256 x 256 tiles, cta_group::2), the kernel that carries
 # the training step; the smaller shapes above all run the one-CTA kernel.
 PAIR_SHAPES = [(2048, 1536, 512), (1104, 2000, 208), (2304, 4608, 3584)]      # every extent a multiple of 16 bytes in fp8 (TMA rows)

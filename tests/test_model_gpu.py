@@ -172,6 +172,18 @@ def test_swiglu_in_gemm_epilogues_is_bit_identical(mm):
         assert torch.equal(base[3][n], fused[3][n]), n
 
 
+@pytest.mark.parametrize("kw", [dict(), dict(recompute_swiglu=True), dict(recompute_block=True), dict(overlap_dw=True)], ids=lambda d: "+".join(d) or "plain")
+def test_swiglu_backward_two_pass_is_bit_identical(kw):
+    """The SwiGLU gradient as abs-max pass + quantising pass (its bf16 form never stored, the first pass doubling as the
+    SwiGLU recompute) gives the bytes of the separate kernels: same losses, norms and gradients."""
+    base = run(LLamaOptions(matmul_type="e4m3", swiglu_backward_two_pass=False, **kw), steps=3, ga=2)
+    two = run(LLamaOptions(matmul_type="e4m3", swiglu_backward_two_pass=True, **kw), steps=3, ga=2)
+    assert two[1]._kmajor and two[1].opts.swiglu_backward_two_pass
+    assert two[2] == base[2], (two[2], base[2])
+    for n in base[3]:
+        assert torch.equal(base[3][n], two[3][n]), n
+
+
 def test_lmhead_transposed_operands_match():
     base = run(LLamaOptions(matmul_type="e4m3", lmhead_transposed_operands=False), steps=3, ga=2)
     tr = run(LLamaOptions(matmul_type="e4m3", lmhead_transposed_operands=True), steps=3, ga=2)
