@@ -164,6 +164,10 @@ def main():
     ap.add_argument("--kmajor-backward", type=int, default=None, help="0 = backward GEMMs read MN-major operands in place, 1 = transposed fp8 copies (default)")
     ap.add_argument("--cuda-graphs", type=int, default=-1,
                     help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs; default), 0 = plain launches")
+    ap.add_argument("--time-breakdown", action="store_true", help="diagnostic: print milliseconds per phase of the last timed step to stderr (adds a synchronisation per step)")
+    ap.add_argument("--memcpy-all-gather", action="store_true", help="weight all-gathers as copy-engine transfers instead of SM stores")
+    ap.add_argument("--memcpy-send-recv", action="store_true", help="with --all-to-all-reduce: gradient exchange as copy-engine transfers")
+    ap.add_argument("--all-to-all-reduce", action="store_true")
     ap.add_argument("--zero-level", type=int, default=0, help="0 = pick from --gpus (1 GPU: unsharded, else 3)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -202,7 +206,10 @@ def main():
     opts.offload_opt_m = opts.offload_opt_v = args.offload_opt
     opts.persistent_quants = args.persistent_quants
     B, T, GA = args.batch, args.seq_len, args.grad_accum
-    trainer = api.LLMQTrainer(ngpu=args.gpus, config=cfg, options=opts, batch_size=B, seq_len=T, grad_accum=GA)
+    opts.use_all_to_all_reduce = bool(args.all_to_all_reduce)
+    opts.trigger_timing_events = bool(args.time_breakdown)
+    trainer = api.LLMQTrainer(ngpu=args.gpus, config=cfg, options=opts, batch_size=B, seq_len=T, grad_accum=GA,
+                              memcpy_all_gather=args.memcpy_all_gather, memcpy_send_recv=args.memcpy_send_recv)
     trainer.init_weights()
     dev, comm, rank = trainer.device, trainer.comm, trainer.rank
     gen = torch.Generator().manual_seed(1234 + rank)
@@ -246,6 +253,8 @@ def main():
     sync_all()
     launches = L.launch_count - l0
     ms_dev = e0.elapsed_time(e1)
+    if args.time_breakdown and isinstance(res, dict) and res.get("time_breakdown"):
+        print(f"[rank {rank}] phases of the last step (ms): " + ", ".join(f"{k} {v:.1f}" for k, v in res["time_breakdown"].items()), file=sys.stderr)
     # ---- end-to-end region through the public API with pinned-host inputs and host-read results
     sync_all()
     t0 = time.perf_counter()
