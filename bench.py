@@ -164,6 +164,7 @@ def main():
     ap.add_argument("--kmajor-backward", type=int, default=None, help="0 = backward GEMMs read MN-major operands in place, 1 = transposed fp8 copies (default)")
     ap.add_argument("--cuda-graphs", type=int, default=-1,
                     help="1 = replay per-block CUDA graphs (the reference's --use-cuda-graphs; default), 0 = plain launches")
+    ap.add_argument("--gather-behind-first-gemm", type=int, default=None, help="ZeRO-3: 1 = weight gathers start beside attention, 0 = at the top of the previous block (default)")
     ap.add_argument("--time-breakdown", action="store_true", help="diagnostic: print milliseconds per phase of the last timed step to stderr (adds a synchronisation per step)")
     ap.add_argument("--memcpy-all-gather", action="store_true", help="weight all-gathers as copy-engine transfers instead of SM stores")
     ap.add_argument("--memcpy-send-recv", action="store_true", help="with --all-to-all-reduce: gradient exchange as copy-engine transfers")
@@ -208,6 +209,8 @@ def main():
     B, T, GA = args.batch, args.seq_len, args.grad_accum
     opts.use_all_to_all_reduce = bool(args.all_to_all_reduce)
     opts.trigger_timing_events = bool(args.time_breakdown)
+    if args.gather_behind_first_gemm is not None:
+        opts.gather_behind_first_gemm = bool(args.gather_behind_first_gemm)
     trainer = api.LLMQTrainer(ngpu=args.gpus, config=cfg, options=opts, batch_size=B, seq_len=T, grad_accum=GA,
                               memcpy_all_gather=args.memcpy_all_gather, memcpy_send_recv=args.memcpy_send_recv)
     trainer.init_weights()
@@ -241,29 +244,44 @@ def main():
     sync_all()
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
-    # ---- device-timed region
     l0 = L.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    for i in range(args.steps):
-        step_no += 1
-        res = run_step(i, step_no, False)
-    e1.record()
-    sync_all()
-    launches = L.launch_count - l0
-    ms_dev = e0.elapsed_time(e1)
-    if args.time_breakdown and isinstance(res, dict) and res.get("time_breakdown"):
-        print(f"[rank {rank}] phases of the last step (ms): " + ", ".join(f"{k} {v:.1f}" for k, v in res["time_breakdown"].items()), file=sys.stderr)
-    # ---- end-to-end region through the public API with pinned-host inputs and host-read results
-    sync_all()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        step_no += 1
-        res = run_step(i, step_no, True)
-        loss_host = res["loss"]
-    sync_all()
-    ms_e2e = (time.perf_counter() - t0) * 1e3
+    loss_host = None
+
+    def device_region():
+        nonlocal step_no, res
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        e0.record()
+        for i in range(args.steps):
+            step_no += 1
+            res = run_step(i, step_no, False)
+        e1.record()
+        sync_all()
+        return e0.elapsed_time(e1)
+
+    def e2e_region():
+        # end to end through the public API: pinned-host inputs every step, the step's loss and norm read on the host
+        nonlocal step_no, res, loss_host
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            step_no += 1
+            res = run_step(i, step_no, True)
+            loss_host = res["loss"]
+        sync_all()
+        return (time.perf_counter() - t0) * 1e3
+
+    if os.environ.get("LLMQ_BENCH_E2E_FIRST", "0") == "1":      # diagnostic: which of the two regions runs first
+        ms_e2e = e2e_region()
+        l0 = L.launch_count
+        ms_dev = device_region()
+        launches = L.launch_count - l0
+    else:
+        ms_dev = device_region()
+        launches = L.launch_count - l0
+        if args.time_breakdown and isinstance(res, dict) and res.get("time_breakdown"):
+            print(f"[rank {rank}] phases of the last step (ms): " + ", ".join(f"{k} {v:.1f}" for k, v in res["time_breakdown"].items()), file=sys.stderr)
+        ms_e2e = e2e_region()
     sampler.stop_flag.set()
     sampler.join(timeout=3)
     t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=dev)

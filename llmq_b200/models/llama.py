@@ -115,6 +115,8 @@ class LlamaModel:
         if (opts.use_cuda_graphs and self.device.type == "cuda" and not opts.offload_residual
                 and os.environ.get("LLMQ_GEMM_POLL", "0") != "1"):
             self.graphs = _BlockGraphs(self.device)
+        # sharded weights on several GPUs: each block body runs as two parts with the next block's weight gather started between them
+        self._split_blocks = bool(self.comm.world > 1 and opts.shard_weights and opts.gather_behind_first_gemm)
         self.weights = WeightsManager(cfg, opts, self.comm, self.device, self.fused)
         self.grads = GradientManager(cfg, opts, self.comm, self.device, self.weights)
         self.opt_state = OptimizerStateManager(cfg, opts, self.comm, self.device, self.weights)
@@ -294,6 +296,7 @@ class LlamaModel:
         self.stack_report = {"capacity": self.stack.capacity, "high_water": self.stack.high_water, "breakdown": sizing.high_water_breakdown()}
         self.tmp = t
         self.host_scalars = torch.zeros(8, dtype=torch.float32, pin_memory=(dev.type == "cuda"))
+        self._submarks = bool(self.opts.trigger_timing_events and os.environ.get("LLMQ_SUBMARKS", "0") == "1")
 
     # ---- optional phase timing (--debug-time-breakdown): CUDA events on the main stream, read after the step
     def _mark(self, name: str) -> None:
@@ -301,6 +304,11 @@ class LlamaModel:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record(torch.cuda.current_stream(self.device))
             self._marks.append((name, ev))
+
+    def _submark(self, name: str) -> None:
+        """Finer marks inside the blocks (LLMQ_SUBMARKS=1, plain launches only): the phase totals then cover only their tails."""
+        if self._submarks and self.graphs is None:
+            self._mark(name)
 
     def time_breakdown(self) -> Dict[str, float]:
         """Milliseconds per phase since the last call (phases of all micro-steps are summed); synchronises."""
@@ -512,11 +520,13 @@ class LlamaModel:
         a.x.written(0)
         self.stats.zero_()
         w.gather_block(0)
+        split = self._split_blocks
         for l in range(L):
-            if l + 1 < L:
+            if l + 1 < L and not split:
                 w.gather_block(l + 1)
             r_layer = nvtx.push(f"Layer {l}", self.device)
             p = w.get_block(l)
+            self._submark("f:wait")
             am, _ = self._slot(l, S_LN1)
             if l == 0:
                 K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.x.current(0), p.ln1_w, cfg.rms_norm_eps, absmax=am)
@@ -524,10 +534,17 @@ class LlamaModel:
                 K.rmsnorm_forward(a.ln1[l], a.rstd1[l], a.res_att[l - 1], p.ln1_w, cfg.rms_norm_eps, residual_out=a.x.write_target(l),
                                   inp2=self.tmp.proj, absmax=am)
                 a.x.written(l)
-            if self.graphs is not None:
-                self.graphs.run(("fwd", l), lambda: self._forward_block(l, p))
+            self._submark("f:ln1")
+            if split:
+                # The gather of the next block starts behind this block's first GEMM, so that its pushes (a grid over all SMs)
+                # share the GPU with RoPE and attention, whose many short CTAs flow around them, instead of holding up the
+                # CTA pairs of a persistent GEMM: started at the top of the block they delayed the QKV GEMM by their own length.
+                self._run_block(("fwd", l, 0), lambda: self._forward_block(l, p, 0))
+                if l + 1 < L:
+                    w.gather_block(l + 1)
+                self._run_block(("fwd", l, 1), lambda: self._forward_block(l, p, 1))
             else:
-                self._forward_block(l, p)
+                self._run_block(("fwd", l), lambda: self._forward_block(l, p))
             w.release_block(l)
             nvtx.pop(r_layer)
         K.rmsnorm_forward(self.lnf, self.rstd_f, a.res_att[L - 1], w.get_lnf(), cfg.rms_norm_eps, residual_out=a.x.write_target(L),
@@ -535,18 +552,32 @@ class LlamaModel:
         a.x.written(L)
         nvtx.pop(r_fwd)
 
-    def _forward_block(self, l: int, p) -> None:
+    def _run_block(self, key: tuple, fn) -> None:
+        if self.graphs is not None:
+            self.graphs.run(key, fn)
+        else:
+            fn()
+
+    def _forward_block(self, l: int, p, part: Optional[int] = None) -> None:
+        """``part``: None = the whole block, 0 = the QKV projection only, 1 = everything behind it."""
         cfg, a, t = self.cfg, self.acts, self.tmp
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         BT = self.B * self.T
-        qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
-        self._fwd_mm(qkv2d, a.ln1[l], a.ln1_q[l] if self.quant else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b, ready=p.ready["qkv_w"])
+        if part != 1:
+            qkv2d = a.qkv[l].view(BT, cfg.qkv_channels)
+            self._fwd_mm(qkv2d, a.ln1[l], a.ln1_q[l] if self.quant else None, self._slot(l, S_LN1), p.qkv_w, p.scales["qkv_w"], p.qkv_b, ready=p.ready["qkv_w"])
+            self._submark("f:qkv")
+        if part == 0:
+            return
         K.rope(a.qkv[l], a.qkv[l], self.freqs, Hq, Hkv)
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
         K.attention_forward(att4, a.lse[l], a.qkv[l], Hq, Hkv, absmax=self._slot(l, S_ATT)[0] if self.quant else None)
+        self._submark("f:att")
         self._fwd_mm(t.proj, a.att[l], a.att_q[l] if self.quant else None, self._slot(l, S_ATT), p.o_w, p.scales["o_w"], ready=p.ready["o_w"])
+        self._submark("f:o")
         K.rmsnorm_forward(a.ln2[l], a.rstd2[l], a.x.current(l), p.ln2_w, cfg.rms_norm_eps, residual_out=a.res_att[l], inp2=t.proj,
                           absmax=self._slot(l, S_LN2)[0])
+        self._submark("f:ln2")
         if self._fuse_swiglu and (int(self.opts.fuse_swiglu) & 1) and p.ready["up_w"] is None:
             # up projection and SwiGLU from one accumulator tile: the activation never re-reads the projection
             am, sc = self._slot(l, S_LN2)
@@ -558,8 +589,11 @@ class LlamaModel:
                 K.gemm_swiglu_forward(a.up[l], a.swiglu[l], a.ln2[l], p.up_w, absmax=self._slot(l, S_SWIGLU)[0])
         else:
             self._fwd_mm(a.up[l], a.ln2[l], a.ln2_q[l] if self.quant else None, self._slot(l, S_LN2), p.up_w, p.scales["up_w"], ready=p.ready["up_w"])
+            self._submark("f:up")
             K.swiglu_forward(a.swiglu[l], a.up[l], absmax=self._slot(l, S_SWIGLU)[0])
+            self._submark("f:swiglu")
         self._fwd_mm(t.proj, a.swiglu[l], a.swiglu_q[l] if self.quant else None, self._slot(l, S_SWIGLU), p.down_w, p.scales["down_w"], ready=p.ready["down_w"])
+        self._submark("f:down")
 
     # ================================================================================== validation
     @torch.no_grad()
@@ -684,23 +718,33 @@ class LlamaModel:
             r_layer = nvtx.push(f"Layer {l}", self.device)
             dw, acc = g.get_block_full(l)
             a.x.prefetch(l - 1)
-            if l > 0:
+            split = self._split_blocks
+            if l > 0 and not split:
                 w.gather_block(l - 1)
             p = w.get_block(l)
-            if self.graphs is not None:
-                def body(l=l, p=p, dw=dw, acc=acc):
+            self._submark("b:wait")
+
+            def body(part, l=l, p=p, dw=dw, acc=acc):
+                if part != 1:
                     self._recompute_block(l, p)
-                    self._backward_block(l, p, dw, acc)
-                self.graphs.run(("bwd", l, bool(acc)), body)
+                    self._submark("b:recompute")
+                self._backward_block(l, p, dw, acc, part)
+            if split:
+                # as in forward(): the next gather starts behind the MLP and output-projection GEMMs, beside the attention kernels
+                self._run_block(("bwd", l, bool(acc), 0), lambda: body(0))
+                if l > 0:
+                    w.gather_block(l - 1)
+                self._run_block(("bwd", l, bool(acc), 1), lambda: body(1))
             else:
-                self._recompute_block(l, p)
-                self._backward_block(l, p, dw, acc)
+                self._run_block(("bwd", l, bool(acc)), lambda: body(None))
             # LN1 backward adds into the residual gradient, which then belongs to layer l-1 (or the embedding)
             slot = self._slot(l - 1, S_DRESFFN)[0] if l > 0 else None
             K.rmsnorm_backward(t.d_res, dw["ln1_w"], t.norm_scratch, t.d_ln, a.x.get(l), p.ln1_w, a.rstd1[l], absmax=slot,
                                accumulate_dweight=True)
+            self._submark("b:ln1")
             w.release_block(l)
             g.notify_block(l)
+            self._submark("b:notify")
             nvtx.pop(r_layer)
         if not cfg.tie_word_embeddings and micro_step == 0:
             g.nb_full["embed"].zero_()             # untied: nothing has written this buffer yet in this step
@@ -779,13 +823,17 @@ class LlamaModel:
                     and p.ready["down_w"] is None and p.ready["up_w"] is None
                     and not (self._fuse_swiglu and int(self.opts.fuse_swiglu) & 2))
 
-    def _backward_block(self, l: int, p, dw: Dict[str, torch.Tensor], acc: bool) -> None:
+    def _backward_block(self, l: int, p, dw: Dict[str, torch.Tensor], acc: bool, part: Optional[int] = None) -> None:
+        """``part``: None = the whole block, 0 = MLP and attention output projection, 1 = attention core and QKV projection."""
         cfg, a, t = self.cfg, self.acts, self.tmp
         Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         BT, q = self.B * self.T, self.quant
         sc_of = lambda s: self._slot(l, s)[1]
         fused_dw = getattr(self.grads, "fused_dw", None)
         rs = (lambda name: fused_dw(l, name)) if (fused_dw is not None and not self.mx) else (lambda name: None)
+        if part == 1:
+            self._backward_block_attention(l, p, dw, acc, rs, sc_of)
+            return
         # ---- MLP down:  d_sw = d_res @ Wdown ; dWdown += d_res^T @ swiglu
         fuse_sw = self._fuse_swiglu and bool(int(self.opts.fuse_swiglu) & 2) and p.ready["down_w"] is None
         two_pass = self._swiglu_two_pass(p)
@@ -805,28 +853,43 @@ class LlamaModel:
                      a.swiglu[l], a.swiglu_q[l] if q else None, sc_of(S_SWIGLU), p.down_w, p.scales["down_w"], acc, ready=p.ready["down_w"], dw_rs=rs("down_w"),
                      swiglu_inout=a.up[l] if fuse_sw else None, swiglu_absmax=self._slot(l, S_DMLPUP)[0], dout_qT=t.d_res_qT,
                      inp_qT_ready=sw_T_ready, before_dw=before_dw)
+        self._submark("b:down")
         ev_down = self._dw_events[-1] if self._dw_events else None      # dW(down) reads d_res / its fp8 copy
         # ---- SwiGLU backward, in place over the saved up-projection (unless the GEMM epilogue above already did it)
         if two_pass:
             K.swiglu_backward_quant(t.d_up_q, t.d_up_qT, self._slot(l, S_DMLPUP)[1], t.d_sw, a.up[l], self._slot(l, S_DMLPUP)[0])
         elif not fuse_sw:
             K.swiglu_backward(a.up[l], t.d_sw, a.up[l], absmax=self._slot(l, S_DMLPUP)[0])
+        self._submark("b:swiglu")
         # ---- MLP up:  d_ln2 = d_up @ Wup ; dWup += d_up^T @ ln2
         self._bwd_mm(t.d_ln, dw["up_w"], None, a.up[l], t.d_up_q if q else None, self._slot(l, S_DMLPUP),
                      a.ln2[l], a.ln2_q[l] if q else None, sc_of(S_LN2), p.up_w, p.scales["up_w"], acc, ready=p.ready["up_w"], dw_rs=rs("up_w"),
                      dout_qT=t.d_up_qT, dout_ready=two_pass)
+        self._submark("b:up")
         # ---- LN2 backward: d_res += ...   (d_res now is the gradient wrt the post-attention residual)
         self._wait_dw(ev_down)                                          # the next two kernels overwrite d_res and its fp8 copy
         K.rmsnorm_backward(t.d_res, dw["ln2_w"], t.norm_scratch, t.d_ln, a.res_att[l], p.ln2_w, a.rstd2[l],
                            absmax=self._slot(l, S_DRESATT)[0], accumulate_dweight=True)
+        self._submark("b:ln2")
         # ---- attention out projection
         self._bwd_mm(t.d_ln, dw["o_w"], None, t.d_res, t.d_res_q if q else None, self._slot(l, S_DRESATT),
                      a.att[l], a.att_q[l] if q else None, sc_of(S_ATT), p.o_w, p.scales["o_w"], acc, ready=p.ready["o_w"], dw_rs=rs("o_w"),
                      dout_qT=t.d_res_qT)
+        self._submark("b:o")
+        if part == 0:
+            self._join_dw()
+            return
+        self._backward_block_attention(l, p, dw, acc, rs, sc_of)
+
+    def _backward_block_attention(self, l: int, p, dw: Dict[str, torch.Tensor], acc: bool, rs, sc_of) -> None:
+        cfg, a, t = self.cfg, self.acts, self.tmp
+        Hq, Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        BT, q = self.B * self.T, self.quant
         # ---- attention core
         att4 = a.att[l].view(self.B, self.T, Hq, cfg.head_size)
         K.attention_backward(t.d_qkv, t.att_scratch, t.d_ln.view(self.B, self.T, Hq, cfg.head_size), att4, a.lse[l], a.qkv[l], Hq, Hkv)
         K.rope(t.d_qkv, t.d_qkv, self.freqs, Hq, Hkv, backward=True, absmax=self._slot(l, S_DQKV)[0])
+        self._submark("b:att")
         # ---- QKV projection
         dqkv2d = t.d_qkv.view(BT, cfg.qkv_channels)
         self._bwd_mm(t.d_ln, dw["qkv_w"], dw.get("qkv_b"), dqkv2d, t.d_qkv_q if q else None, self._slot(l, S_DQKV),

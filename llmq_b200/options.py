@@ -40,6 +40,10 @@ class LLamaOptions:
     # Also selected by matmul_type = "mxe4m3" / "mxfp8".
     block_scaled: bool = False
     swiglu_backward_two_pass: bool = True     # fp8 K-major backward: SwiGLU gradient as abs-max pass + quantise/transpose pass, its bf16 form never stored
+    # ZeRO-3: start the next block's weight gather behind the current block's first GEMM(s), beside attention, instead of at the
+    # top of the block (each block body then runs as two graphs).  Off: no gain measured on 2 GPUs (481.3 / 485.2 ms off, 483.9 /
+    # 482.8 ms on; the pushes need most SMs to fill NVLink - limited to 16 SMs the step took 492-507 ms).
+    gather_behind_first_gemm: bool = False
     kmajor_backward: bool = True              # fp8 backward GEMMs read transposed fp8 copies (all operands K-major) instead of MN-major tiles
     lmhead_transposed_operands: bool = True   # LM-head backward reads W^T / lnf^T copies (K-major GEMM operands)
     # ... and a transposed copy of each d(logits) chunk for the dW GEMM: no measurable gain (469.3 / 472.4 ms with, 472.1 / 470.7 ms

@@ -80,10 +80,11 @@ def _launch(opts_kw, fail_rank=-1, world=2):
 
 @pytest.mark.parametrize("kw", [dict(), dict(shard_gradients=True), dict(shard_weights=True, shard_gradients=True),
                                 dict(shard_weights=True, shard_gradients=True, matmul_type="e4m3", persistent_quants=True),
+                                dict(shard_weights=True, shard_gradients=True, gather_behind_first_gemm=True),
                                 dict(matmul_type="e4m3", recompute_block=True)], ids=lambda d: "+".join(map(str, d)) or "zero1")
 def test_two_ranks_match_single_rank(kw):
     from llmq_b200.parallel.comm import LocalComm
-    ref_out, ref_w = _run_model(LocalComm(), {k: v for k, v in kw.items() if not k.startswith("shard") and k != "persistent_quants"},
+    ref_out, ref_w = _run_model(LocalComm(), {k: v for k, v in kw.items() if not k.startswith("shard") and k not in ("persistent_quants", "gather_behind_first_gemm")},
                                 2 * B, slice(0, 2 * B))
     res = _launch(kw)
     assert all(v[0] == "ok" for v in res.values()), res

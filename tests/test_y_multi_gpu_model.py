@@ -38,15 +38,18 @@ def _worker(rank, world, port, q):
         runs += [(3, 2, "mx-nccl"), (3, 2, "mx-fused")]          # block-scaled e4m3 matmuls on sharded bf16 weights
         runs += [(3, 2, "pq-fused"), (3, 2, "pqhost-fused")]     # quantised shards kept for the whole step (device / pinned host)
         runs += [(2, 2, "copy-fused"), (3, 2, "copy-fused")]     # copy-engine all-gather and all-to-all reduction (the memcpy flags)
+        runs += [(3, 2, "split-fused")]                          # block bodies in two parts, the next gather started between them
         for zero, ga, mode in runs:
             if True:
                 mx = mode.startswith("mx-")
                 pq = mode.startswith("pq")
                 cp = mode.startswith("copy")
-                coll = mode.split("-")[1] if (mx or pq or cp) else mode.split("+")[0]
+                sp = mode.startswith("split")
+                coll = mode.split("-")[1] if (mx or pq or cp or sp) else mode.split("+")[0]
                 os.environ["LLMQ_GEMM_RS"] = "1" if mode.endswith("gemm_rs") else "0"
                 opts = LLamaOptions(matmul_type="mxe4m3" if mx else "e4m3", collectives=coll, momentum_type="bf16", variance_type="bf16")
                 opts.set_zero_level(zero)
+                opts.gather_behind_first_gemm = sp
                 if cp:
                     opts.memcpy_all_gather = opts.memcpy_send_recv = opts.use_all_to_all_reduce = True
                 if pq:
@@ -57,7 +60,7 @@ def _worker(rank, world, port, q):
                 assert (m.weights.fused is not None) == (coll == "fused"), (mode, zero)
                 assert (m.grads.fused is not None) == (coll == "fused"), (mode, zero)
                 assert m.grads.gemm_rs == mode.endswith("gemm_rs")
-                assert m.grads.a2a_copy == cp
+                assert m.grads.a2a_copy == cp and m._split_blocks == sp
                 m.init_weights(3)
                 out = []
                 for step in range(1, 4):
@@ -114,7 +117,8 @@ def test_fused_training_matches_nccl():
     assert a[-1][0] < a[0][0]
     # kept quantised shards change where the bytes come from, not the bytes (two runs of one mode differ in the last
     # digits of the gradient norm already, so the bound is the one used against NCCL above)
-    for mode in ("pq-fused", "pqhost-fused"):
+    # (the same holds for "split-fused", which only moves the gathers within the schedule)
+    for mode in ("pq-fused", "pqhost-fused", "split-fused"):
         for (l0, n0), (l1, n1) in zip(r0[(3, 2, "fused")], r0[(3, 2, mode)]):
             assert abs(l0 - l1) < 5e-3 and abs(n0 - n1) < 2e-2 * max(1.0, n0), (mode, r0[(3, 2, mode)], r0[(3, 2, "fused")])
         assert r0[(3, 2, mode)][0][0] == r0[(3, 2, "fused")][0][0]          # the first forward pass sees the same weights
