@@ -138,6 +138,25 @@ def bench_elementwise(a, tm):
     up, sw = _rand((rows, 2 * D), torch.bfloat16), torch.empty(rows, D, dtype=torch.bfloat16, device=DEV)
     ms = tm.time(lambda: K.swiglu_forward(sw, up, absmax=am))
     res["swiglu_forward"] = (ms, rows * D * 6)
+    # the fp8 K-major backward path: what it replaced (bf16 gradient, then quantise + transpose, plus the transposed recompute)
+    # and its two passes
+    F8 = torch.float8_e4m3fn
+    dq, dqt, act_t = torch.empty(rows, 2 * D, dtype=F8, device=DEV), torch.empty(2 * D, rows, dtype=F8, device=DEV), torch.empty(D, rows, dtype=F8, device=DEV)
+    dgrad = torch.empty(rows, 2 * D, dtype=torch.bfloat16, device=DEV)
+    am2, sc2 = torch.full((1,), 8.0, device=DEV), torch.empty(1, device=DEV)
+    ms = tm.time(lambda: K.swiglu_backward(dgrad, sw, up, absmax=am))
+    res["swiglu_backward_out_of_place"] = (ms, rows * D * 10)
+    ms = tm.time(lambda: K.quantize_transpose(dq, dqt, sc, dgrad, am))
+    res["quantize_transpose_dup"] = (ms, rows * D * 8)
+    ms = tm.time(lambda: K.swiglu_forward_transposed(act_t, up, known_absmax=am2, q_scale=sc2))
+    res["swiglu_forward_transposed"] = (ms, rows * D * 5)
+    ms = tm.time(lambda: K.swiglu_backward_stats(am, sw, up))
+    res["swiglu_backward_stats"] = (ms, rows * D * 6)
+    ms = tm.time(lambda: K.swiglu_backward_stats(am, sw, up, act_t=act_t, act_absmax=am2, act_scale=sc2))
+    res["swiglu_backward_stats_with_act"] = (ms, rows * D * 7)
+    ms = tm.time(lambda: K.swiglu_backward_quant(dq, dqt, sc, sw, up, am))
+    res["swiglu_backward_quant"] = (ms, rows * D * 10)
+    del dq, dqt, act_t, dgrad
     ms = tm.time(lambda: K.swiglu_backward(up, sw, up, absmax=am))
     res["swiglu_backward"] = (ms, rows * D * 10)
     swq = torch.empty(rows, D, dtype=torch.float8_e4m3fn, device=DEV)
