@@ -41,6 +41,7 @@ constexpr float kRescaleThreshold = 8.f;     // in log2 units
 struct FwdParams {
     int B, T, Hq, Hkv;
     float scale;
+    int turns;                   // 1: the two softmax warpgroups take turns with their exponentials
     __nv_bfloat16* out;          // (B, T, Hq, HS)
     float* lse;                  // (B, Hq, T), natural log
     float* absmax;               // optional
@@ -71,7 +72,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
     uint8_t* sK = sQ + 2 * TILE_BYTES;                    // [KV_STAGES][TILE_BYTES]
     uint8_t* sV = sK + KV_STAGES * TILE_BYTES;            // [KV_STAGES][TILE_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + KV_STAGES * TILE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -93,8 +94,9 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
     const int qcol = h * HS, kcol = (p.Hq + kvh) * HS, vcol = (p.Hq + p.Hkv + kvh) * HS;
 
     // barriers: 0 q_full | 1-2 k_full | 3-4 k_empty | 5-6 v_full | 7-8 v_empty | 9-10 s_full[X] | 11-12 p_ready[X] (first 64 keys)
-    //           | 13-14 o_done[X] | 15-16 p_ready2[X] (second 64 keys).  One phase per key tile on every barrier, so a waiter that
-    //           comes late can be at most one completed phase behind and the parity test stays unambiguous.
+    //           | 13-14 o_done[X] | 15-16 p_ready2[X] (second 64 keys) | 17-18 turn[X] (the exponentials of X may start).
+    //           One phase per key tile on every barrier, so a waiter that comes late can be at most one completed phase
+    //           behind and the parity test stays unambiguous.
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0;
     auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
@@ -105,13 +107,19 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
     auto p_ready = [&](int x) { return bar0 + 8u * (11 + x); };
     auto o_done = [&](int x) { return bar0 + 8u * (13 + x); };
     auto p_ready2 = [&](int x) { return bar0 + 8u * (15 + x); };
+    auto turn = [&](int x) { return bar0 + 8u * (17 + x); };
+    // The two softmax warpgroups take turns with their exponentials for as long as both tiles have key tiles left: a warp alone
+    // on its SM sub-partition keeps the MUFU unit busy (128 x 32 ex2 at 4 per clock), two at once only halve each other's rate
+    // and then both wait for the tensor pipe together.  Tile A goes first; each warpgroup hands the turn over when its
+    // exponentials are issued.
+    const int n_pair = (active == 2 && p.turns) ? min(nA, nB) : 0;
     if (tid == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(k_full(s), 1); mbar_init(v_full(s), 1);
             mbar_init(k_empty(s), active); mbar_init(v_empty(s), active);      // one arrival per active query tile
         }
-        for (int x = 0; x < 2; ++x) { mbar_init(s_full(x), 1); mbar_init(p_ready(x), 4); mbar_init(p_ready2(x), 4); mbar_init(o_done(x), 1); }
+        for (int x = 0; x < 2; ++x) { mbar_init(s_full(x), 1); mbar_init(p_ready(x), 4); mbar_init(p_ready2(x), 4); mbar_init(o_done(x), 1); mbar_init(turn(x), 4); }
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -249,6 +257,11 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
                 }
                 m_ref = m_new;
             }
+            // ---- this warpgroup's turn: A waits for B's tile j-1 (phase j-1 of turn[A]), B for A's tile j (phase j of turn[B])
+            const bool paired = j < n_pair;
+            if (paired && (x == 1 || j > 0)) {
+                if (!mbar_wait(turn(x), (x == 0 ? j - 1 : j) & 1, abort_flag)) { ok = false; break; }
+            }
             // ---- probabilities -> bf16 -> tensor memory (over the first 64 score columns, which are in registers by now)
             const float moff = m_ref * sl2;
             float sum0 = 0.f, sum1 = 0.f;
@@ -269,6 +282,7 @@ attn_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_qkv,     // qk
                     warp_arrive(p_ready(x));
                 }
             }
+            if (paired) warp_arrive(turn(1 - x));              // every exponential of this tile is issued: the other tile's turn
             const float sum = sum0 + sum1;
             l_sum += sum;
             tmem_st_wait();
@@ -353,6 +367,8 @@ int llmq_attention_forward_pingpong(void* out, float* lse, const void* qkv, int 
     FwdParams p{};
     p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.scale = 1.f / sqrtf(static_cast<float>(HS));
     p.out = static_cast<__nv_bfloat16*>(out); p.lse = lse; p.absmax = absmax; p.status = status;
+    static const bool no_turns = [] { const char* e = getenv("LLMQ_ATTN_FWD_TURNS"); return e && e[0] == '0'; }();      // for A/B measurements
+    p.turns = no_turns ? 0 : 1;
     const int nqb = (T + 2 * BQ - 1) / (2 * BQ);
     attn_fwd_pingpong_kernel<<<nqb * Hq * B, NUM_THREADS, smem, s>>>(tmap, p);
     return LLMQ_LAUNCH_CHECK();
