@@ -7,12 +7,13 @@ can never pass on a PyTorch fallback by accident.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
 import torch
 
-_LIBDIR = Path(__file__).resolve().parent.parent / "lib"
+_LIBDIR = Path(os.environ.get("LLMQ_LIB_DIR") or (Path(__file__).resolve().parent.parent / "lib"))      # LLMQ_LIB_DIR: another build of the libraries
 _lock = threading.Lock()
 _kernels = None
 _rt = None
