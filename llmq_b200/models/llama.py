@@ -16,7 +16,6 @@ from __future__ import annotations
 
 import os
 
-import math
 from types import SimpleNamespace
 from typing import Dict, List, Optional
 
